@@ -1,0 +1,21 @@
+"""Compile the CPU oracle (test infrastructure) into oracle/liboracle.so with g++."""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SRC = os.path.join(HERE, "oracle.cpp")
+OUT = os.path.join(HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= os.path.getmtime(SRC):
+        return OUT
+    cmd = ["g++", "-O3", "-march=x86-64-v3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-pthread", "-o", OUT, SRC]
+    subprocess.run(cmd, check=True)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv))
