@@ -1,0 +1,349 @@
+"""datago_b200: the B200 image path of datago (decode -> bucket -> resize -> crop) behind a C ABI.
+
+This module is the thin Python side of include/datago_b200.h (ctypes, no torch needed).  Pixel work is
+done by the CUDA library only; importing works without a GPU (bucket / geometry / sharding queries are
+host code), but creating a device context or running a batch without one raises DatagoB200Error.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from .build import build as _build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+DG_DEVICE_NONE = -1
+BATCH_DECODE_ONLY = 1
+BATCH_TIMING = 2
+STAGES = ("unstuff", "huffman", "idct", "color", "resize_h", "resize_v", "resize_shift")
+STATUS_NAMES = {0: "ok", 1: "invalid", 2: "cuda", 3: "truncated", 4: "bad_marker", 5: "unsupported", 6: "bad_table",
+                7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large"}
+
+
+class DatagoB200Error(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"[{STATUS_NAMES.get(code, code)}] {msg}")
+        self.code = code
+
+
+class ImageConfig(C.Structure):
+    _fields_ = [("crop_and_resize", C.c_int32), ("default_image_size", C.c_uint32), ("downsampling_ratio", C.c_uint32),
+                ("min_aspect_ratio", C.c_double), ("max_aspect_ratio", C.c_double)]
+
+    @classmethod
+    def from_dict(cls, d):
+        """From the `image_config` object of datago's client JSON (missing numbers default to 0, as serde does)."""
+        return cls(int(bool(d.get("crop_and_resize", False))), int(d.get("default_image_size", 0)),
+                   int(d.get("downsampling_ratio", 0)), float(d.get("min_aspect_ratio", 0.0)),
+                   float(d.get("max_aspect_ratio", 0.0)))
+
+
+class Plan(C.Structure):
+    _fields_ = [("src_w", C.c_uint32), ("src_h", C.c_uint32), ("channels", C.c_uint32), ("target_w", C.c_uint32),
+                ("target_h", C.c_uint32), ("new_w", C.c_uint32), ("new_h", C.c_uint32), ("crop_left", C.c_double),
+                ("crop_top", C.c_double), ("crop_w", C.c_double), ("crop_h", C.c_double), ("identity", C.c_int32),
+                ("key", C.c_char * 16)]
+
+    def as_tuple(self):
+        return (self.key.decode(), self.target_w, self.target_h, self.new_w, self.new_h, self.crop_left,
+                self.crop_top, self.crop_w, self.crop_h, self.identity)
+
+
+class JpegInfo(C.Structure):
+    _fields_ = [("width", C.c_uint32), ("height", C.c_uint32), ("channels", C.c_uint32), ("hsamp", C.c_uint32),
+                ("vsamp", C.c_uint32), ("mcux", C.c_uint32), ("mcuy", C.c_uint32), ("restart_interval", C.c_uint32),
+                ("scan_offset", C.c_uint64), ("scan_len", C.c_uint64)]
+
+
+class Item(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("len", C.c_uint64), ("raw_w", C.c_uint32), ("raw_h", C.c_uint32),
+                ("raw_c", C.c_uint32), ("reserved", C.c_uint32), ("forced_key", C.c_char_p)]
+
+
+class Result(C.Structure):
+    _fields_ = [("status", C.c_int32), ("original_width", C.c_uint32), ("original_height", C.c_uint32),
+                ("width", C.c_uint32), ("height", C.c_uint32), ("channels", C.c_uint32), ("bit_depth", C.c_uint32),
+                ("nbytes", C.c_uint64), ("device_data", C.c_void_p), ("plan", Plan)]
+
+
+_lib = None
+
+
+def library_path():
+    return os.path.join(_HERE, "libdatago_b200.so")
+
+
+def lib():
+    """The loaded CUDA library; built on first use when the .so is missing or older than its sources."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if not os.path.exists(path) or os.environ.get("DATAGO_B200_REBUILD"):
+        path = _build()
+    L = C.CDLL(path)
+    vp, u32p, u64p = C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint64)
+    sig = {
+        "dg_last_error": (C.c_char_p, []),
+        "dg_version": (C.c_char_p, []),
+        "dg_ctx_create": (C.c_int, [C.c_int, C.POINTER(ImageConfig), C.POINTER(vp)]),
+        "dg_ctx_create_on_stream": (C.c_int, [C.c_int, C.POINTER(ImageConfig), vp, C.POINTER(vp)]),
+        "dg_ctx_destroy": (None, [vp]),
+        "dg_ctx_stream": (vp, [vp]),
+        "dg_size_list": (C.c_int, [C.POINTER(ImageConfig), C.c_int, vp, vp]),
+        "dg_bucket_table": (C.c_int, [vp, C.c_int, vp, vp, vp, vp]),
+        "dg_closest_aspect_ratio": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_char_p]),
+        "dg_aspect_ratio_to_str": (None, [C.c_uint32, C.c_uint32, C.c_char_p]),
+        "dg_plan_geometry": (C.c_int, [vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, C.POINTER(Plan)]),
+        "dg_jpeg_probe": (C.c_int, [C.c_char_p, C.c_uint64, C.POINTER(JpegInfo)]),
+        "dg_rank_slice": (C.c_int, [C.c_uint64, C.c_uint64, C.c_uint64, u64p, u64p]),
+        "dg_key_hash": (C.c_uint64, [C.c_char_p, C.c_uint64]),
+        "dg_key_rank": (C.c_uint64, [C.c_char_p, C.c_uint64, C.c_uint64]),
+        "dg_batch_create": (C.c_int, [vp, C.POINTER(Item), C.c_int, C.c_uint32, C.POINTER(vp)]),
+        "dg_batch_upload": (C.c_int, [vp]),
+        "dg_batch_run": (C.c_int, [vp]),
+        "dg_batch_download": (C.c_int, [vp, C.POINTER(vp)]),
+        "dg_batch_sync": (C.c_int, [vp]),
+        "dg_batch_result": (C.c_int, [vp, C.c_int, C.POINTER(Result)]),
+        "dg_batch_stage_ms": (C.c_int, [vp, C.POINTER(C.c_float)]),
+        "dg_batch_counters": (C.c_int, [vp, u64p, u64p, u32p]),
+        "dg_batch_debug": (C.c_int, [vp, C.c_int, C.POINTER(vp), u64p, C.POINTER(vp)]),
+        "dg_batch_destroy": (None, [vp]),
+        "dg_process": (C.c_int, [vp, C.POINTER(Item), C.c_int, C.c_uint32, C.POINTER(vp), C.POINTER(Result)]),
+        "dg_copy_to_host": (C.c_int, [vp, vp, vp, C.c_uint64]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
+           "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
+           "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
+           "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_debug dg_batch_destroy dg_process "
+           "dg_copy_to_host").split()
+
+
+def _check(rc):
+    if rc:
+        raise DatagoB200Error(rc, lib().dg_last_error().decode())
+
+
+# ---- host-only helpers ----------------------------------------------------------------------------------------------
+def size_list(image_config):
+    cfg = ImageConfig.from_dict(image_config)
+    w = np.zeros(4096, np.uint32)
+    h = np.zeros(4096, np.uint32)
+    n = lib().dg_size_list(C.byref(cfg), 4096, w.ctypes.data, h.ctypes.data)
+    return [(int(w[i]), int(h[i])) for i in range(n)]
+
+
+def aspect_ratio_to_str(w, h):
+    b = C.create_string_buffer(16)
+    lib().dg_aspect_ratio_to_str(w, h, b)
+    return b.value.decode()
+
+
+def jpeg_probe(data: bytes):
+    info = JpegInfo()
+    _check(lib().dg_jpeg_probe(data, len(data), C.byref(info)))
+    return info
+
+
+def rank_slice(quorum, rank, world_size):
+    s, e = C.c_uint64(), C.c_uint64()
+    _check(lib().dg_rank_slice(quorum, rank, world_size, C.byref(s), C.byref(e)))
+    return int(s.value), int(e.value)
+
+
+def key_hash(key: str):
+    b = key.encode()
+    return int(lib().dg_key_hash(b, len(b)))
+
+
+def key_rank(key: str, world_size: int):
+    b = key.encode()
+    return int(lib().dg_key_rank(b, len(b), world_size))
+
+
+# ---- context and batches --------------------------------------------------------------------------------------------
+class Context:
+    """One device + stream + (optional) aspect-ratio transform; the counterpart of the `Option<ARAwareTransform>`
+    a DatagoClient holds (src/client.rs:92-95 of datago)."""
+
+    def __init__(self, device=0, image_config=None, stream=None):
+        self._h = C.c_void_p()
+        cfg = ImageConfig.from_dict(image_config) if image_config else None
+        ref = C.byref(cfg) if cfg is not None else None
+        if stream is None:
+            _check(lib().dg_ctx_create(device, ref, C.byref(self._h)))
+        else:
+            _check(lib().dg_ctx_create_on_stream(device, ref, C.c_void_p(stream), C.byref(self._h)))
+        self.device = device
+        self.image_config = image_config
+
+    def close(self):
+        if self._h:
+            lib().dg_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def stream(self):
+        return lib().dg_ctx_stream(self._h)
+
+    def bucket_table(self):
+        """[(key, aspect ratio, w, h)] sorted by aspect ratio."""
+        w = np.zeros(4096, np.uint32)
+        h = np.zeros(4096, np.uint32)
+        ar = np.zeros(4096, np.float64)
+        keys = C.create_string_buffer(16 * 4096)
+        n = lib().dg_bucket_table(self._h, 4096, w.ctypes.data, h.ctypes.data, ar.ctypes.data, C.addressof(keys))
+        return [(keys.raw[16 * i:16 * i + 16].split(b"\0")[0].decode(), float(ar[i]), int(w[i]), int(h[i]))
+                for i in range(n)]
+
+    def closest_aspect_ratio(self, w, h):
+        b = C.create_string_buffer(16)
+        _check(lib().dg_closest_aspect_ratio(self._h, w, h, b))
+        return b.value.decode()
+
+    def plan_geometry(self, w, h, channels=3, forced_key=None):
+        p = Plan()
+        _check(lib().dg_plan_geometry(self._h, w, h, channels, forced_key.encode() if forced_key else None, C.byref(p)))
+        return p
+
+    def batch(self, inputs, forced_keys=None, flags=0):
+        return Batch(self, inputs, forced_keys, flags)
+
+    def process(self, inputs, forced_keys=None, flags=0):
+        """create + upload + run + download + sync in one go: list of (status, numpy array or None, Result)."""
+        with self.batch(inputs, forced_keys, flags) as b:
+            b.upload()
+            b.run()
+            outs = b.download()
+            b.sync()
+            res = [b.result(i) for i in range(len(b))]
+        return [(r.status, o if r.status == 0 else None, r) for r, o in zip(res, outs)]
+
+    def copy_to_host(self, device_ptr, nbytes):
+        out = np.empty(nbytes, np.uint8)
+        _check(lib().dg_copy_to_host(self._h, out.ctypes.data, C.c_void_p(device_ptr), nbytes))
+        return out
+
+
+class Batch:
+    """A batch of samples.  inputs: bytes (JPEG files) or numpy uint8 arrays HxW / HxWx3 (raw pixels)."""
+
+    def __init__(self, ctx, inputs, forced_keys=None, flags=0):
+        self.ctx = ctx
+        self._n = len(inputs)
+        self._items = (Item * max(1, self._n))()
+        self._keep = []
+        for i, x in enumerate(inputs):
+            it = self._items[i]
+            if isinstance(x, (bytes, bytearray, memoryview)):
+                buf = (C.c_char * len(x)).from_buffer_copy(bytes(x)) if not isinstance(x, bytes) else x
+                self._keep.append(buf)
+                it.data = C.cast(C.c_char_p(buf) if isinstance(buf, bytes) else buf, C.c_void_p)
+                it.len = len(x)
+            else:
+                a = np.ascontiguousarray(x, np.uint8)
+                self._keep.append(a)
+                it.data = a.ctypes.data
+                it.len = a.nbytes
+                it.raw_h, it.raw_w = a.shape[:2]
+                it.raw_c = 1 if a.ndim == 2 else a.shape[2]
+            if forced_keys and forced_keys[i]:
+                it.forced_key = forced_keys[i].encode()
+        self._h = C.c_void_p()
+        _check(lib().dg_batch_create(ctx._h, self._items, self._n, flags, C.byref(self._h)))
+        self._outs = None
+
+    def __len__(self):
+        return self._n
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def close(self):
+        if self._h:
+            lib().dg_batch_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload(self):
+        _check(lib().dg_batch_upload(self._h))
+
+    def run(self):
+        _check(lib().dg_batch_run(self._h))
+
+    def sync(self):
+        _check(lib().dg_batch_sync(self._h))
+
+    def result(self, i):
+        r = Result()
+        _check(lib().dg_batch_result(self._h, i, C.byref(r)))
+        return r
+
+    def host_buffers(self):
+        """numpy arrays shaped like each ok payload (None for failed items)."""
+        outs = []
+        for i in range(self._n):
+            r = self.result(i)
+            if r.status:
+                outs.append(None)
+            else:
+                shape = (r.height, r.width, 3) if r.channels == 3 else (r.height, r.width)
+                outs.append(np.empty(shape, np.uint8))
+        return outs
+
+    def download(self, outs=None):
+        """Queue device->host copies into `outs` (from host_buffers()); valid after sync()."""
+        if outs is None:
+            outs = self.host_buffers()
+        ptrs = (C.c_void_p * max(1, self._n))(*[o.ctypes.data if o is not None else None for o in outs])
+        self._outs = outs
+        _check(lib().dg_batch_download(self._h, ptrs))
+        return outs
+
+    def stage_ms(self):
+        ms = (C.c_float * len(STAGES))()
+        _check(lib().dg_batch_stage_ms(self._h, ms))
+        return dict(zip(STAGES, [float(v) for v in ms]))
+
+    def counters(self):
+        h2d, d2h, k = C.c_uint64(), C.c_uint64(), C.c_uint32()
+        _check(lib().dg_batch_counters(self._h, C.byref(h2d), C.byref(d2h), C.byref(k)))
+        return dict(h2d_bytes=int(h2d.value), d2h_bytes=int(d2h.value), kernel_launches=int(k.value))
+
+    def debug_coefficients(self, i):
+        """int16 [blocks, 64] coefficients of JPEG item i in scan order (single-wave batches, after sync)."""
+        coef, nb = C.c_void_p(), C.c_uint64()
+        _check(lib().dg_batch_debug(self._h, i, C.byref(coef), C.byref(nb), None))
+        raw = self.ctx.copy_to_host(coef.value, int(nb.value) * 128)
+        return raw.view(np.int16).reshape(int(nb.value), 64)
+
+    def debug_decoded(self, i):
+        r = self.result(i)
+        dec = C.c_void_p()
+        _check(lib().dg_batch_debug(self._h, i, None, None, C.byref(dec)))
+        n = r.original_width * r.original_height * r.channels
+        raw = self.ctx.copy_to_host(dec.value, n)
+        return raw.reshape((r.original_height, r.original_width, 3) if r.channels == 3 else (r.original_height, r.original_width))

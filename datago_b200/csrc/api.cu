@@ -1,0 +1,989 @@
+// C ABI of the B200 image path (declared in include/datago_b200.h) and the batch scheduler behind it.
+//
+// A batch is planned on the host (headers, bucket geometry, filter tables, device descriptors), its inputs are
+// staged in pinned memory and uploaded with a handful of large copies, and its images run through the kernels
+// in "waves": groups of images whose intermediates (unstuffed streams, coefficients, planes, full-size decoded
+// images, resize intermediates) share one scratch block that the next wave reuses.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <array>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "host.h"
+#include "kernels.h"
+
+using namespace dg;
+
+// ---------------------------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+static int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define CU(call)                                                                                         \
+    do {                                                                                                 \
+        cudaError_t e_ = (call);                                                                         \
+        if (e_ != cudaSuccess) return fail(DG_E_CUDA, "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+    } while (0)
+
+extern "C" const char* dg_last_error(void) { return g_err; }
+extern "C" const char* dg_version(void) { return "datago_b200 0.1 (sm_100a)"; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// context: device, stream, transform, caches of device and pinned blocks
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+struct Block {
+    void* ptr = nullptr;
+    size_t size = 0;
+    bool busy = false;
+};
+
+// Grow-only cache: a batch borrows blocks and hands them back; nothing is freed before the ctx goes away, so steady
+// state makes no allocation calls.
+struct BlockCache {
+    bool pinned;
+    std::vector<Block> blocks;
+    explicit BlockCache(bool p) : pinned(p) {}
+    int acquire(size_t size, int* index) {
+        if (size == 0) size = 256;
+        int best = -1;
+        for (size_t i = 0; i < blocks.size(); ++i)
+            if (!blocks[i].busy && blocks[i].size >= size && (best < 0 || blocks[i].size < blocks[best].size)) best = (int)i;
+        if (best < 0) {
+            // replace the largest idle block that is too small, so the cache does not pile up stale sizes
+            int victim = -1;
+            for (size_t i = 0; i < blocks.size(); ++i)
+                if (!blocks[i].busy && (victim < 0 || blocks[i].size > blocks[victim].size)) victim = (int)i;
+            Block nb;
+            nb.size = size + size / 8 + 4096;
+            if (victim >= 0) {
+                if (pinned) cudaFreeHost(blocks[victim].ptr); else cudaFree(blocks[victim].ptr);
+                blocks[victim] = Block();
+            }
+            cudaError_t e = pinned ? cudaHostAlloc(&nb.ptr, nb.size, cudaHostAllocDefault) : cudaMalloc(&nb.ptr, nb.size);
+            if (e != cudaSuccess) return fail(DG_E_CUDA, "%s of %zu bytes: %s", pinned ? "cudaHostAlloc" : "cudaMalloc", nb.size, cudaGetErrorString(e));
+            if (victim >= 0) { blocks[victim] = nb; best = victim; }
+            else { blocks.push_back(nb); best = (int)blocks.size() - 1; }
+        }
+        blocks[best].busy = true;
+        *index = best;
+        return DG_OK;
+    }
+    void release(int index) { if (index >= 0) blocks[index].busy = false; }
+    void clear() {
+        for (auto& b : blocks) if (b.ptr) { if (pinned) cudaFreeHost(b.ptr); else cudaFree(b.ptr); }
+        blocks.clear();
+    }
+};
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct dg_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    bool has_tfm = false;
+    dg_image_config cfg{};
+    Transform tfm;
+    std::mutex mu;
+    BlockCache dev{false}, pin{true};
+    size_t wave_bytes = (size_t)8 << 30;  // coefficient bytes per wave
+};
+
+static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool have_stream, dg_ctx** out) {
+    if (!out) return fail(DG_E_INVALID, "out is NULL");
+    *out = nullptr;
+    if (device != DG_DEVICE_NONE) {
+        int count = 0;
+        cudaError_t e = cudaGetDeviceCount(&count);
+        if (e != cudaSuccess || count == 0)
+            return fail(DG_E_CUDA, "no usable CUDA device (%s); this library has no CPU path", e != cudaSuccess ? cudaGetErrorString(e) : "count is 0");
+        if (device < 0 || device >= count) return fail(DG_E_INVALID, "device %d out of range (%d present)", device, count);
+    }
+    dg_ctx* c = new dg_ctx();
+    c->device = device;
+    if (cfg && cfg->crop_and_resize) {
+        if (!config_valid(*cfg)) { delete c; return fail(DG_E_INVALID, "image_config: size, ratio and aspect-ratio bounds must be positive and ordered"); }
+        c->cfg = *cfg;
+        c->tfm = make_transform(*cfg);
+        c->has_tfm = !c->tfm.buckets.empty();
+        if (!c->has_tfm) { delete c; return fail(DG_E_INVALID, "image_config yields an empty bucket table"); }
+    }
+    if (device == DG_DEVICE_NONE) { *out = c; return DG_OK; }  // planning only: bucket and geometry queries
+    if (cudaSetDevice(device) != cudaSuccess) { delete c; return fail(DG_E_CUDA, "cudaSetDevice(%d) failed", device); }
+    if (have_stream) c->stream = (cudaStream_t)stream;
+    else {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return fail(DG_E_CUDA, "cudaStreamCreate failed"); }
+        c->own_stream = true;
+    }
+    if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
+    *out = c;
+    return DG_OK;
+}
+
+extern "C" int dg_ctx_create(int device, const dg_image_config* cfg, dg_ctx** out) { return ctx_create(device, cfg, nullptr, false, out); }
+extern "C" int dg_ctx_create_on_stream(int device, const dg_image_config* cfg, void* s, dg_ctx** out) { return ctx_create(device, cfg, s, true, out); }
+
+extern "C" void dg_ctx_destroy(dg_ctx* c) {
+    if (!c) return;
+    if (c->device == DG_DEVICE_NONE) { delete c; return; }
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    c->dev.clear();
+    c->pin.clear();
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+extern "C" void* dg_ctx_stream(dg_ctx* c) { return c ? (void*)c->stream : nullptr; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// host-only entry points
+// ---------------------------------------------------------------------------------------------------------------
+extern "C" int dg_size_list(const dg_image_config* cfg, int max_n, uint32_t* w, uint32_t* h) {
+    if (!cfg || !config_valid(*cfg)) return 0;
+    auto l = image_size_list(*cfg);
+    for (int i = 0; i < (int)l.size() && i < max_n; ++i) { w[i] = l[i].first; h[i] = l[i].second; }
+    return (int)l.size();
+}
+
+extern "C" int dg_bucket_table(const dg_ctx* c, int max_n, uint32_t* w, uint32_t* h, double* ar, char* keys) {
+    if (!c || !c->has_tfm) return 0;
+    const auto& b = c->tfm.buckets;
+    for (int i = 0; i < (int)b.size() && i < max_n; ++i) {
+        if (w) w[i] = b[i].w;
+        if (h) h[i] = b[i].h;
+        if (ar) ar[i] = b[i].ar;
+        if (keys) memcpy(keys + 16 * i, b[i].key, 16);
+    }
+    return (int)b.size();
+}
+
+extern "C" int dg_closest_aspect_ratio(const dg_ctx* c, int32_t w, int32_t h, char key_out[16]) {
+    if (!c || !key_out) return fail(DG_E_INVALID, "NULL argument");
+    if (!c->has_tfm) return fail(DG_E_NO_TRANSFORM, "ctx has no crop_and_resize transform");
+    memcpy(key_out, c->tfm.buckets[c->tfm.closest(w, h)].key, 16);
+    return DG_OK;
+}
+
+extern "C" void dg_aspect_ratio_to_str(uint32_t w, uint32_t h, char key_out[16]) { format_key(w, h, key_out); }
+
+extern "C" int dg_plan_geometry(const dg_ctx* c, uint32_t w, uint32_t h, uint32_t channels, const char* forced_key, dg_plan* out) {
+    if (!c || !out || w == 0 || h == 0) return fail(DG_E_INVALID, "NULL argument or empty image");
+    if (!c->has_tfm) return fail(DG_E_NO_TRANSFORM, "ctx has no crop_and_resize transform");
+    int rc = plan_geometry(c->tfm, w, h, channels, forced_key, out);
+    if (rc) return fail(rc, "aspect ratio key '%s' is not in the bucket table", forced_key ? forced_key : "");
+    return DG_OK;
+}
+
+extern "C" int dg_jpeg_probe(const uint8_t* data, uint64_t len, dg_jpeg_info* out) {
+    if (!data || !out) return fail(DG_E_INVALID, "NULL argument");
+    JpegHeader h;
+    int rc = parse_jpeg_header(data, len, h);
+    if (rc) return fail(rc, "JPEG header rejected (status %d)", rc);
+    out->width = h.width; out->height = h.height; out->channels = h.ncomp == 1 ? 1 : 3;
+    out->hsamp = h.hs; out->vsamp = h.vs; out->mcux = h.mcux; out->mcuy = h.mcuy; out->restart_interval = h.restart;
+    out->scan_offset = h.scan_off; out->scan_len = h.scan_len;
+    return DG_OK;
+}
+
+extern "C" int dg_rank_slice(uint64_t quorum, uint64_t rank, uint64_t world, uint64_t* start, uint64_t* end) {
+    if (world == 0 || rank >= world || !start || !end) return fail(DG_E_INVALID, "rank must be less than world size");
+    const uint64_t chunk = quorum / world, rem = quorum % world;
+    *start = rank < rem ? rank * (chunk + 1) : rem * (chunk + 1) + (rank - rem) * chunk;
+    *end = rank + 1 <= rem ? (rank + 1) * (chunk + 1) : rem * (chunk + 1) + (rank + 1 - rem) * chunk;
+    return DG_OK;
+}
+
+extern "C" uint64_t dg_key_hash(const char* key, uint64_t len) { return siphash13_str(key, len); }
+extern "C" uint64_t dg_key_rank(const char* key, uint64_t len, uint64_t world) { return world ? siphash13_str(key, len) % world : 0; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// batch planning
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+// Appends arrays to one host image of the batch's device metadata; offsets become device pointers after upload.
+struct Meta {
+    std::vector<uint8_t> bytes;
+    size_t put(const void* src, size_t n, size_t align = 16) {
+        size_t off = align_up(bytes.size(), align);
+        bytes.resize(off + n);
+        if (n) memcpy(bytes.data() + off, src, n);
+        return off;
+    }
+    template <typename T> size_t put(const std::vector<T>& v, size_t align = 16) { return put(v.data(), v.size() * sizeof(T), align); }
+};
+
+struct OwnerMapOff {  // OwnerMap with meta offsets instead of pointers
+    size_t first = 0, coarse = 0;
+    uint32_t n = 0, shift = 6, total = 0;
+};
+
+OwnerMapOff put_owner_map(Meta& m, const std::vector<uint32_t>& first /* n + 1 */) {
+    OwnerMapOff o;
+    o.n = (uint32_t)first.size() - 1;
+    o.total = first.back();
+    o.shift = 6;
+    std::vector<uint32_t> coarse((o.total >> o.shift) + 1, 0);
+    uint32_t owner = 0;
+    for (size_t k = 0; k < coarse.size(); ++k) {
+        const uint32_t idx = (uint32_t)k << o.shift;
+        while (owner + 1 < o.n && first[owner + 1] <= idx) ++owner;
+        coarse[k] = owner;
+    }
+    o.first = m.put(first);
+    o.coarse = m.put(coarse);
+    return o;
+}
+
+struct ItemPlan {
+    int status = DG_OK;
+    bool is_jpeg = false, transform = false;
+    uint32_t w = 0, h = 0, c = 0;  // decoded / raw size
+    dg_plan plan{};
+    uint32_t out_w = 0, out_h = 0;
+    size_t out_off = 0, out_bytes = 0;  // in the output arena
+    size_t raw_in_off = 0;              // raw pixel inputs: offset in the input arena
+    JpegHeader* hdr = nullptr;
+    int wave = -1, wave_local = -1;     // JPEG index inside its wave
+    size_t coef_off_blocks = 0, decoded_off = 0;
+    uint32_t nblocks = 0;
+};
+
+struct WavePlan {
+    int first_item = 0, last_item = 0;  // [first, last)
+    std::vector<JpegDesc> descs;
+    std::vector<uint32_t> spec_list, restart_list, restart_first, block_first, color_first;
+    std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
+    std::vector<uint32_t> pass_first[4];
+    std::vector<CopyJob> copies;
+    std::vector<uint32_t> copy_first;
+    // scratch layout (bytes from the wave scratch base)
+    size_t us_bytes = 0, coef_blocks = 0, plane_bytes = 0, decoded_bytes = 0, mid_bytes = 0, nseg = 0;
+    size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
+    // meta offsets
+    size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0;
+    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy;
+};
+
+struct StageEvent { int stage; cudaEvent_t a, b; };
+
+}  // namespace
+
+struct dg_batch {
+    dg_ctx* ctx = nullptr;
+    uint32_t flags = 0;
+    int n = 0;
+    std::vector<ItemPlan> items;
+    std::vector<JpegHeader> headers;
+    std::vector<WavePlan> waves;
+    Meta meta;
+    // persistent device block: [meta | status | blob | raw inputs | outputs]
+    int blk_persist = -1, blk_scratch = -1, blk_pin = -1, blk_pin_status = -1;
+    uint8_t* d_persist = nullptr;
+    uint8_t* d_scratch = nullptr;
+    uint8_t* h_pin = nullptr;       // pinned image of [meta | status zeros | blob]
+    uint32_t* h_status = nullptr;   // pinned, n words
+    size_t off_meta = 0, off_status = 0, off_blob = 0, off_rawin = 0, off_out = 0, persist_bytes = 0;
+    size_t blob_bytes = 0, rawin_bytes = 0, out_bytes = 0, pin_bytes = 0;
+    size_t m_huff = 0, m_qt = 0, m_tables = 0;
+    std::vector<const uint8_t*> raw_src;  // caller memory of raw items (valid until upload)
+    uint64_t h2d = 0, d2h = 0;
+    uint32_t launches = 0;
+    bool uploaded = false, ran = false;
+    std::vector<StageEvent> events;
+    float stage_ms[DG_STAGE_COUNT] = {0};
+};
+
+namespace {
+
+struct Planner {
+    dg_ctx* ctx;
+    dg_batch* b;
+    std::unordered_map<std::string, uint32_t> huff_ids, qt_ids;
+    std::vector<HuffTable> huff_pool;
+    std::vector<uint16_t> qt_pool;
+    std::map<std::array<uint64_t, 4>, std::pair<size_t, FilterTable*>> table_ids;  // key -> (word offset, table)
+    std::vector<FilterTable*> tables;
+    std::vector<uint32_t> table_words;
+
+    ~Planner() { for (auto* t : tables) delete t; }
+
+    int huff_id(const JpegHeader::RawHuff& raw, uint32_t* id) {
+        std::string key((const char*)raw.bits, 17);
+        key.append((const char*)raw.vals, 256);
+        auto it = huff_ids.find(key);
+        if (it != huff_ids.end()) { *id = it->second; return DG_OK; }
+        HuffTable t;
+        if (!build_huff_table(raw, t)) return DG_E_BAD_TABLE;
+        *id = (uint32_t)huff_pool.size();
+        huff_pool.push_back(t);
+        huff_ids.emplace(std::move(key), *id);
+        return DG_OK;
+    }
+    uint32_t qt_id(const uint16_t* q) {
+        std::string key((const char*)q, 128);
+        auto it = qt_ids.find(key);
+        if (it != qt_ids.end()) return it->second;
+        uint32_t id = (uint32_t)(qt_pool.size() / 64);
+        qt_pool.insert(qt_pool.end(), q, q + 64);
+        qt_ids.emplace(std::move(key), id);
+        return id;
+    }
+    // returns the table and its word offset in the pool
+    const FilterTable* table(int in_size, double in0, double in1, int out_size, size_t* word_off) {
+        std::array<uint64_t, 4> key;
+        key[0] = (uint64_t)in_size << 32 | (uint32_t)out_size;
+        memcpy(&key[1], &in0, 8);
+        memcpy(&key[2], &in1, 8);
+        key[3] = 0;
+        auto it = table_ids.find(key);
+        if (it != table_ids.end()) { *word_off = it->second.first; return it->second.second; }
+        FilterTable* t = new FilterTable(make_filter_table(in_size, in0, in1, out_size));
+        tables.push_back(t);
+        size_t off = align_up(table_words.size(), 4);
+        table_words.resize(off + t->words());
+        t->pack(table_words.data() + off);
+        table_ids.emplace(key, std::make_pair(off, t));
+        *word_off = off;
+        return t;
+    }
+};
+
+// One image's chain of convolution passes (see kernels_resize.cu).  Buffers are described by byte offsets first and
+// turned into pointers when the device blocks are known.
+struct PassDraft {
+    int stage;  // 0 H1, 1 V1, 2 H2, 3 V2
+    size_t tab_off;
+    const FilterTable* tab;
+    uint32_t t0, count;       // outputs along the filtered axis
+    uint32_t other;           // extent along the other axis
+    // resolved when chaining
+};
+
+}  // namespace
+
+// Plans the resize of one image: appends passes / copy jobs to the wave.  src: device pointer of the source image
+// (tight pitch), dst: device pointer of the payload (tight pitch), mid: scratch for intermediates.
+static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C, const uint8_t* src, uint8_t* dst,
+                        uint8_t* mid_base, size_t* mid_used) {
+    const uint32_t w = p.src_w, h = p.src_h, tw = p.target_w, th = p.target_h;
+    auto add_copy = [&](const uint8_t* s, uint32_t pitch, uint32_t row_bytes, uint32_t rows) {
+        CopyJob j;
+        j.src = s; j.dst = dst; j.src_pitch = pitch; j.row_bytes = row_bytes; j.rows = rows; j.tile_first = 0;
+        wv.copies.push_back(j);
+    };
+    if (p.identity) { add_copy(src, w * C, w * C, h); return; }
+    const bool h1 = p.new_w != w, v1 = p.new_h != h;
+    const bool h2 = (double)tw != p.crop_w || p.crop_left != std::round(p.crop_left);
+    const bool v2 = (double)th != p.crop_h || p.crop_top != std::round(p.crop_top);
+    size_t o_h1 = 0, o_v1 = 0, o_h2 = 0, o_v2 = 0;
+    const FilterTable* T_h1 = h1 ? pl.table((int)w, 0.0, (double)w, (int)p.new_w, &o_h1) : nullptr;
+    const FilterTable* T_v1 = v1 ? pl.table((int)h, 0.0, (double)h, (int)p.new_h, &o_v1) : nullptr;
+    const FilterTable* T_h2 = h2 ? pl.table((int)p.new_w, p.crop_left, p.crop_left + p.crop_w, (int)tw, &o_h2) : nullptr;
+    const FilterTable* T_v2 = v2 ? pl.table((int)p.new_h, p.crop_top, p.crop_top + p.crop_h, (int)th, &o_v2) : nullptr;
+    // region of the resized (new_w x new_h) image that the crop step reads
+    int ca, cb, ra, rb;
+    if (h2) { ca = T_h2->first_in(); cb = T_h2->last_in(0, (int)tw); } else { ca = (int)p.crop_left; cb = ca + (int)tw; }
+    if (v2) { ra = T_v2->first_in(); rb = T_v2->last_in(0, (int)th); } else { ra = (int)p.crop_top; rb = ra + (int)th; }
+    // rows of the horizontally resized image that the vertical pass reads
+    int ma, mb;
+    if (v1) { ma = T_v1->start[ra]; mb = T_v1->last_in(ra, rb); } else { ma = ra; mb = rb; }
+
+    struct Buf { const uint8_t* ptr; uint32_t pitch; int col0, row0; };  // origin in the current coordinate system
+    Buf cur{src, w * C, 0, 0};
+    const int n_pass = (int)h1 + (int)v1 + (int)h2 + (int)v2;
+    int done = 0;
+    auto next_dst = [&](uint32_t out_w, uint32_t out_h, uint32_t* pitch) -> uint8_t* {
+        if (done + 1 == n_pass) { *pitch = tw * C; return dst; }
+        *pitch = (uint32_t)align_up((size_t)out_w * C, 16);
+        uint8_t* ptr = mid_base + *mid_used;
+        *mid_used += align_up((size_t)*pitch * out_h, 256);
+        return ptr;
+    };
+    auto emit = [&](int stage, bool horizontal, const FilterTable* T, size_t tab_off, uint32_t t0, uint32_t out_w, uint32_t out_h,
+                    const uint8_t* s, int32_t origin, uint32_t spitch, uint8_t* d, uint32_t dpitch) {
+        ConvPass cp;
+        memset(&cp, 0, sizeof cp);
+        cp.src = s; cp.dst = d; cp.src_pitch = spitch; cp.dst_pitch = dpitch; cp.out_w = out_w; cp.out_h = out_h;
+        cp.channels = C; cp.src_origin = origin; cp.t0 = t0; cp.tab_n = (uint32_t)T->n; cp.window = (uint32_t)T->window;
+        cp.precision = (uint32_t)T->precision; cp.tab_off = tab_off;
+        cp.tiles_x = horizontal ? conv_h_tiles_x(out_w) : conv_v_tiles_x(out_w * C);
+        wv.passes[stage].push_back(cp);
+        ++done;
+    };
+    if (h1) {  // source rows [ma, mb) -> columns [ca, cb)
+        uint32_t pitch;
+        const uint32_t ow = (uint32_t)(cb - ca), oh = (uint32_t)(mb - ma);
+        uint8_t* d = next_dst(ow, oh, &pitch);
+        emit(0, true, T_h1, o_h1, (uint32_t)ca, ow, oh, cur.ptr + (size_t)(ma - cur.row0) * cur.pitch, cur.col0, cur.pitch, d, pitch);
+        cur = Buf{d, pitch, ca, ma};
+    }
+    if (v1) {  // rows [ma, mb) -> rows [ra, rb), columns [ca, cb)
+        uint32_t pitch;
+        const uint32_t ow = (uint32_t)(cb - ca), oh = (uint32_t)(rb - ra);
+        uint8_t* d = next_dst(ow, oh, &pitch);
+        emit(1, false, T_v1, o_v1, (uint32_t)ra, ow, oh, cur.ptr + (size_t)(ca - cur.col0) * C, cur.row0, cur.pitch, d, pitch);
+        cur = Buf{d, pitch, ca, ra};
+    }
+    if (h2) {  // columns [ca, cb) -> output columns [0, tw), rows [ra, rb)
+        uint32_t pitch;
+        const uint32_t oh = (uint32_t)(rb - ra);
+        uint8_t* d = next_dst(tw, oh, &pitch);
+        emit(2, true, T_h2, o_h2, 0, tw, oh, cur.ptr + (size_t)(ra - cur.row0) * cur.pitch, cur.col0, cur.pitch, d, pitch);
+        cur = Buf{d, pitch, 0, ra};
+        ca = 0;
+    }
+    if (v2) {  // rows [ra, rb) -> output rows [0, th)
+        uint32_t pitch;
+        uint8_t* d = next_dst(tw, th, &pitch);
+        emit(3, false, T_v2, o_v2, 0, tw, th, cur.ptr + (size_t)(ca - cur.col0) * C, cur.row0, cur.pitch, d, pitch);
+        cur = Buf{d, pitch, 0, 0};
+    }
+    if (n_pass == 0)  // same scale, integral crop: a strided copy
+        add_copy(src + ((size_t)ra * w + ca) * C, w * C, tw * C, th);
+}
+
+// worst-case scratch of the intermediates of one image's resize
+static size_t resize_mid_bound(const dg_plan& p, uint32_t C) {
+    if (p.identity) return 0;
+    const size_t a = align_up((size_t)p.new_w * C, 16) * (size_t)(std::max(p.src_h, p.new_h) + 8);
+    const size_t b = align_up((size_t)p.new_w * C, 16) * (size_t)(p.new_h + 8);
+    return align_up(a, 256) + 2 * align_up(b, 256);
+}
+
+static int abandon(dg_batch* b, int rc) {
+    dg_ctx* ctx = b->ctx;
+    ctx->dev.release(b->blk_persist);
+    ctx->dev.release(b->blk_scratch);
+    ctx->pin.release(b->blk_pin);
+    ctx->pin.release(b->blk_pin_status);
+    delete b;
+    return rc;
+}
+
+extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, dg_batch** out) {
+    if (!ctx || !out || n < 0 || (n > 0 && !items)) return fail(DG_E_INVALID, "NULL argument");
+    *out = nullptr;
+    if (ctx->device == DG_DEVICE_NONE) return fail(DG_E_INVALID, "planning-only context: pixel work needs a CUDA device (there is no CPU path)");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    dg_batch* b = new dg_batch();
+    b->ctx = ctx; b->flags = flags; b->n = n;
+    b->items.resize(n);
+    b->headers.resize(n);
+    b->raw_src.assign(n, nullptr);
+    const bool transform = ctx->has_tfm && !(flags & DG_BATCH_DECODE_ONLY);
+    Planner pl{ctx, b};
+
+    // ---- pass 1: headers, geometry, arena layout -----------------------------------------------------------------------
+    size_t blob = 0, rawin = 0, outb = 0;
+    for (int i = 0; i < n; ++i) {
+        ItemPlan& it = b->items[i];
+        const dg_item& src = items[i];
+        it.transform = transform;
+        if (!src.data) { it.status = DG_E_INVALID; continue; }
+        if (src.raw_w) {
+            if (src.raw_h == 0 || (src.raw_c != 1 && src.raw_c != 3) || src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; continue; }
+            it.w = src.raw_w; it.h = src.raw_h; it.c = src.raw_c;
+        } else {
+            JpegHeader& h = b->headers[i];
+            it.status = parse_jpeg_header(src.data, src.len, h);
+            if (it.status) continue;
+            if (h.scan_len > 0xFFFFFF00ull) { it.status = DG_E_TOO_LARGE; continue; }
+            it.is_jpeg = true; it.hdr = &h;
+            it.w = h.width; it.h = h.height; it.c = h.ncomp == 1 ? 1 : 3;
+        }
+        if (transform) {
+            it.status = plan_geometry(ctx->tfm, it.w, it.h, it.c, src.forced_key, &it.plan);
+            if (it.status) continue;
+            it.out_w = it.plan.target_w; it.out_h = it.plan.target_h;
+        } else {
+            it.out_w = it.w; it.out_h = it.h;
+            it.plan.src_w = it.w; it.plan.src_h = it.h; it.plan.channels = it.c;
+        }
+        it.out_bytes = (size_t)it.out_w * it.out_h * it.c;
+        it.out_off = outb;
+        outb += align_up(it.out_bytes, 256);
+        if (it.is_jpeg) blob += align_up(b->headers[i].scan_len, 16) + 16;
+        else { it.raw_in_off = rawin; rawin += align_up((size_t)it.w * it.h * it.c, 256); b->raw_src[i] = src.data; }
+    }
+    b->blob_bytes = blob; b->rawin_bytes = rawin; b->out_bytes = outb;
+
+    // ---- pass 2: waves ----------------------------------------------------------------------------------------------------
+    {
+        WavePlan* wv = nullptr;
+        size_t coef_bytes = 0, big_bytes = 0;
+        for (int i = 0; i < n; ++i) {
+            ItemPlan& it = b->items[i];
+            if (it.status) continue;
+            size_t need_coef = 0, need_big = 0;
+            if (it.is_jpeg) {
+                const JpegHeader& h = *it.hdr;
+                it.nblocks = h.mcux * h.mcuy * (h.ncomp == 1 ? 1 : h.hs * h.vs + 2);
+                need_coef = (size_t)it.nblocks * 128;
+                if (transform) need_big += align_up((size_t)it.w * it.h * it.c, 256);
+            }
+            if (transform) need_big += resize_mid_bound(it.plan, it.c);
+            if (!wv || (coef_bytes + need_coef > ctx->wave_bytes && coef_bytes > 0) || (big_bytes + need_big > 2 * ctx->wave_bytes && big_bytes > 0)) {
+                b->waves.emplace_back();
+                wv = &b->waves.back();
+                wv->first_item = i;
+                coef_bytes = big_bytes = 0;
+            }
+            coef_bytes += need_coef; big_bytes += need_big;
+            it.wave = (int)b->waves.size() - 1;
+            wv->last_item = i + 1;
+        }
+    }
+
+    // ---- pass 3: per-wave scratch layout and JPEG descriptors ------------------------------------------------------
+    size_t scratch_max = 0, blob_off = 0;
+    for (WavePlan& wv : b->waves) {
+        size_t us = 0, planes = 0, decoded = 0, mids = 0, blocks = 0, segs = 0;
+        uint32_t color_tiles_total = 0, restart_total = 0;
+        wv.block_first.push_back(0);
+        wv.color_first.push_back(0);
+        wv.restart_first.push_back(0);
+        for (int i = wv.first_item; i < wv.last_item; ++i) {
+            ItemPlan& it = b->items[i];
+            if (it.status || it.wave < 0) continue;
+            if (transform) mids += resize_mid_bound(it.plan, it.c);
+            if (!it.is_jpeg) continue;
+            const JpegHeader& h = *it.hdr;
+            JpegDesc d;
+            memset(&d, 0, sizeof d);
+            for (uint32_t c = 0; c < 3 && !it.status; ++c) {
+                const uint32_t cc = c < h.ncomp ? c : 0;
+                d.qt[c] = pl.qt_id(h.qt[h.comp_tq[cc]]);
+                int rc = pl.huff_id(h.dc[h.comp_td[cc]], &d.dc_tab[c]);
+                if (!rc) rc = pl.huff_id(h.ac[h.comp_ta[cc]], &d.ac_tab[c]);
+                if (rc) it.status = rc;
+            }
+            if (it.status) continue;  // nothing has been laid out for this image yet
+            d.raw_off = blob_off; d.raw_len = (uint32_t)h.scan_len;
+            blob_off += align_up(h.scan_len, 16) + 16;
+            d.us_off = us; us += align_up(h.scan_len + 32, 16);
+            d.block_off = blocks; d.nblocks = it.nblocks;
+            d.width = h.width; d.height = h.height; d.mcux = h.mcux; d.mcuy = h.mcuy;
+            d.ncomp = h.ncomp; d.hs = h.hs; d.vs = h.vs; d.bpm = h.ncomp == 1 ? 1 : h.hs * h.vs + 2;
+            for (uint32_t c = 0; c < 3; ++c) {
+                const uint32_t hs = c == 0 ? h.hs : 1, vs = c == 0 ? h.vs : 1;
+                d.plane_pitch[c] = h.mcux * hs * 8;
+                d.plane_rows[c] = h.mcuy * vs * 8;
+                if (c < h.ncomp) { d.plane_off[c] = planes; planes += align_up((size_t)d.plane_pitch[c] * d.plane_rows[c], 256); }
+            }
+            d.restart = h.restart;
+            const uint32_t mcus = h.mcux * h.mcuy;
+            d.nseg = h.restart ? (mcus + h.restart - 1) / h.restart : 1;
+            d.seg_off = (uint32_t)segs; segs += d.nseg;
+            d.item = (uint32_t)i;
+            if (transform) { d.out_off = decoded; it.decoded_off = decoded; decoded += align_up((size_t)it.w * it.h * it.c, 256); }
+            else d.out_off = it.out_off;
+            it.coef_off_blocks = blocks;
+            blocks += it.nblocks;
+            it.wave_local = (int)wv.descs.size();
+            if (h.restart) { wv.restart_list.push_back((uint32_t)wv.descs.size()); restart_total += d.nseg; wv.restart_first.push_back(restart_total); }
+            else wv.spec_list.push_back((uint32_t)wv.descs.size());
+            wv.descs.push_back(d);
+            wv.block_first.push_back((uint32_t)blocks);
+            color_tiles_total += color_tiles(h.width, h.height);
+            wv.color_first.push_back(color_tiles_total);
+        }
+        wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
+        size_t o = 0;
+        wv.off_us = o; o += align_up(us, 256);
+        wv.off_uslen = o; o += align_up(wv.descs.size() * 4, 256);
+        wv.off_segfound = o; o += align_up(wv.descs.size() * 4, 256);
+        wv.off_segstart = o; o += align_up(segs * 4, 256);
+        wv.off_coef = o; o += align_up(blocks * 128, 256);
+        wv.off_planes = o; o += align_up(planes, 256);
+        wv.off_decoded = o; o += align_up(decoded, 256);
+        wv.off_mid = o; o += align_up(mids, 256);
+        wv.total = o;
+        scratch_max = std::max(scratch_max, o);
+    }
+
+    // ---- device and pinned blocks (addresses are needed by the resize descriptors) ------------------------------------
+    // persistent layout: [status | blob | raw inputs | outputs | meta]; meta size is known only after planning the
+    // resize passes, so it gets a bound: descriptors + tables are small next to the pixel buffers.
+    int rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch);
+    if (rc) return abandon(b, rc);
+    b->d_scratch = (uint8_t*)ctx->dev.blocks[b->blk_scratch].ptr;
+
+    b->off_status = 0;
+    b->off_blob = align_up((size_t)n * 4, 256);
+    b->off_rawin = b->off_blob + align_up(blob, 256);
+    b->off_out = b->off_rawin + align_up(rawin, 256);
+    const size_t fixed_bytes = b->off_out + align_up(outb, 256);
+
+    // Resize descriptors hold device addresses inside the persistent block, whose size depends on the metadata that
+    // contains them.  So the passes are planned twice: once against a stand-in base to size the metadata (filter
+    // tables are cached, the second round is cheap), once with the real base address.
+    uint8_t* const kBaseS = b->d_scratch;
+    for (int round = 0; round < 2; ++round) {
+        uint8_t* baseP = round == 0 ? kBaseS : b->d_persist;
+        for (WavePlan& wv : b->waves) {
+            for (int s = 0; s < 4; ++s) { wv.passes[s].clear(); wv.pass_first[s].clear(); }
+            wv.copies.clear(); wv.copy_first.clear();
+            if (!transform) continue;
+            size_t mid_used = 0;
+            for (int i = wv.first_item; i < wv.last_item; ++i) {
+                ItemPlan& it = b->items[i];
+                if (it.status || it.wave < 0) continue;
+                const uint8_t* src = it.is_jpeg ? kBaseS + wv.off_decoded + it.decoded_off : baseP + b->off_rawin + it.raw_in_off;
+                uint8_t* dst = baseP + b->off_out + it.out_off;
+                plan_resize(pl, wv, it.plan, it.c, src, dst, kBaseS + wv.off_mid, &mid_used);
+            }
+            if (mid_used > wv.mid_bytes) return abandon(b, fail(DG_E_INVALID, "internal: resize scratch bound exceeded"));
+            for (int s = 0; s < 4; ++s) {
+                uint32_t t = 0;
+                wv.pass_first[s].push_back(0);
+                for (ConvPass& cp : wv.passes[s]) {
+                    cp.tile_first = t;
+                    t += (s & 1) ? conv_v_tiles(cp.out_w * cp.channels, cp.out_h) : conv_h_tiles(cp.out_w, cp.out_h);
+                    wv.pass_first[s].push_back(t);
+                }
+            }
+            uint32_t t = 0;
+            wv.copy_first.push_back(0);
+            for (CopyJob& j : wv.copies) {
+                j.tile_first = t;
+                t += (uint32_t)(((uint64_t)j.row_bytes * j.rows + kCopyTileBytes - 1) / kCopyTileBytes);
+                wv.copy_first.push_back(t);
+            }
+        }
+        // meta image
+        Meta& m = b->meta;
+        m.bytes.clear();
+        b->m_huff = m.put(pl.huff_pool, 16);
+        b->m_qt = m.put(pl.qt_pool, 16);
+        b->m_tables = m.put(pl.table_words, 16);
+        for (WavePlan& wv : b->waves) {
+            wv.m_descs = m.put(wv.descs, 16);
+            wv.m_spec = m.put(wv.spec_list);
+            wv.m_restart_list = m.put(wv.restart_list);
+            wv.m_restart = put_owner_map(m, wv.restart_first);
+            wv.m_blocks = put_owner_map(m, wv.block_first);
+            wv.m_color = put_owner_map(m, wv.color_first);
+            for (int s = 0; s < 4; ++s) {
+                wv.m_passes[s] = m.put(wv.passes[s], 16);
+                if (wv.pass_first[s].empty()) wv.pass_first[s].push_back(0);
+                wv.m_pass[s] = put_owner_map(m, wv.pass_first[s]);
+            }
+            wv.m_copies = m.put(wv.copies, 16);
+            if (wv.copy_first.empty()) wv.copy_first.push_back(0);
+            wv.m_copy = put_owner_map(m, wv.copy_first);
+        }
+        if (round == 0) {
+            b->off_meta = fixed_bytes;
+            b->persist_bytes = fixed_bytes + align_up(m.bytes.size(), 256);
+            rc = ctx->dev.acquire(b->persist_bytes, &b->blk_persist);
+            if (rc) return abandon(b, rc);
+            b->d_persist = (uint8_t*)ctx->dev.blocks[b->blk_persist].ptr;
+            if (!transform) break;  // no pointers inside the metadata
+        }
+    }
+
+    // ---- pinned staging: [status zeros | blob] + meta ----------------------------------------------------------------
+    b->pin_bytes = b->off_blob + align_up(blob, 256) + align_up(b->meta.bytes.size(), 256);
+    rc = ctx->pin.acquire(b->pin_bytes, &b->blk_pin);
+    if (!rc) rc = ctx->pin.acquire(std::max<size_t>((size_t)n * 4, 256), &b->blk_pin_status);
+    if (rc) return abandon(b, rc);
+    b->h_pin = (uint8_t*)ctx->pin.blocks[b->blk_pin].ptr;
+    b->h_status = (uint32_t*)ctx->pin.blocks[b->blk_pin_status].ptr;
+    memset(b->h_pin, 0, b->off_blob);
+    {
+        size_t off = 0;
+        for (WavePlan& wv : b->waves)
+            for (int i = wv.first_item; i < wv.last_item; ++i) {
+                const ItemPlan& it = b->items[i];
+                if (it.status || !it.is_jpeg || it.wave_local < 0) continue;
+                const JpegHeader& h = *it.hdr;
+                uint8_t* dst = b->h_pin + b->off_blob + off;
+                memcpy(dst, items[i].data + h.scan_off, h.scan_len);
+                const size_t padded = align_up(h.scan_len, 16) + 16;
+                memset(dst + h.scan_len, 0, padded - h.scan_len);
+                off += padded;
+            }
+    }
+    memcpy(b->h_pin + b->off_blob + align_up(blob, 256), b->meta.bytes.data(), b->meta.bytes.size());
+    *out = b;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_upload(dg_batch* b) {
+    if (!b) return fail(DG_E_INVALID, "NULL batch");
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    b->h2d = 0;
+    // status zeros + compressed blob
+    const size_t head = b->off_blob + align_up(b->blob_bytes, 256);
+    CU(cudaMemcpyAsync(b->d_persist, b->h_pin, head, cudaMemcpyHostToDevice, ctx->stream));
+    b->h2d += head;
+    // metadata
+    CU(cudaMemcpyAsync(b->d_persist + b->off_meta, b->h_pin + head, b->meta.bytes.size(), cudaMemcpyHostToDevice, ctx->stream));
+    b->h2d += b->meta.bytes.size();
+    // raw pixel inputs straight from caller memory
+    for (int i = 0; i < b->n; ++i) {
+        const ItemPlan& it = b->items[i];
+        if (it.status || it.is_jpeg || !b->raw_src[i]) continue;
+        const size_t bytes = (size_t)it.w * it.h * it.c;
+        CU(cudaMemcpyAsync(b->d_persist + b->off_rawin + it.raw_in_off, b->raw_src[i], bytes, cudaMemcpyHostToDevice, ctx->stream));
+        b->h2d += bytes;
+    }
+    b->uploaded = true;
+    return DG_OK;
+}
+
+static OwnerMap resolve(const dg_batch* b, const OwnerMapOff& o) {
+    OwnerMap m;
+    const uint8_t* base = b->d_persist + b->off_meta;
+    m.first = (const uint32_t*)(base + o.first);
+    m.coarse = (const uint32_t*)(base + o.coarse);
+    m.n = o.n; m.shift = o.shift; m.total = o.total;
+    return m;
+}
+
+extern "C" int dg_batch_run(dg_batch* b) {
+    if (!b) return fail(DG_E_INVALID, "NULL batch");
+    if (!b->uploaded) return fail(DG_E_INVALID, "dg_batch_run before dg_batch_upload");
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    const uint8_t* meta = b->d_persist + b->off_meta;
+    const bool timing = (b->flags & DG_BATCH_TIMING) != 0;
+    const bool transform = ctx->has_tfm && !(b->flags & DG_BATCH_DECODE_ONLY);
+    size_t ev = 0;
+    auto mark = [&](int stage, bool begin) -> cudaError_t {
+        if (!timing) return cudaSuccess;
+        if (begin) {
+            if (ev == b->events.size()) {
+                StageEvent se{stage, nullptr, nullptr};
+                cudaError_t e = cudaEventCreate(&se.a);
+                if (e == cudaSuccess) e = cudaEventCreate(&se.b);
+                if (e != cudaSuccess) return e;
+                b->events.push_back(se);
+            }
+            b->events[ev].stage = stage;
+            return cudaEventRecord(b->events[ev].a, s);
+        }
+        return cudaEventRecord(b->events[ev++].b, s);
+    };
+    b->launches = 0;
+    if (b->ran) CU(cudaMemsetAsync(b->d_persist + b->off_status, 0, (size_t)b->n * 4, s));  // status words of the previous run
+    for (WavePlan& wv : b->waves) {
+        uint8_t* sc = b->d_scratch;
+        if (!wv.descs.empty()) {
+            JpegWave w;
+            memset(&w, 0, sizeof w);
+            w.descs = (const JpegDesc*)(meta + wv.m_descs);
+            w.n = (uint32_t)wv.descs.size();
+            w.raw = b->d_persist + b->off_blob;
+            w.us = sc + wv.off_us;
+            w.us_len = (uint32_t*)(sc + wv.off_uslen);
+            w.seg_start = (uint32_t*)(sc + wv.off_segstart);
+            w.seg_found = (uint32_t*)(sc + wv.off_segfound);
+            w.coef = (int16_t*)(sc + wv.off_coef);
+            w.planes = sc + wv.off_planes;
+            w.out = transform ? sc + wv.off_decoded : b->d_persist + b->off_out;
+            w.status = (uint32_t*)(b->d_persist + b->off_status);
+            w.huff = (const HuffTable*)(meta + b->m_huff);
+            w.qt = (const uint16_t*)(meta + b->m_qt);
+            w.spec_list = (const uint32_t*)(meta + wv.m_spec);
+            w.n_spec = (uint32_t)wv.spec_list.size();
+            w.restart_list = (const uint32_t*)(meta + wv.m_restart_list);
+            w.restart_segs = resolve(b, wv.m_restart);
+            w.blocks = resolve(b, wv.m_blocks);
+            w.color_tiles = resolve(b, wv.m_color);
+            CU(mark(DG_STAGE_UNSTUFF, true));
+            launch_unstuff(w, s);
+            ++b->launches;
+            CU(mark(DG_STAGE_UNSTUFF, false));
+            CU(mark(DG_STAGE_HUFFMAN, true));
+            CU(cudaMemsetAsync(w.coef, 0, wv.coef_blocks * 128, s));
+            launch_huffman(w, s, &b->launches);
+            CU(mark(DG_STAGE_HUFFMAN, false));
+            CU(mark(DG_STAGE_IDCT, true));
+            launch_idct(w, s);
+            ++b->launches;
+            CU(mark(DG_STAGE_IDCT, false));
+            CU(mark(DG_STAGE_COLOR, true));
+            launch_color(w, s);
+            ++b->launches;
+            CU(mark(DG_STAGE_COLOR, false));
+        }
+        if (transform) {
+            const uint32_t* tables = (const uint32_t*)(meta + b->m_tables);
+            static const int kStageOf[4] = {DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V, DG_STAGE_RESIZE_SHIFT, DG_STAGE_RESIZE_SHIFT};
+            for (int st = 0; st < 4; ++st) {
+                if (wv.passes[st].empty()) continue;
+                CU(mark(kStageOf[st], true));
+                const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
+                if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
+                else launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, s);
+                ++b->launches;
+                CU(mark(kStageOf[st], false));
+            }
+            if (!wv.copies.empty()) {
+                CU(mark(DG_STAGE_RESIZE_SHIFT, true));
+                launch_copy((const CopyJob*)(meta + wv.m_copies), resolve(b, wv.m_copy), s);
+                ++b->launches;
+                CU(mark(DG_STAGE_RESIZE_SHIFT, false));
+            }
+        }
+    }
+    CU(cudaGetLastError());
+    b->ran = true;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_download(dg_batch* b, uint8_t* const* host_out) {
+    if (!b || !host_out) return fail(DG_E_INVALID, "NULL argument");
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    b->d2h = 0;
+    for (int i = 0; i < b->n; ++i) {
+        const ItemPlan& it = b->items[i];
+        if (it.status || !host_out[i]) continue;
+        CU(cudaMemcpyAsync(host_out[i], b->d_persist + b->off_out + it.out_off, it.out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        b->d2h += it.out_bytes;
+    }
+    return DG_OK;
+}
+
+static int device_status_to_code(uint32_t bits) {
+    if (bits == 0) return DG_OK;
+    if (bits & kStSyncLimit) return DG_E_SYNC_LIMIT;
+    if (bits & kStBadMarker) return DG_E_BAD_MARKER;
+    if (bits & (kStBadCode | kStCoefRange)) return DG_E_BAD_CODE;
+    return DG_E_TRUNCATED;
+}
+
+extern "C" int dg_batch_sync(dg_batch* b) {
+    if (!b) return fail(DG_E_INVALID, "NULL batch");
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    if (b->ran) {
+        CU(cudaMemcpyAsync(b->h_status, b->d_persist + b->off_status, (size_t)b->n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        b->d2h += (size_t)b->n * 4;
+    }
+    CU(cudaStreamSynchronize(ctx->stream));
+    if (b->ran) {
+        for (int i = 0; i < b->n; ++i)
+            if (b->items[i].status == DG_OK && b->h_status[i]) b->items[i].status = device_status_to_code(b->h_status[i]);
+        if (b->flags & DG_BATCH_TIMING) {
+            for (float& v : b->stage_ms) v = 0.f;
+            for (const StageEvent& se : b->events) {
+                float ms = 0.f;
+                if (cudaEventElapsedTime(&ms, se.a, se.b) == cudaSuccess) b->stage_ms[se.stage] += ms;
+            }
+        }
+    }
+    return DG_OK;
+}
+
+extern "C" int dg_batch_result(const dg_batch* b, int i, dg_result* out) {
+    if (!b || !out || i < 0 || i >= b->n) return fail(DG_E_INVALID, "bad index");
+    const ItemPlan& it = b->items[i];
+    memset(out, 0, sizeof *out);
+    out->status = it.status;
+    out->original_width = it.w; out->original_height = it.h;
+    if (it.status == DG_OK) {
+        out->width = it.out_w; out->height = it.out_h; out->channels = it.c; out->bit_depth = 8;
+        out->nbytes = it.out_bytes;
+        out->device_data = b->d_persist + b->off_out + it.out_off;
+    }
+    out->plan = it.plan;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_stage_ms(const dg_batch* b, float ms[DG_STAGE_COUNT]) {
+    if (!b || !ms) return fail(DG_E_INVALID, "NULL argument");
+    memcpy(ms, b->stage_ms, sizeof b->stage_ms);
+    return DG_OK;
+}
+
+extern "C" int dg_batch_counters(const dg_batch* b, uint64_t* h2d, uint64_t* d2h, uint32_t* launches) {
+    if (!b) return fail(DG_E_INVALID, "NULL batch");
+    if (h2d) *h2d = b->h2d;
+    if (d2h) *d2h = b->d2h;
+    if (launches) *launches = b->launches;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_debug(const dg_batch* b, int i, const int16_t** coef, uint64_t* nblocks, const uint8_t** decoded) {
+    if (!b || i < 0 || i >= b->n) return fail(DG_E_INVALID, "bad index");
+    const ItemPlan& it = b->items[i];
+    if (it.status || !it.is_jpeg || it.wave < 0) return fail(DG_E_INVALID, "item has no JPEG intermediates");
+    if ((int)b->waves.size() != 1) return fail(DG_E_INVALID, "intermediates are only kept for single-wave batches");
+    const WavePlan& wv = b->waves[it.wave];
+    if (coef) *coef = (const int16_t*)(b->d_scratch + wv.off_coef) + it.coef_off_blocks * 64;
+    if (nblocks) *nblocks = it.nblocks;
+    const bool transform = b->ctx->has_tfm && !(b->flags & DG_BATCH_DECODE_ONLY);
+    if (decoded) *decoded = transform ? b->d_scratch + wv.off_decoded + it.decoded_off : b->d_persist + b->off_out + it.out_off;
+    return DG_OK;
+}
+
+extern "C" void dg_batch_destroy(dg_batch* b) {
+    if (!b) return;
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (StageEvent& se : b->events) { cudaEventDestroy(se.a); cudaEventDestroy(se.b); }
+    ctx->dev.release(b->blk_persist);
+    ctx->dev.release(b->blk_scratch);
+    ctx->pin.release(b->blk_pin);
+    ctx->pin.release(b->blk_pin_status);
+    delete b;
+}
+
+extern "C" int dg_process(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, uint8_t* const* host_out, dg_result* results) {
+    dg_batch* b = nullptr;
+    int rc = dg_batch_create(ctx, items, n, flags, &b);
+    if (rc) return rc;
+    rc = dg_batch_upload(b);
+    if (!rc) rc = dg_batch_run(b);
+    if (!rc && host_out) rc = dg_batch_download(b, host_out);
+    if (!rc) rc = dg_batch_sync(b);
+    if (!rc && results)
+        for (int i = 0; i < n; ++i) { dg_batch_result(b, i, &results[i]); results[i].device_data = nullptr; }
+    dg_batch_destroy(b);
+    return rc;
+}
+
+extern "C" int dg_copy_to_host(dg_ctx* ctx, void* dst, const void* src, uint64_t nbytes) {
+    if (!ctx || !dst || !src || ctx->device == DG_DEVICE_NONE) return fail(DG_E_INVALID, "NULL argument or planning-only context");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+    CU(cudaStreamSynchronize(ctx->stream));
+    return DG_OK;
+}

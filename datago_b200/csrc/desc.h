@@ -1,0 +1,72 @@
+// Descriptors shared by the host planner and the device kernels.  Plain structs, 8-byte aligned.
+#pragma once
+#include <stdint.h>
+
+namespace dg {
+
+constexpr int kLutBits = 9;  // Huffman fast-lookup width
+
+// One Huffman table (DC or AC) prepared for the device (T.81 Annex C code assignment).
+struct HuffTable {
+    uint16_t lut[1 << kLutBits];  // next 9 bits -> (length << 8) | symbol; 0 = longer code
+    int32_t maxcode[18];          // [l], l = 1..16: largest code of length l, -1 if none; [17] = INT_MAX
+    int32_t valoff[17];           // [l]: index of the first symbol of length l minus its first code
+    uint8_t vals[256];
+};
+
+// Status bits a kernel may set for an image (ORed into status[item]).
+enum : uint32_t {
+    kStTruncated = 1u,   // entropy data ended before all blocks were decoded
+    kStBadCode = 2u,     // a code that is not in the Huffman table
+    kStBadMarker = 4u,   // restart markers missing / out of sequence
+    kStSyncLimit = 8u,   // subsequence synchronisation hit its iteration cap
+    kStCoefRange = 16u,  // coefficient index ran past the end of a block
+};
+
+// One baseline JPEG of a wave.
+struct JpegDesc {
+    uint64_t raw_off;       // entropy-coded segment inside the raw blob (16-byte aligned)
+    uint64_t us_off;        // this image's slice of the unstuffed buffer (16-byte aligned, capacity raw_len + 32)
+    uint64_t block_off;     // first 8x8 block in the coefficient buffer
+    uint64_t plane_off[3];  // byte offset of each component plane (MCU-padded, pitch = plane_pitch)
+    uint64_t out_off;       // byte offset of the decoded image (tightly packed HWC) in the decode target buffer
+    uint32_t raw_len;
+    uint32_t width, height;
+    uint32_t mcux, mcuy;
+    uint32_t ncomp, hs, vs, bpm;  // components, luma sampling factors, blocks per MCU
+    uint32_t qt[3];               // quantisation table pool index per component
+    uint32_t dc_tab[3], ac_tab[3];  // Huffman table pool index per component
+    uint32_t restart;             // MCUs per restart interval, 0 = none
+    uint32_t nseg;                // restart segments expected (1 when restart == 0)
+    uint32_t seg_off;             // first entry of this image in the segment-start array
+    uint32_t nblocks;
+    uint32_t plane_pitch[3];
+    uint32_t plane_rows[3];
+    uint32_t item;                // index in the batch (status word, result)
+    uint32_t pad;
+};
+
+// One 1-D convolution pass over a region of one image (u8, 1 or 3 interleaved channels).
+// horizontal: dst(x, y) = clip8((round + sum_i k[i][t0 + x] * src(start[t0 + x] - src_origin + i, y)) >> precision)
+// vertical:   dst(x, y) = clip8((round + sum_i k[i][t0 + y] * src(x, start[t0 + y] - src_origin + i)) >> precision)
+struct ConvPass {
+    const uint8_t* src;  // first needed row (horizontal) / first needed column (vertical) already applied
+    uint8_t* dst;
+    uint32_t src_pitch, dst_pitch;  // bytes
+    uint32_t out_w, out_h;          // produced region in pixels
+    uint32_t channels;
+    int32_t src_origin;             // coordinate, along the filtered axis, of element 0 of `src`
+    uint32_t t0;                    // first table entry used
+    uint32_t tab_n, window, precision;
+    uint64_t tab_off;               // word offset in the table pool: start[tab_n] | size[tab_n] | int16 k[window][tab_n]
+    uint32_t tile_first;            // first CTA tile of this pass in the launch (prefix sum)
+    uint32_t tiles_x;               // tiles per row of tiles
+};
+
+struct CopyJob {  // identity payloads / pitch removal
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t src_pitch, row_bytes, rows, tile_first;
+};
+
+}  // namespace dg

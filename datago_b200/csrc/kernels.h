@@ -1,0 +1,61 @@
+// Launch interface between the batch scheduler (api.cu) and the sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "desc.h"
+
+namespace dg {
+
+// Maps a flat work index (block, tile, segment) to its owner (image, pass): first[owner] <= idx < first[owner + 1].
+// coarse[idx >> shift] is the owner of work item (idx >> shift) << shift, so the search is a short forward walk.
+struct OwnerMap {
+    const uint32_t* first;   // n + 1 entries
+    const uint32_t* coarse;
+    uint32_t n, shift, total;
+};
+
+struct JpegWave {
+    const JpegDesc* descs;   // device, n images
+    uint32_t n;
+    const uint8_t* raw;      // compressed blob
+    uint8_t* us;             // unstuffed streams
+    uint32_t* us_len;        // [n] bytes of each unstuffed stream
+    uint32_t* seg_start;     // restart-segment starts (bytes into the image's unstuffed stream)
+    uint32_t* seg_found;     // [n] segments actually present
+    int16_t* coef;           // [blocks][64], scan order, natural order inside a block
+    uint8_t* planes;         // component planes after the IDCT
+    uint8_t* out;            // decoded images
+    uint32_t* status;        // [items of the batch]
+    const HuffTable* huff;   // table pool
+    const uint16_t* qt;      // quantisation pool, 64 entries each, natural order
+    // speculative (no restart marker) images and restart-interval images of this wave
+    const uint32_t* spec_list; uint32_t n_spec;
+    OwnerMap restart_segs;   // owner = index into restart_list
+    const uint32_t* restart_list;
+    OwnerMap blocks;         // owner = image
+    OwnerMap color_tiles;    // owner = image
+};
+
+void launch_unstuff(const JpegWave& w, cudaStream_t s);
+void launch_huffman(const JpegWave& w, cudaStream_t s, uint32_t* launches);
+void launch_idct(const JpegWave& w, cudaStream_t s);
+void launch_color(const JpegWave& w, cudaStream_t s);
+
+// tiles of the colour kernel for a w x h image
+constexpr uint32_t kColorTileW = 128, kColorTileH = 8;
+inline uint32_t color_tiles(uint32_t w, uint32_t h) { return ((w + kColorTileW - 1) / kColorTileW) * ((h + kColorTileH - 1) / kColorTileH); }
+
+// ---- resize ---------------------------------------------------------------------------------------------------------
+constexpr uint32_t kConvTileW = 64, kConvTileH = 4;     // horizontal pass: output pixels per CTA
+constexpr uint32_t kVTileBytes = 256, kVTileH = 4;      // vertical pass: output bytes x rows per CTA
+inline uint32_t conv_h_tiles_x(uint32_t out_w) { return (out_w + kConvTileW - 1) / kConvTileW; }
+inline uint32_t conv_h_tiles(uint32_t out_w, uint32_t out_h) { return conv_h_tiles_x(out_w) * ((out_h + kConvTileH - 1) / kConvTileH); }
+inline uint32_t conv_v_tiles_x(uint32_t row_bytes) { return (row_bytes + kVTileBytes - 1) / kVTileBytes; }
+inline uint32_t conv_v_tiles(uint32_t row_bytes, uint32_t out_h) { return conv_v_tiles_x(row_bytes) * ((out_h + kVTileH - 1) / kVTileH); }
+constexpr uint32_t kCopyTileBytes = 4096;
+
+void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
+void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
+void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s);
+
+}  // namespace dg

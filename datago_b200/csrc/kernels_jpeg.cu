@@ -1,0 +1,548 @@
+// Baseline JPEG on sm_100a: byte unstuffing, Huffman entropy decode, dequantise + 8x8 integer IDCT,
+// chroma upsampling + YCbCr->RGB.  Replaces the zune-jpeg decode datago reaches through
+// image::load_from_memory (src/worker_wds.rs:45) / ImageReader::decode (src/worker_files.rs:14-16).
+//
+// All of it is integer / byte work bound by HBM traffic or by serial bit-parsing latency; no tensor cores.
+#include <cstdint>
+
+#include "kernels.h"
+
+namespace dg {
+
+// ---------------------------------------------------------------------------------------------------------------
+// helpers
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t owner_of(const OwnerMap& m, uint32_t idx) {
+    uint32_t o = __ldg(m.coarse + (idx >> m.shift));
+    while (o + 1 < m.n && __ldg(m.first + o + 1) <= idx) ++o;
+    return o;
+}
+
+__device__ const uint8_t kNatural[64] = {0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,
+                                         12, 19, 26, 33, 40, 48, 41, 34, 27, 20, 13, 6,  7,  14, 21, 28,
+                                         35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23, 30, 37, 44, 51,
+                                         58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
+
+// ---------------------------------------------------------------------------------------------------------------
+// K0  unstuff: one CTA per image walks the entropy-coded segment in 4 KB steps, drops stuffed zeros (FF 00 -> FF),
+//     fill bytes and RSTn markers, records where each restart segment starts in the compacted stream and stops at
+//     the first other marker (EOI).  The compacted stream lets the entropy decoder load aligned 32-bit words.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kUnstuffThreads = 256;
+
+__global__ void __launch_bounds__(kUnstuffThreads) k_unstuff(JpegWave w) {
+    const JpegDesc& d = w.descs[blockIdx.x];
+    const uint8_t* in = w.raw + d.raw_off;
+    uint8_t* out = w.us + d.us_off;
+    uint32_t* seg = w.seg_start + d.seg_off;
+    const uint32_t len = d.raw_len;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    __shared__ uint32_t s_end;
+    __shared__ uint32_t s_warp[kUnstuffThreads / 32];
+    uint32_t kept = 0, nrst = 0;  // running totals, identical in every thread
+    if (tid == 0) seg[0] = 0;
+
+    for (uint32_t base = 0; base < len; base += kUnstuffThreads * 16) {
+        if (tid == 0) s_end = 0xFFFFFFFFu;
+        __syncthreads();
+        const uint32_t i0 = base + tid * 16;
+        uint8_t b[18];
+        {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (i0 < len) v = __ldg(reinterpret_cast<const uint4*>(in + i0));  // blob slices are padded to 16 bytes with zeros
+            const uint32_t ww[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j) b[j + 1] = (uint8_t)(ww[j >> 2] >> (8 * (j & 3)));
+            b[0] = (i0 > 0 && i0 <= len) ? __ldg(in + i0 - 1) : 0;
+            b[17] = (i0 + 16 < len) ? __ldg(in + i0 + 16) : 0;
+        }
+        uint32_t keep = 0, rst = 0, term = 0xFFFFFFFFu;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t idx = i0 + j;
+            if (idx >= len) break;
+            const uint8_t cur = b[j + 1], pv = b[j], nx = b[j + 2];
+            bool k = true;
+            if (cur == 0xFF) {
+                if (nx == 0x00) k = true;                      // data byte FF (its stuffed zero is dropped below)
+                else if (nx == 0xFF) k = false;                // fill byte
+                else if (nx >= 0xD0 && nx <= 0xD7) { k = false; rst |= 1u << j; }
+                else { k = false; if (term == 0xFFFFFFFFu) term = idx; }  // any other marker ends the scan
+            } else if (pv == 0xFF && (cur == 0x00 || (cur >= 0xD0 && cur <= 0xD7))) {
+                k = false;
+            }
+            if (k) keep |= 1u << j;
+        }
+        if (term != 0xFFFFFFFFu) atomicMin(&s_end, term);
+        __syncthreads();
+        const uint32_t end = s_end;
+        if (end != 0xFFFFFFFFu) {  // nothing at or after the terminating marker survives
+            if (i0 >= end) { keep = 0; rst = 0; }
+            else if (end - i0 < 16) { const uint32_t m = (1u << (end - i0)) - 1; keep &= m; rst &= m; }
+        }
+        // exclusive scan of (restart count << 16 | kept count) over the CTA
+        const uint32_t mine = ((uint32_t)__popc(rst) << 16) | (uint32_t)__popc(keep);
+        uint32_t inc = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o); if (lane >= o) inc += t; }
+        if (lane == 31) s_warp[warp] = inc;
+        __syncthreads();
+        uint32_t wpre = 0, tot = 0;
+#pragma unroll
+        for (int i = 0; i < kUnstuffThreads / 32; ++i) { const uint32_t t = s_warp[i]; if (i < warp) wpre += t; tot += t; }
+        const uint32_t excl = wpre + inc - mine;
+        uint32_t pos = kept + (excl & 0xFFFFu), r = nrst + (excl >> 16);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (keep & (1u << j)) out[pos++] = b[j + 1];
+            if (rst & (1u << j)) { ++r; if (r < d.nseg) seg[r] = pos; }
+        }
+        kept += tot & 0xFFFFu;
+        nrst += tot >> 16;
+        if (end != 0xFFFFFFFFu) break;
+        __syncthreads();  // s_end and s_warp are rewritten by the next step
+    }
+    if (tid < 16) out[kept + tid] = 0;  // the bit reader may look a few bytes past the end
+    if (tid == 0) {
+        w.us_len[blockIdx.x] = kept;
+        w.seg_found[blockIdx.x] = nrst + 1;
+    }
+}
+
+void launch_unstuff(const JpegWave& w, cudaStream_t s) {
+    if (w.n) k_unstuff<<<w.n, kUnstuffThreads, 0, s>>>(w);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// K1  Huffman entropy decode.
+//
+// The decoder state between two symbols is (bit position, slot), slot = 64 * block index + zig-zag index: every
+// block owns exactly 64 slots, an AC run or an end-of-block only advances the slot.  Knowing the slot modulo the
+// MCU size gives the component (hence the tables) and whether the next symbol is a DC or an AC code.
+//
+//  * images with restart intervals: one thread per restart segment; the segment's first MCU and the zero DC
+//    predictors are known, so coefficients are written in a single pass.
+//  * images without: the stream is cut into subsequences of kSubseqBits bits, one thread each.  Thread j decodes
+//    from a guessed entry state, then re-decodes from the exit state of thread j-1 until entry(j) == exit(j-1)
+//    for every j (Huffman streams re-synchronise after a few symbols, so this takes 2-3 rounds; the loop is
+//    bounded by the thread count because thread j is final after round j).  A prefix sum over the slots and DC
+//    differences of the subsequences then gives every thread its output position and DC predictors, and a last
+//    pass writes the coefficients.  One CTA walks one image in chunks of kSpecThreads subsequences, carrying
+//    the exact state across chunks, so no CTA ever waits on another.
+// ---------------------------------------------------------------------------------------------------------------
+struct BitReader {
+    const uint32_t* words;
+    uint32_t nwords;
+    uint64_t buf;
+    int avail;
+    uint32_t wi;
+    __device__ __forceinline__ uint32_t load(uint32_t i) const { return i < nwords ? __byte_perm(__ldg(words + i), 0, 0x0123) : 0u; }
+    __device__ __forceinline__ void seek(uint32_t bitpos) {
+        wi = bitpos >> 5;
+        const int sh = bitpos & 31;
+        buf = (((uint64_t)load(wi) << 32) | load(wi + 1)) << sh;
+        avail = 64 - sh;
+        wi += 2;
+    }
+    __device__ __forceinline__ void refill() {
+        if (avail <= 32) { buf |= (uint64_t)load(wi++) << (32 - avail); avail += 32; }
+    }
+    __device__ __forceinline__ uint32_t peek() const { return (uint32_t)(buf >> 32); }
+    __device__ __forceinline__ void skip(uint32_t n) { buf <<= n; avail -= (int)n; }
+};
+
+struct HuffCtx {
+    const HuffTable* dc0; const HuffTable* dc1; const HuffTable* dc2;
+    const HuffTable* ac0; const HuffTable* ac1; const HuffTable* ac2;
+    uint32_t luma_blocks;  // blocks of component 0 per MCU
+    uint32_t mcu_slots;    // 64 * blocks per MCU
+};
+
+// Decodes symbols that start in [p, end_bit) while fewer than max_slots slots have been consumed.
+// dc0..2: sums of DC differences (WRITE == false) or running DC predictors (WRITE == true).
+template <bool WRITE>
+__device__ __forceinline__ void decode_span(BitReader& br, uint32_t& p, const uint32_t end_bit, const uint32_t total_bits,
+                                            uint32_t& slotmod, uint32_t& nslots, const uint32_t max_slots, int32_t& dc0,
+                                            int32_t& dc1, int32_t& dc2, const HuffCtx& hc, int16_t* __restrict__ coef,
+                                            const uint32_t slot_abs, uint32_t& err) {
+    while (p < end_bit && nslots < max_slots) {
+        br.refill();
+        const uint32_t top = br.peek();
+        const uint32_t z = slotmod & 63u, c = slotmod >> 6;
+        const int comp = c < hc.luma_blocks ? 0 : (int)(c - hc.luma_blocks) + 1;
+        const HuffTable* t = z == 0 ? (comp == 0 ? hc.dc0 : comp == 1 ? hc.dc1 : hc.dc2)
+                                    : (comp == 0 ? hc.ac0 : comp == 1 ? hc.ac1 : hc.ac2);
+        const uint32_t e = t->lut[top >> (32 - kLutBits)];
+        uint32_t len, sym;
+        if (e) {
+            len = e >> 8; sym = e & 255u;
+        } else {
+            len = kLutBits + 1;
+            while (len <= 16 && (int32_t)(top >> (32 - len)) > t->maxcode[len]) ++len;
+            if (len > 16) { len = 16; sym = 0; if (WRITE) err |= kStBadCode; }
+            else sym = t->vals[(int32_t)(top >> (32 - len)) + t->valoff[len]];
+        }
+        const uint32_t s = sym & 15u, used = len + s;
+        if (p + used > total_bits) { p = total_bits; break; }  // the stream ends inside this symbol
+        int32_t v = 0;
+        if (s) {
+            const uint32_t raw = (top << len) >> (32 - s);
+            v = raw < (1u << (s - 1)) ? (int32_t)raw - (int32_t)(1u << s) + 1 : (int32_t)raw;
+        }
+        uint32_t adv;
+        if (z == 0) {
+            int32_t now;
+            if (comp == 0) now = (dc0 += v); else if (comp == 1) now = (dc1 += v); else now = (dc2 += v);
+            if (WRITE) coef[(size_t)(slot_abs + nslots)] = (int16_t)now;  // slot of a DC code is 64 * block
+            adv = 1;
+        } else {
+            const uint32_t r = sym >> 4;
+            if (s == 0) {
+                adv = (r == 15u && z + 16u <= 64u) ? 16u : 64u - z;  // ZRL, or end of block
+            } else {
+                const uint32_t zz = z + r;
+                if (zz > 63u) { adv = 64u - z; if (WRITE) err |= kStCoefRange; }
+                else {
+                    if (WRITE) coef[(size_t)(slot_abs + nslots - z) + kNatural[zz]] = (int16_t)v;
+                    adv = r + 1u;
+                }
+            }
+        }
+        br.skip(used);
+        p += used;
+        nslots += adv;
+        slotmod += adv;
+        if (slotmod >= hc.mcu_slots) slotmod -= hc.mcu_slots;
+    }
+}
+
+__device__ __forceinline__ void load_ctx(HuffCtx& hc, const JpegDesc& d, const HuffTable* pool) {
+    hc.dc0 = pool + d.dc_tab[0]; hc.ac0 = pool + d.ac_tab[0];
+    hc.dc1 = pool + d.dc_tab[1]; hc.ac1 = pool + d.ac_tab[1];
+    hc.dc2 = pool + d.dc_tab[2]; hc.ac2 = pool + d.ac_tab[2];
+    hc.luma_blocks = d.hs * d.vs;
+    hc.mcu_slots = d.bpm * 64u;
+}
+
+// ---- restart-interval images: one thread per segment -----------------------------------------------------------
+constexpr int kRestartThreads = 128;
+
+__global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
+    const uint32_t g = blockIdx.x * kRestartThreads + threadIdx.x;
+    if (g >= w.restart_segs.total) return;
+    const uint32_t r = owner_of(w.restart_segs, g);
+    const uint32_t img = w.restart_list[r];
+    const uint32_t k = g - w.restart_segs.first[r];
+    const JpegDesc& d = w.descs[img];
+    const uint32_t found = w.seg_found[img];
+    if (k == 0 && found != d.nseg) atomicOr(w.status + d.item, kStBadMarker);
+    if (k >= found) return;
+    const uint32_t* seg = w.seg_start + d.seg_off;
+    const uint32_t us_len = w.us_len[img];
+    const uint32_t b0 = seg[k], b1 = (k + 1 < found && k + 1 < d.nseg) ? seg[k + 1] : us_len;
+    const uint32_t mcus = d.mcux * d.mcuy;
+    const uint32_t m0 = k * d.restart, m1 = min(m0 + d.restart, mcus);
+    HuffCtx hc;
+    load_ctx(hc, d, w.huff);
+    BitReader br;
+    br.words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
+    br.nwords = (us_len + 3) / 4 + 2;
+    uint32_t p = b0 * 8u, slotmod = 0, nslots = 0, err = 0;
+    int32_t dc0 = 0, dc1 = 0, dc2 = 0;
+    br.seek(p);
+    const uint32_t want = (m1 - m0) * hc.mcu_slots;
+    decode_span<true>(br, p, b1 * 8u, b1 * 8u, slotmod, nslots, want, dc0, dc1, dc2, hc, w.coef + d.block_off * 64,
+                      m0 * hc.mcu_slots, err);
+    if (nslots < want) err |= kStTruncated;
+    if (err) atomicOr(w.status + d.item, err);
+}
+
+// ---- images without restart markers: speculative subsequences, one CTA per image ---------------------------------
+constexpr int kSpecThreads = 512;
+constexpr uint32_t kSubseqBits = 1024;
+
+struct Scan4 { uint32_t n; int32_t a, b, c; };
+
+__global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
+    const uint32_t img = w.spec_list[blockIdx.x];
+    const JpegDesc& d = w.descs[img];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    __shared__ HuffTable s_tab[6];
+    __shared__ uint32_t s_exit_p[kSpecThreads];
+    __shared__ uint32_t s_exit_sm[kSpecThreads];
+    __shared__ Scan4 s_warp[kSpecThreads / 32];
+    __shared__ uint32_t s_carry_p, s_carry_slot;
+    __shared__ int32_t s_carry_dc[3];
+
+    // stage the image's Huffman tables in shared memory (word copies)
+    {
+        const uint32_t ids[6] = {d.dc_tab[0], d.dc_tab[1], d.dc_tab[2], d.ac_tab[0], d.ac_tab[1], d.ac_tab[2]};
+        constexpr int kWords = sizeof(HuffTable) / 4;
+        for (int t = 0; t < 6; ++t) {
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(w.huff + ids[t]);
+            uint32_t* dst = reinterpret_cast<uint32_t*>(&s_tab[t]);
+            for (int i = tid; i < kWords; i += kSpecThreads) dst[i] = __ldg(src + i);
+        }
+        if (tid == 0) { s_carry_p = 0; s_carry_slot = 0; s_carry_dc[0] = s_carry_dc[1] = s_carry_dc[2] = 0; }
+    }
+    __syncthreads();
+    HuffCtx hc;
+    hc.dc0 = &s_tab[0]; hc.dc1 = &s_tab[1]; hc.dc2 = &s_tab[2];
+    hc.ac0 = &s_tab[3]; hc.ac1 = &s_tab[4]; hc.ac2 = &s_tab[5];
+    hc.luma_blocks = d.hs * d.vs;
+    hc.mcu_slots = d.bpm * 64u;
+
+    const uint32_t us_len = w.us_len[img];
+    const uint32_t total_bits = us_len * 8u;
+    const uint32_t total_slots = d.nblocks * 64u;
+    const uint32_t nsub = (total_bits + kSubseqBits - 1) / kSubseqBits;
+    BitReader br;
+    br.words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
+    br.nwords = (us_len + 3) / 4 + 2;
+    int16_t* coef = w.coef + d.block_off * 64;
+    uint32_t err = 0;
+
+    for (uint32_t chunk = 0; chunk < nsub; chunk += kSpecThreads) {
+        const uint32_t j = chunk + tid;
+        const bool active = j < nsub;
+        const uint32_t end_bit = min((j + 1) * kSubseqBits, total_bits);
+        // entry state: exact for the first subsequence of the chunk, a guess (AC code of the first block) elsewhere
+        uint32_t entry_p = tid == 0 ? s_carry_p : j * kSubseqBits;
+        uint32_t entry_sm = tid == 0 ? s_carry_slot % hc.mcu_slots : 1u;
+        uint32_t n = 0;
+        int32_t a = 0, b = 0, c = 0;
+        bool redo = active;
+        for (int round = 0; round <= kSpecThreads + 1; ++round) {
+            if (redo) {
+                uint32_t p = entry_p, sm = entry_sm, dummy = 0;
+                n = 0; a = 0; b = 0; c = 0;
+                br.seek(p);
+                decode_span<false>(br, p, end_bit, total_bits, sm, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, dummy);
+                s_exit_p[tid] = p;
+                s_exit_sm[tid] = sm;
+            }
+            __syncthreads();
+            redo = false;
+            if (active && tid > 0) {
+                const uint32_t pp = s_exit_p[tid - 1], ps = s_exit_sm[tid - 1];
+                if (pp != entry_p || ps != entry_sm) { entry_p = pp; entry_sm = ps; redo = true; }
+            }
+            if (!__syncthreads_or(redo)) break;
+            if (round == kSpecThreads + 1) err |= kStSyncLimit;
+        }
+        // exclusive prefix over (slots, DC sums) of the chunk
+        Scan4 inc{active ? n : 0u, active ? a : 0, active ? b : 0, active ? c : 0};
+        const Scan4 mine = inc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t tn = __shfl_up_sync(0xFFFFFFFFu, inc.n, o);
+            const int32_t ta = __shfl_up_sync(0xFFFFFFFFu, inc.a, o), tb = __shfl_up_sync(0xFFFFFFFFu, inc.b, o),
+                          tc = __shfl_up_sync(0xFFFFFFFFu, inc.c, o);
+            if (lane >= o) { inc.n += tn; inc.a += ta; inc.b += tb; inc.c += tc; }
+        }
+        if (lane == 31) s_warp[warp] = inc;
+        __syncthreads();
+        Scan4 pre{0, 0, 0, 0}, tot{0, 0, 0, 0};
+        for (int i = 0; i < kSpecThreads / 32; ++i) {
+            const Scan4 t = s_warp[i];
+            if (i < warp) { pre.n += t.n; pre.a += t.a; pre.b += t.b; pre.c += t.c; }
+            tot.n += t.n; tot.a += t.a; tot.b += t.b; tot.c += t.c;
+        }
+        const uint32_t slot0 = s_carry_slot + pre.n + inc.n - mine.n;
+        int32_t p0 = s_carry_dc[0] + pre.a + inc.a - mine.a, p1 = s_carry_dc[1] + pre.b + inc.b - mine.b,
+                p2 = s_carry_dc[2] + pre.c + inc.c - mine.c;
+        // write pass
+        if (active && slot0 < total_slots) {
+            uint32_t p = entry_p, sm = entry_sm, nn = 0;
+            br.seek(p);
+            decode_span<true>(br, p, end_bit, total_bits, sm, nn, total_slots - slot0, p0, p1, p2, hc, coef, slot0, err);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t last = min((uint32_t)kSpecThreads, nsub - chunk) - 1;
+            s_carry_p = s_exit_p[last];
+            s_carry_slot += tot.n;
+            s_carry_dc[0] += tot.a; s_carry_dc[1] += tot.b; s_carry_dc[2] += tot.c;
+        }
+        __syncthreads();
+    }
+    if (tid == 0 && s_carry_slot < total_slots) err |= kStTruncated;
+    if (err) atomicOr(w.status + d.item, err);
+}
+
+void launch_huffman(const JpegWave& w, cudaStream_t s, uint32_t* launches) {
+    if (w.restart_segs.total) {
+        k_huff_restart<<<(w.restart_segs.total + kRestartThreads - 1) / kRestartThreads, kRestartThreads, 0, s>>>(w);
+        ++*launches;
+    }
+    if (w.n_spec) {
+        k_huff_spec<<<w.n_spec, kSpecThreads, 0, s>>>(w);
+        ++*launches;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// K2  dequantise + 8x8 inverse DCT (the 13-bit fixed-point "islow" factorisation), +128, clamp.
+//     One thread per block; coefficients are read as eight 16-byte words, rows are written as 8-byte words into the
+//     component plane.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void idct_1d(int32_t (&x)[8], int32_t (&o)[8]) {
+    constexpr int32_t F_0_298 = 2446, F_0_390 = 3196, F_0_541 = 4433, F_0_765 = 6270, F_0_899 = 7373, F_1_175 = 9633,
+                      F_1_501 = 12299, F_1_847 = 15137, F_1_961 = 16069, F_2_053 = 16819, F_2_562 = 20995, F_3_072 = 25172;
+    int32_t z2 = x[2], z3 = x[6];
+    int32_t z1 = (z2 + z3) * F_0_541;
+    int32_t t2 = z1 - z3 * F_1_847, t3 = z1 + z2 * F_0_765;
+    int32_t t0 = (int32_t)((uint32_t)(x[0] + x[4]) << 13), t1 = (int32_t)((uint32_t)(x[0] - x[4]) << 13);
+    const int32_t t10 = t0 + t3, t13 = t0 - t3, t11 = t1 + t2, t12 = t1 - t2;
+    t0 = x[7]; t1 = x[5]; t2 = x[3]; t3 = x[1];
+    z1 = t0 + t3; z2 = t1 + t2; z3 = t0 + t2;
+    int32_t z4 = t1 + t3;
+    const int32_t z5 = (z3 + z4) * F_1_175;
+    t0 *= F_0_298; t1 *= F_2_053; t2 *= F_3_072; t3 *= F_1_501;
+    z1 *= -F_0_899; z2 *= -F_2_562; z3 *= -F_1_961; z4 *= -F_0_390;
+    z3 += z5; z4 += z5;
+    t0 += z1 + z3; t1 += z2 + z4; t2 += z2 + z3; t3 += z1 + z4;
+    o[0] = t10 + t3; o[7] = t10 - t3; o[1] = t11 + t2; o[6] = t11 - t2;
+    o[2] = t12 + t1; o[5] = t12 - t1; o[3] = t13 + t0; o[4] = t13 - t0;
+}
+
+constexpr int kIdctThreads = 128;
+
+__global__ void __launch_bounds__(kIdctThreads) k_idct(JpegWave w) {
+    const uint32_t g = blockIdx.x * kIdctThreads + threadIdx.x;
+    if (g >= w.blocks.total) return;
+    const uint32_t img = owner_of(w.blocks, g);
+    const JpegDesc& d = w.descs[img];
+    const uint32_t blk = g - (uint32_t)d.block_off;
+    const uint32_t mcu = blk / d.bpm, k = blk - mcu * d.bpm;
+    const uint32_t my = mcu / d.mcux, mx = mcu - my * d.mcux;
+    const uint32_t luma = d.hs * d.vs;
+    uint32_t comp, bx, by;
+    if (k < luma) { comp = 0; bx = mx * d.hs + k % d.hs; by = my * d.vs + k / d.hs; }
+    else { comp = k - luma + 1; bx = mx; by = my; }
+    const uint4* src = reinterpret_cast<const uint4*>(w.coef + (size_t)g * 64);
+    const uint4* qq = reinterpret_cast<const uint4*>(w.qt + (size_t)d.qt[comp] * 64);
+
+    int32_t ws[8][8];  // [row][col]
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        const uint4 cv = src[r];
+        const uint4 qv = __ldg(qq + r);
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, qw[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            ws[r][2 * i] = (int32_t)(int16_t)(cw[i] & 0xFFFFu) * (int32_t)(qw[i] & 0xFFFFu);
+            ws[r][2 * i + 1] = (int32_t)(int16_t)(cw[i] >> 16) * (int32_t)(qw[i] >> 16);
+        }
+    }
+    // columns
+#pragma unroll
+    for (int cidx = 0; cidx < 8; ++cidx) {
+        int32_t x[8], o[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) x[r] = ws[r][cidx];
+        idct_1d(x, o);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) ws[r][cidx] = (o[r] + (1 << 10)) >> 11;
+    }
+    // rows
+    uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        int32_t o[8];
+        idct_1d(ws[r], o);
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            int32_t v = ((o[i] + (1 << 17)) >> 18) + 128;
+            v = min(max(v, 0), 255);
+            if (i < 4) lo |= (uint32_t)v << (8 * i); else hi |= (uint32_t)v << (8 * (i - 4));
+        }
+        *reinterpret_cast<uint2*>(dst + (size_t)r * d.plane_pitch[comp]) = make_uint2(lo, hi);
+    }
+}
+
+void launch_idct(const JpegWave& w, cudaStream_t s) {
+    if (w.blocks.total) k_idct<<<(w.blocks.total + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// K3  chroma upsampling (triangle filter with replicated edges; plain replication when the chroma plane is at most
+//     two samples wide) + YCbCr -> RGB in 16-bit fixed point, interleaved RGB8 out.  Grayscale: rows are copied.
+//     One thread per 2x2 output quad.
+// ---------------------------------------------------------------------------------------------------------------
+struct ChromaPlane {
+    const uint8_t* p;
+    uint32_t pitch;
+    int dw, dh, hs, vs;
+    __device__ __forceinline__ int px(int x, int y) const { return __ldg(p + (size_t)y * pitch + x); }
+    __device__ __forceinline__ int colsum(int cx, int y) const {
+        const int cy = y >> 1;
+        int far = (y & 1) ? cy + 1 : cy - 1;
+        far = min(max(far, 0), dh - 1);
+        return 3 * px(cx, cy) + px(cx, far);
+    }
+    __device__ __forceinline__ int at(int x, int y) const {
+        if (hs == 1 && vs == 1) return px(x, y);
+        if (hs == 2 && dw <= 2) return px(x >> 1, vs == 2 ? y >> 1 : y);
+        if (hs == 1) return (colsum(x, y) + ((y & 1) ? 2 : 1)) >> 2;
+        const int cx = x >> 1;
+        if (vs == 1) {
+            const int t = px(cx, y);
+            if (x & 1) return cx == dw - 1 ? t : (3 * t + px(cx + 1, y) + 2) >> 2;
+            return cx == 0 ? t : (3 * t + px(cx - 1, y) + 1) >> 2;
+        }
+        const int t = colsum(cx, y);
+        if (x & 1) return cx == dw - 1 ? (t * 4 + 7) >> 4 : (t * 3 + colsum(cx + 1, y) + 7) >> 4;
+        return cx == 0 ? (t * 4 + 8) >> 4 : (t * 3 + colsum(cx - 1, y) + 8) >> 4;
+    }
+};
+
+__device__ __forceinline__ uint8_t clamp_u8(int v) { return (uint8_t)min(max(v, 0), 255); }
+
+constexpr int kColorThreads = (kColorTileW / 2) * (kColorTileH / 2);
+
+__global__ void __launch_bounds__(kColorThreads) k_color(JpegWave w) {
+    const uint32_t img = owner_of(w.color_tiles, blockIdx.x);
+    const JpegDesc& d = w.descs[img];
+    const uint32_t tile = blockIdx.x - w.color_tiles.first[img];
+    const uint32_t tiles_x = (d.width + kColorTileW - 1) / kColorTileW;
+    const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
+    const int x0 = (int)(tx * kColorTileW + (threadIdx.x % (kColorTileW / 2)) * 2);
+    const int y0 = (int)(ty * kColorTileH + (threadIdx.x / (kColorTileW / 2)) * 2);
+    const int W = (int)d.width, H = (int)d.height;
+    if (x0 >= W || y0 >= H) return;
+    const uint8_t* yp = w.planes + d.plane_off[0];
+    const uint32_t ypitch = d.plane_pitch[0];
+    if (d.ncomp == 1) {
+        uint8_t* o = w.out + d.out_off;
+        for (int dy = 0; dy < 2 && y0 + dy < H; ++dy)
+            for (int dx = 0; dx < 2 && x0 + dx < W; ++dx)
+                o[(size_t)(y0 + dy) * W + x0 + dx] = __ldg(yp + (size_t)(y0 + dy) * ypitch + x0 + dx);
+        return;
+    }
+    const int dw = (W * 1 + (int)d.hs - 1) / (int)d.hs, dh = (H + (int)d.vs - 1) / (int)d.vs;
+    const ChromaPlane cbp{w.planes + d.plane_off[1], d.plane_pitch[1], dw, dh, (int)d.hs, (int)d.vs};
+    const ChromaPlane crp{w.planes + d.plane_off[2], d.plane_pitch[2], dw, dh, (int)d.hs, (int)d.vs};
+    uint8_t* o = w.out + d.out_off;
+    for (int dy = 0; dy < 2 && y0 + dy < H; ++dy) {
+        const int y = y0 + dy;
+        for (int dx = 0; dx < 2 && x0 + dx < W; ++dx) {
+            const int x = x0 + dx;
+            const int Y = __ldg(yp + (size_t)y * ypitch + x);
+            const int cb = cbp.at(x, y) - 128, cr = crp.at(x, y) - 128;
+            uint8_t* px = o + ((size_t)y * W + x) * 3;
+            px[0] = clamp_u8(Y + ((91881 * cr + 32768) >> 16));
+            px[1] = clamp_u8(Y + ((-22554 * cb - 46802 * cr + 32768) >> 16));
+            px[2] = clamp_u8(Y + ((116130 * cb + 32768) >> 16));
+        }
+    }
+}
+
+void launch_color(const JpegWave& w, cudaStream_t s) {
+    if (w.color_tiles.total) k_color<<<w.color_tiles.total, kColorThreads, 0, s>>>(w);
+}
+
+}  // namespace dg

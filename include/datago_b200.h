@@ -1,0 +1,180 @@
+/*
+ * datago_b200 -- C ABI of the B200 image path that replaces datago's per-sample
+ * "decode -> bucket -> resize -> crop" routine.
+ *
+ * datago (Rust) has no FFI seam for this path: the work happens in ordinary Rust calls into the
+ * `image` and `fast_image_resize` crates.  This header cuts the seam at those calls; each entry point
+ * names the datago source line(s) it stands in for (paths relative to the datago tree).
+ *
+ * Conventions
+ *   - plain C, POD structs, no exceptions; every function that can fail returns a dg_status (0 = ok)
+ *     and leaves a message readable with dg_last_error() on the calling thread;
+ *   - a dg_ctx is bound to one CUDA device and one stream; calls on one ctx are serialised by an
+ *     internal lock, so the tokio worker threads of src/worker_files.rs:83-121 may share it;
+ *   - the CUDA path is the only path: there is no CPU fallback.  dg_ctx_create fails when no
+ *     device is usable.
+ */
+#ifndef DATAGO_B200_H
+#define DATAGO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define DG_API __attribute__((visibility("default")))
+#else
+#define DG_API
+#endif
+
+typedef enum dg_status {
+    DG_OK = 0,
+    DG_E_INVALID = 1,      /* bad argument */
+    DG_E_CUDA = 2,         /* a CUDA runtime call failed; see dg_last_error */
+    DG_E_TRUNCATED = 3,    /* JPEG ends early (headers or entropy-coded data) */
+    DG_E_BAD_MARKER = 4,   /* not a JPEG / marker structure broken */
+    DG_E_UNSUPPORTED = 5,  /* progressive, arithmetic, 12-bit, CMYK, unsupported sampling */
+    DG_E_BAD_TABLE = 6,    /* Huffman / quantisation table missing or malformed */
+    DG_E_BAD_CODE = 7,     /* entropy decoding met a code that is not in the table */
+    DG_E_UNKNOWN_KEY = 8,  /* forced aspect-ratio key is not a bucket (datago panics: image_processing.rs:335) */
+    DG_E_NO_TRANSFORM = 9, /* a bucket query on a ctx created without crop_and_resize */
+    DG_E_SYNC_LIMIT = 10,  /* entropy decoder did not converge within its iteration cap */
+    DG_E_TOO_LARGE = 11    /* input exceeds a stated size limit */
+} dg_status;
+
+/* image_config of the client JSON: ImageTransformConfig, src/image_processing.rs:43-70 (the fields on this path). */
+typedef struct dg_image_config {
+    int32_t crop_and_resize;
+    uint32_t default_image_size;
+    uint32_t downsampling_ratio;
+    double min_aspect_ratio;
+    double max_aspect_ratio;
+} dg_image_config;
+
+/* Geometry of crop_and_resize for one image: src/image_processing.rs:259-310. */
+typedef struct dg_plan {
+    uint32_t src_w, src_h, channels; /* decoded size; 3 = RGB8, 1 = L8 */
+    uint32_t target_w, target_h;     /* bucket size = output size */
+    uint32_t new_w, new_h;           /* size after the first (whole-image) resize */
+    double crop_left, crop_top;      /* CropBox::fit_src_into_dst_size(new_w, new_h, target_w, target_h, None) */
+    double crop_w, crop_h;
+    int32_t identity;                /* 1: source already has the bucket size and is returned unchanged (:266-267) */
+    char key[16];                    /* bucket key, format!("{:.3}", w / h) */
+} dg_plan;
+
+typedef struct dg_jpeg_info {
+    uint32_t width, height, channels; /* channels of the decoded image: 3 or 1 */
+    uint32_t hsamp, vsamp;            /* luma sampling factors (2,2 = 4:2:0; 1,1 = 4:4:4) */
+    uint32_t mcux, mcuy, restart_interval;
+    uint64_t scan_offset, scan_len;   /* entropy-coded segment within the file */
+} dg_jpeg_info;
+
+/* One unit of work of a batch. */
+typedef struct dg_item {
+    const uint8_t* data;   /* JPEG file bytes, or raw interleaved 8-bit pixels when raw_w > 0 (host memory) */
+    uint64_t len;
+    uint32_t raw_w, raw_h, raw_c; /* raw input: size and channels (1 or 3); 0 for JPEG input */
+    uint32_t reserved;
+    const char* forced_key; /* NULL or "": bucket chosen from the image's own aspect ratio; else the key to force
+                               (the "same bucket for every payload of a sample" rule, src/worker_wds.rs:68-76) */
+} dg_item;
+
+/* Per-item outcome: the fields of ImagePayload (src/structs.rs:52-71) plus where the pixels are. */
+typedef struct dg_result {
+    int32_t status;               /* dg_status of this item */
+    uint32_t original_width, original_height;
+    uint32_t width, height, channels, bit_depth;
+    uint64_t nbytes;              /* width * height * channels */
+    const uint8_t* device_data;   /* HWC, row-major, tightly packed, in device memory owned by the batch */
+    dg_plan plan;                 /* valid when the ctx has a transform */
+} dg_result;
+
+typedef struct dg_ctx dg_ctx;
+typedef struct dg_batch dg_batch;
+
+enum {
+    DG_BATCH_DECODE_ONLY = 1u,  /* ignore the ctx transform: payload = decoded image (image_to_payload with img_tfm None) */
+    DG_BATCH_TIMING = 2u        /* record CUDA events around each stage of dg_batch_run */
+};
+
+/* Stages reported by dg_batch_stage_ms. */
+enum { DG_STAGE_UNSTUFF = 0, DG_STAGE_HUFFMAN, DG_STAGE_IDCT, DG_STAGE_COLOR, DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V,
+       DG_STAGE_RESIZE_SHIFT, DG_STAGE_COUNT };
+
+DG_API const char* dg_last_error(void);
+DG_API const char* dg_version(void);
+
+/* ---- context ------------------------------------------------------------------------------------------------ */
+/* DatagoClient::new builds the transform once (src/client.rs:92-95 -> image_processing.rs:77-120).
+ * cfg NULL or crop_and_resize == 0: no transform (payloads are the decoded images).
+ * Invalid configs (size 0, ratio 0, min_ar <= 0, max_ar < min_ar) return DG_E_INVALID where datago asserts (:78-93). */
+#define DG_DEVICE_NONE (-1) /* planning-only ctx: bucket / geometry queries work, every pixel entry point fails */
+DG_API int dg_ctx_create(int device, const dg_image_config* cfg, dg_ctx** out);
+/* Same, running on a caller-owned CUDA stream (a cudaStream_t passed as void*). */
+DG_API int dg_ctx_create_on_stream(int device, const dg_image_config* cfg, void* cuda_stream, dg_ctx** out);
+DG_API void dg_ctx_destroy(dg_ctx* ctx);
+/* The cudaStream_t all work of this ctx is queued on. */
+DG_API void* dg_ctx_stream(dg_ctx* ctx);
+
+/* ---- bucket logic (host only; no device work) ------------------------------------------------------------------- */
+/* build_image_size_list, src/image_processing.rs:188-219: the raw list, duplicates kept. Returns the count. */
+DG_API int dg_size_list(const dg_image_config* cfg, int max_n, uint32_t* w, uint32_t* h);
+/* The key -> size map sorted by aspect ratio (get_ar_aware_transform, :96-119). keys: 16 bytes per entry. Returns the count. */
+DG_API int dg_bucket_table(const dg_ctx* ctx, int max_n, uint32_t* w, uint32_t* h, double* ar, char* keys);
+/* ARAwareTransform::get_closest_aspect_ratio, :222-252. */
+DG_API int dg_closest_aspect_ratio(const dg_ctx* ctx, int32_t w, int32_t h, char key_out[16]);
+/* aspect_ratio_to_str, :130-133. */
+DG_API void dg_aspect_ratio_to_str(uint32_t w, uint32_t h, char key_out[16]);
+/* Geometry half of crop_and_resize, :259-310. */
+DG_API int dg_plan_geometry(const dg_ctx* ctx, uint32_t w, uint32_t h, uint32_t channels, const char* forced_key, dg_plan* out);
+/* Header-only look at a JPEG (what image::ImageReader learns before decode(), src/worker_files.rs:14-16). */
+DG_API int dg_jpeg_probe(const uint8_t* data, uint64_t len, dg_jpeg_info* out);
+
+/* ---- sharding (host only) ----------------------------------------------------------------------------------------- */
+/* get_data_slice_multirank, src/generator_files.rs:24-42. DG_E_INVALID when rank >= world_size (datago asserts). */
+DG_API int dg_rank_slice(uint64_t quorum, uint64_t rank, uint64_t world_size, uint64_t* start, uint64_t* end);
+/* hash_fn, src/generator_wds.rs:50-54: Rust's DefaultHasher over the key string. */
+DG_API uint64_t dg_key_hash(const char* key, uint64_t len);
+/* The rank a webdataset key belongs to, src/generator_wds.rs:140-148. */
+DG_API uint64_t dg_key_rank(const char* key, uint64_t len, uint64_t world_size);
+
+/* ---- batches: image::load_from_memory + image_to_payload for many samples at once ---------------------------- */
+/* Replaces, per item, the decode call (src/worker_files.rs:8-17, src/worker_wds.rs:45, src/worker_http.rs:64)
+ * followed by image_to_payload (src/image_processing.rs:341-431).
+ * create: parses headers, plans geometry, builds device descriptors and filter tables, copies the compressed
+ *         (or raw) bytes into pinned staging.  Items whose header is bad keep a non-zero status and are skipped,
+ *         as datago drops a sample whose decode fails (src/worker_files.rs:63-70).
+ * upload: host -> device copies (async on the ctx stream).
+ * run:    all kernels (async).  May be called repeatedly on an uploaded batch.
+ * download: device -> host copy of every ok item into host_out[i] (entries may be NULL to skip).
+ * sync:   waits for the stream and collects per-item device status words.
+ */
+DG_API int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, dg_batch** out);
+DG_API int dg_batch_upload(dg_batch* b);
+DG_API int dg_batch_run(dg_batch* b);
+DG_API int dg_batch_download(dg_batch* b, uint8_t* const* host_out);
+DG_API int dg_batch_sync(dg_batch* b);
+DG_API int dg_batch_result(const dg_batch* b, int i, dg_result* out);
+/* Milliseconds per stage of the last dg_batch_run of a DG_BATCH_TIMING batch (after dg_batch_sync). */
+DG_API int dg_batch_stage_ms(const dg_batch* b, float ms[DG_STAGE_COUNT]);
+/* Bytes copied host->device by upload, and kernels launched by one run. */
+DG_API int dg_batch_counters(const dg_batch* b, uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint32_t* kernel_launches);
+/* Intermediate device buffers, for stage-by-stage parity tests: coefficient words (int16, scan order) and, for
+ * decode+resize batches, the full-size decoded image of item i. */
+DG_API int dg_batch_debug(const dg_batch* b, int i, const int16_t** coef, uint64_t* nblocks, const uint8_t** decoded);
+DG_API void dg_batch_destroy(dg_batch* b);
+
+/* One call doing create + upload + run + download + sync + destroy; results[i] (optional) receive the outcomes
+ * (device_data is NULL there: the batch is gone). */
+DG_API int dg_process(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, uint8_t* const* host_out, dg_result* results);
+
+/* Device -> host copy helper for callers without a CUDA binding (tests). */
+DG_API int dg_copy_to_host(dg_ctx* ctx, void* dst, const void* device_src, uint64_t nbytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
