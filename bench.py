@@ -1,0 +1,367 @@
+"""Benchmark of the image hot path on B200: decoded(+bucketed) images/s on seeded synthetic JPEGs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c0|c1] [--images M] [--impl reference]
+
+A step is one pass of the path over the whole workload (default: the 8192-JPEG decode-throughput set).  `value` is
+measured with the compressed inputs already in HBM (CUDA events on the library's stream around K back-to-back passes);
+`e2e` goes through the public batch API from host JPEG bytes to host pixel buffers.  Multi-GPU runs are weak-scaled:
+every rank owns one workload-sized shard of an N-times larger job (contiguous rank slices, the rule datago's file
+source uses) and there is no collective on the data path; only the timing is reduced across ranks.
+`--impl reference` times the CPU implementation of the same path (the oracle port; the reference's Rust crates are not
+buildable here) on all host cores.
+"""
+import argparse
+import json
+import os
+import pickle
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+METRIC = "decoded+bucketed images/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def dataset(workload, count, rank, world, barrier):
+    """The seeded workload, generated once per box (rank 0) and shared through /dev/shm."""
+    from datago_b200 import synth
+    cache = f"/dev/shm/datago_b200_{workload}_{count}.pkl"
+    if rank == 0 and not os.path.exists(cache):
+        procs = max(1, (os.cpu_count() or 8) - 1)
+        t = time.time()
+        items = synth.make(workload, range(count), processes=procs)
+        with open(cache + ".tmp", "wb") as f:
+            pickle.dump(items, f, protocol=4)
+        os.replace(cache + ".tmp", cache)
+        print(f"[bench] generated {count} {workload} items on {procs} processes in {time.time() - t:.1f}s", file=sys.stderr)
+    barrier()
+    with open(cache, "rb") as f:
+        return pickle.load(f)
+
+
+class ClockSampler:
+    QUERY = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def window(self, t0, t1):
+        """Keep the samples taken inside [t0, t1]; when the window is too short to hold three, keep all of them
+        (the sampler runs from the first warm-up pass on, so they are all under load)."""
+        inside = [r for (t, r) in self.rows if t0 <= t <= t1]
+        self.rows = inside if len(inside) >= 3 else [r for (_, r) in self.rows]
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.rows and isinstance(self.rows[0], tuple):
+            self.rows = [r for (_, r) in self.rows]
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i] == "Active" for r in self.rows)]
+        pw = [float(r[2]) for r in self.rows if len(r) > 2 and r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons}
+
+
+def workload_stats(items, workload):
+    """Pixels and algorithmic bytes of one pass (per-unit figures: see DESIGN.md)."""
+    import datago_b200 as dg
+    st = dict(images=len(items), pixels=0, compressed=0, coef_bytes=0, plane_bytes=0, rgb_bytes=0, ecs_bits=0)
+    for it in items:
+        if isinstance(it, (bytes, bytearray)):
+            i = dg.jpeg_probe(it)
+            bpm = 1 if i.channels == 1 else i.hsamp * i.vsamp + 2
+            blocks = i.mcux * i.mcuy * bpm
+            st["pixels"] += i.width * i.height
+            st["compressed"] += i.scan_len
+            st["coef_bytes"] += blocks * 128      # 2 * s * P_mcu
+            st["plane_bytes"] += blocks * 64
+            st["rgb_bytes"] += i.width * i.height * i.channels
+        else:
+            st["pixels"] += it.shape[0] * it.shape[1]
+            st["rgb_bytes"] += it.nbytes
+    return st
+
+
+def cpu_baseline(items, kind, cfg, budget_s=12.0):
+    """The oracle port on all host cores over a bounded sample of the workload."""
+    import oracle
+    threads = os.cpu_count() or 1
+    probe_n = min(len(items), max(2 * threads, 8))
+    call = oracle.run_batch(items[:probe_n], kind, cfg, threads)
+    t = time.time()
+    call()
+    per_image = max(1e-4, (time.time() - t) / probe_n)  # seconds per image with all threads busy
+    n = int(min(len(items), max(probe_n, budget_s / per_image)))
+    call = oracle.run_batch(items[:n], kind, cfg, threads)
+    t = time.time()
+    ok = call()
+    dt = time.time() - t
+    return {"value": ok / dt, "unit": "images/s", "cores": threads, "kind": "port",
+            "sample": f"first {n} of {len(items)} items of the workload, {dt:.1f}s wall"}
+
+
+def pil_yardstick(items, budget_s=6.0):
+    """libjpeg-turbo through Pillow on a thread pool: an independent SIMD-optimised CPU decoder, for scale."""
+    import io
+    from concurrent.futures import ThreadPoolExecutor
+    from PIL import Image
+    threads = os.cpu_count() or 1
+
+    def one(b):
+        return np.asarray(Image.open(io.BytesIO(b)).convert("RGB")).shape[0]
+    n = min(len(items), 8 * threads)
+    with ThreadPoolExecutor(threads) as ex:
+        t = time.time()
+        list(ex.map(one, items[:n]))
+        dt = time.time() - t
+        n2 = int(min(len(items), max(n, budget_s / max(dt / n, 1e-5))))
+        t = time.time()
+        list(ex.map(one, items[:n2]))
+        dt = time.time() - t
+    return {"value": n2 / dt, "unit": "images/s", "cores": threads, "sample": f"{n2} items"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c0", "c1", "c2"])
+    ap.add_argument("--images", type=int, default=0)
+    ap.add_argument("--e2e-chunk", type=int, default=1024)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    from datago_b200 import synth
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    count = args.images or synth.COUNTS[args.workload]
+    cfg = synth.IMAGE_CONFIGS[args.workload]
+    kind = {"c0": 1, "c1": 2, "c2": 0}[args.workload]
+    config = {"workload": {"c0": f"C0 local-file set: {count} 4:2:0 q90 JPEGs 256..2048, decode + 1024/32 bucket crop-resize",
+                           "c1": f"C1 resize-only: {count} raw RGB buffers 512..4096, 512/16 buckets",
+                           "c2": f"C2 JPEG decode throughput: {count} baseline 4:2:0 JPEGs 512..1536, q75-95, half with restart interval 4, decode to RGB8"}[args.workload],
+              "images_per_gpu": count, "sharding": "contiguous rank slices of an N x workload job, no collective",
+              "l2": "inputs and intermediates of one pass exceed the 126 MB L2 many times over; no explicit flush"}
+
+    # ---------------- reference arm: the CPU path on the host cores ------------------------------------------------
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        items = dataset(args.workload, count, 0, 1, lambda: None)
+        vals = []
+        base = None
+        for step in range(args.warmup + args.steps):
+            base = cpu_baseline(items, kind, cfg, budget_s=8.0 if step >= args.warmup else 2.0)
+            if step >= args.warmup:
+                vals.append(base["value"])
+        v = statistics.mean(vals)
+        base["value"] = v
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": "images/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * count / v,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+                          "data": "synthetic", "config": config, "cpu_baseline": base,
+                          "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    # ---------------- our arm ------------------------------------------------------------------------------------------------
+    import torch
+    import torch.distributed as dist
+    import datago_b200 as dg
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    items = dataset(args.workload, count, rank, world, barrier)
+    quorum = world * count
+    start, end = dg.rank_slice(quorum, rank, world)  # this rank's shard of the N x workload job
+    items = [items[i % count] for i in range(start, end)]
+    stats = workload_stats(items, args.workload)
+
+    stream = torch.cuda.Stream()
+    ctx = dg.Context(local_rank, cfg, stream=stream.cuda_stream)
+    flags = dg.BATCH_TIMING
+    peak, peak_src = load_peaks()
+
+    # -- inputs resident in HBM ---------------------------------------------------------------------------------------
+    batch = ctx.batch(items, None, flags)
+    batch.upload()
+    batch.sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(1.0)  # nvidia-smi needs a moment before its first sample
+    for _ in range(args.warmup):
+        batch.run()
+    batch.sync()
+    assert all(batch.result(i).status == 0 for i in range(len(items))), "an image failed to decode"
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    barrier()
+    t_begin = time.time()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            batch.run()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    sampler.window(t_begin, time.time())
+    elapsed_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    batch.sync()
+    stage_ms = batch.stage_ms()  # of the last pass
+    launches = batch.counters()["kernel_launches"] * args.steps
+    batch.close()
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    value = world * len(items) * args.steps / (elapsed_ms / 1000.0)
+
+    # -- end to end through the batch API: host bytes in, host pixels out ------------------------------------------
+    chunk = max(1, min(args.e2e_chunk, len(items)))
+    e2e_steps = max(1, min(args.steps, 3))
+    max_out = 0
+    for c0 in range(0, len(items), chunk):
+        with ctx.batch(items[c0:c0 + chunk], None, 0) as b:
+            max_out = max(max_out, sum(int(b.result(i).nbytes) for i in range(len(b))))
+    pinned = torch.empty(max_out + 4096, dtype=torch.uint8).pin_memory()
+    pin_np = pinned.numpy()
+    h2d = d2h = 0
+
+    def e2e_pass():
+        nonlocal h2d, d2h
+        h2d = d2h = 0
+        for c0 in range(0, len(items), chunk):
+            with ctx.batch(items[c0:c0 + chunk], None, 0) as b:
+                b.upload()
+                b.run()
+                outs, off = [], 0
+                for i in range(len(b)):
+                    r = b.result(i)
+                    shape = (r.height, r.width, 3) if r.channels == 3 else (r.height, r.width)
+                    outs.append(pin_np[off:off + r.nbytes].reshape(shape))
+                    off += int(r.nbytes)
+                b.download(outs)
+                b.sync()
+                c = b.counters()
+                h2d += c["h2d_bytes"]
+                d2h += c["d2h_bytes"]
+
+    e2e_pass()  # warm-up: grows the library's pinned and device block caches
+    torch.cuda.synchronize()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * len(items) * e2e_steps / float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # -- roofline of the dominant kernel, from the stage events of the last timed pass -----------------------------
+    bytes_of = {
+        "unstuff": 2 * stats["compressed"],
+        "coef_clear": stats["coef_bytes"],
+        "huff_restart": None, "huff_spec": None,  # filled below (split by image class)
+        "idct": stats["coef_bytes"] + stats["plane_bytes"],
+        "color": stats["plane_bytes"] + stats["rgb_bytes"],
+    }
+    rst_items = [it for it in items if isinstance(it, (bytes, bytearray)) and dg.jpeg_probe(it).restart_interval]
+    rst_stats = workload_stats(rst_items, args.workload) if rst_items else dict(compressed=0, coef_bytes=0)
+    bytes_of["huff_restart"] = rst_stats["compressed"] + rst_stats["coef_bytes"]
+    bytes_of["huff_spec"] = (stats["compressed"] - rst_stats["compressed"]) + (stats["coef_bytes"] - rst_stats["coef_bytes"])
+    stages = {}
+    for name, ms in stage_ms.items():
+        if ms <= 0:
+            continue
+        b = bytes_of.get(name)
+        stages[name] = {"ms": round(ms, 3)}
+        if b:
+            stages[name]["gbs"] = round(b / ms / 1e6, 1)
+            stages[name]["frac"] = round(b / ms / 1e6 / peak, 4)
+    top = max(stages, key=lambda k: stages[k]["ms"]) if stages else None
+    roofline = None
+    if top:
+        achieved = stages[top].get("gbs")
+        roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": round(achieved / peak, 4) if achieved else None, "traffic": None, "peak_source": peak_src}
+    post_ms = stage_ms.get("idct", 0.0) + stage_ms.get("color", 0.0)
+    post_bytes = stats["coef_bytes"] + stats["rgb_bytes"]
+    post = {"ms": round(post_ms, 3), "bytes": post_bytes, "gbs": round(post_bytes / post_ms / 1e6, 1) if post_ms else None,
+            "frac": round(post_bytes / post_ms / 1e6 / peak, 4) if post_ms else None}
+    huff_ms = stage_ms.get("huff_restart", 0.0) + stage_ms.get("huff_spec", 0.0)
+    sm_mhz = clocks.get("sm_mhz") or 1965.0
+    huff = {"ms": round(huff_ms, 3),
+            "bits_per_cycle_per_sm": round(stats["compressed"] * 8 / (huff_ms / 1000.0 * sm_mhz * 1e6 * 148), 4) if huff_ms else None}
+
+    line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8", "data": "synthetic", "config": config,
+            "mpix_per_s": value * stats["pixels"] / len(items) / 1e6,
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "batch": chunk},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "stages": stages, "post_entropy": post,
+            "huffman": huff}
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(items, kind, cfg)
+        if args.workload != "c1":
+            line["cpu_baseline"]["pillow_libjpeg_turbo_decode"] = pil_yardstick(items)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 DG_DEVICE_NONE = -1
 BATCH_DECODE_ONLY = 1
 BATCH_TIMING = 2
-STAGES = ("unstuff", "huffman", "idct", "color", "resize_h", "resize_v", "resize_shift")
+STAGES = ("unstuff", "coef_clear", "huff_restart", "huff_spec", "idct", "color", "resize_h", "resize_v", "resize_shift")
 STATUS_NAMES = {0: "ok", 1: "invalid", 2: "cuda", 3: "truncated", 4: "bad_marker", 5: "unsupported", 6: "bad_table",
                 7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large"}
 

@@ -824,10 +824,21 @@ extern "C" int dg_batch_run(dg_batch* b) {
             launch_unstuff(w, s);
             ++b->launches;
             CU(mark(DG_STAGE_UNSTUFF, false));
-            CU(mark(DG_STAGE_HUFFMAN, true));
+            CU(mark(DG_STAGE_COEF_CLEAR, true));
             CU(cudaMemsetAsync(w.coef, 0, wv.coef_blocks * 128, s));
-            launch_huffman(w, s, &b->launches);
-            CU(mark(DG_STAGE_HUFFMAN, false));
+            CU(mark(DG_STAGE_COEF_CLEAR, false));
+            if (w.restart_segs.total) {
+                CU(mark(DG_STAGE_HUFF_RESTART, true));
+                launch_huff_restart(w, s);
+                ++b->launches;
+                CU(mark(DG_STAGE_HUFF_RESTART, false));
+            }
+            if (w.n_spec) {
+                CU(mark(DG_STAGE_HUFF_SPEC, true));
+                launch_huff_spec(w, s);
+                ++b->launches;
+                CU(mark(DG_STAGE_HUFF_SPEC, false));
+            }
             CU(mark(DG_STAGE_IDCT, true));
             launch_idct(w, s);
             ++b->launches;

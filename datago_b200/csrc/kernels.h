@@ -37,7 +37,8 @@ struct JpegWave {
 };
 
 void launch_unstuff(const JpegWave& w, cudaStream_t s);
-void launch_huffman(const JpegWave& w, cudaStream_t s, uint32_t* launches);
+void launch_huff_restart(const JpegWave& w, cudaStream_t s);
+void launch_huff_spec(const JpegWave& w, cudaStream_t s);
 void launch_idct(const JpegWave& w, cudaStream_t s);
 void launch_color(const JpegWave& w, cudaStream_t s);
 

@@ -372,15 +372,13 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
     if (err) atomicOr(w.status + d.item, err);
 }
 
-void launch_huffman(const JpegWave& w, cudaStream_t s, uint32_t* launches) {
-    if (w.restart_segs.total) {
+void launch_huff_restart(const JpegWave& w, cudaStream_t s) {
+    if (w.restart_segs.total)
         k_huff_restart<<<(w.restart_segs.total + kRestartThreads - 1) / kRestartThreads, kRestartThreads, 0, s>>>(w);
-        ++*launches;
-    }
-    if (w.n_spec) {
-        k_huff_spec<<<w.n_spec, kSpecThreads, 0, s>>>(w);
-        ++*launches;
-    }
+}
+
+void launch_huff_spec(const JpegWave& w, cudaStream_t s) {
+    if (w.n_spec) k_huff_spec<<<w.n_spec, kSpecThreads, 0, s>>>(w);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

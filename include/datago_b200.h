@@ -101,8 +101,8 @@ enum {
 };
 
 /* Stages reported by dg_batch_stage_ms. */
-enum { DG_STAGE_UNSTUFF = 0, DG_STAGE_HUFFMAN, DG_STAGE_IDCT, DG_STAGE_COLOR, DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V,
-       DG_STAGE_RESIZE_SHIFT, DG_STAGE_COUNT };
+enum { DG_STAGE_UNSTUFF = 0, DG_STAGE_COEF_CLEAR, DG_STAGE_HUFF_RESTART, DG_STAGE_HUFF_SPEC, DG_STAGE_IDCT, DG_STAGE_COLOR,
+       DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V, DG_STAGE_RESIZE_SHIFT, DG_STAGE_COUNT };
 
 DG_API const char* dg_last_error(void);
 DG_API const char* dg_version(void);

@@ -1,0 +1,134 @@
+"""CUDA baseline-JPEG decode against the oracle: bit-exact pixels and coefficients, through the C ABI."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import datago_b200 as dg
+import oracle
+from gpu_common import assert_same, ctx, jpeg, scan_order
+
+pytestmark = pytest.mark.gpu
+
+
+def test_golden_fixtures_bit_exact(golden_dir):
+    dec = np.load(os.path.join(golden_dir, "decode.npz"))
+    paths = sorted(glob.glob(os.path.join(golden_dir, "jpeg_*.jpg")))
+    datas = [open(p, "rb").read() for p in paths]
+    res = ctx().process(datas)
+    for p, (st, out, r) in zip(paths, res):
+        name = os.path.basename(p)[5:-4]
+        assert st == 0, name
+        assert_same(out, dec[name], name)
+        assert (r.original_width, r.original_height) == (out.shape[1], out.shape[0])
+        assert r.bit_depth == 8 and r.channels == (3 if out.ndim == 3 else 1)
+
+
+CASES = [
+    # w, h, sampling, quality, restart, gray
+    (64, 48, "4:2:0", 90, 0, False), (64, 48, "4:2:0", 90, 2, False), (256, 256, "4:2:0", 75, 0, False),
+    (257, 131, "4:2:0", 95, 4, False), (17, 33, "4:2:0", 90, 0, False), (100, 60, "4:4:4", 90, 0, False),
+    (33, 17, "4:4:4", 50, 2, False), (120, 80, "4:2:2", 85, 0, False), (31, 45, "4:2:2", 85, 5, False),
+    (1024, 768, "4:2:0", 85, 0, False), (1024, 768, "4:2:0", 85, 4, False), (1536, 1536, "4:2:0", 95, 0, False),
+    (2048, 1040, "4:4:4", 92, 0, False), (1000, 1000, "4:2:0", 30, 0, False), (640, 480, "4:2:0", 100, 0, False),
+    (640, 480, "4:2:0", 100, 1, False), (3, 3, "4:2:0", 90, 0, False), (1, 1, "4:2:0", 90, 0, False),
+    (2, 5, "4:2:0", 90, 0, False), (8, 8, "4:4:4", 90, 0, False), (90, 70, None, 80, 0, True),
+    (200, 300, None, 80, 3, True), (1200, 900, None, 90, 0, True), (512, 512, "4:2:0", 75, 1000, False),
+]
+
+
+def test_decode_matrix_bit_exact():
+    rng = np.random.default_rng(5)
+    datas = [jpeg(rng, w, h, sub, q, rst, gray) for (w, h, sub, q, rst, gray) in CASES]
+    res = ctx().process(datas)
+    for case, data, (st, out, _) in zip(CASES, datas, res):
+        assert st == 0, case
+        assert_same(out, oracle.jpeg_decode(data), str(case))
+
+
+def test_coefficients_bit_exact():
+    rng = np.random.default_rng(6)
+    datas = [jpeg(rng, 320, 240, "4:2:0", 90, 0), jpeg(rng, 320, 240, "4:2:0", 90, 3), jpeg(rng, 200, 120, "4:4:4", 80, 0),
+             jpeg(rng, 150, 100, None, 85, 0, True), jpeg(rng, 1280, 960, "4:2:0", 95, 0, noise=12.0)]
+    with ctx().batch(datas) as b:
+        b.upload(); b.run(); b.sync()
+        for i, data in enumerate(datas):
+            coefs, _, _ = oracle.jpeg_decode_stages(data)
+            want = scan_order(coefs, oracle.jpeg_info(data))
+            got = b.debug_coefficients(i)
+            assert got.shape == want.shape
+            assert np.array_equal(got, want), i
+
+
+def test_long_noisy_stream_needs_many_subsequence_chunks():
+    # > 512 subsequences per CTA chunk: exercises the carried decoder state between chunks
+    rng = np.random.default_rng(8)
+    a = rng.integers(0, 256, (1024, 1024, 3), dtype=np.uint8)
+    from datago_b200 import synth
+    data = synth.encode_jpeg(a, 98, "4:4:4", 0)
+    assert len(data) > 1_000_000
+    (st, out, _), = ctx().process([data])
+    assert st == 0
+    assert_same(out, oracle.jpeg_decode(data))
+
+
+def test_rerun_gives_identical_output():
+    rng = np.random.default_rng(9)
+    datas = [jpeg(rng, 400, 300), jpeg(rng, 333, 222, rst=2)]
+    with ctx().batch(datas) as b:
+        b.upload()
+        b.run(); first = b.download(); b.sync()
+        first = [f.copy() for f in first]
+        b.run(); second = b.download(); b.sync()
+        for f, s in zip(first, second):
+            assert np.array_equal(f, s)
+
+
+def test_bad_inputs_get_a_status_and_do_not_disturb_neighbours():
+    rng = np.random.default_rng(10)
+    good = jpeg(rng, 320, 200)
+    good_rst = jpeg(rng, 320, 200, rst=2)
+    truncated = good[: len(good) // 2]
+    headless = good[:200]
+    garbage = bytes(rng.integers(0, 256, 5000, dtype=np.uint8))
+    flipped = bytearray(good)
+    for pos in range(len(good) // 2, len(good) // 2 + 400, 7):  # corrupt entropy-coded bytes
+        flipped[pos] ^= 0x5A
+    no_rst = good_rst.replace(b"\xff\xd3", b"\x12\x34")  # knock out some restart markers
+    import io
+    from PIL import Image
+    prog = io.BytesIO()
+    Image.fromarray(np.zeros((64, 64, 3), np.uint8)).save(prog, "JPEG", progressive=True)
+    items = [good, truncated, headless, garbage, bytes(flipped), b"", prog.getvalue(), no_rst, good_rst, good]
+    res = ctx().process(items)
+    want = oracle.jpeg_decode(good)
+    assert res[0][0] == 0 and res[9][0] == 0 and res[8][0] == 0
+    assert_same(res[0][1], want)
+    assert_same(res[9][1], want)
+    assert_same(res[8][1], oracle.jpeg_decode(good_rst))
+    assert res[1][0] == 3          # truncated entropy data
+    assert res[2][0] in (3, 4)     # headers cut
+    assert res[3][0] == 4          # not a JPEG
+    assert res[5][0] in (1, 4)     # empty
+    assert res[6][0] == 5          # progressive
+    assert res[7][0] != 0          # restart markers missing
+    # bit flips may or may not be detectable; what matters is a defined outcome and untouched neighbours
+    assert res[4][0] in (0, 3, 7)
+
+
+def test_unstuffing_of_ff_bytes():
+    # saturated noise at quality 100 produces many FF 00 pairs in the entropy-coded data
+    rng = np.random.default_rng(12)
+    a = (rng.integers(0, 2, (256, 256, 3)) * 255).astype(np.uint8)
+    from datago_b200 import synth
+    for rst in (0, 1):
+        data = synth.encode_jpeg(a, 100, "4:4:4", rst)
+        assert data.count(b"\xff\x00") > 50
+        (st, out, _), = ctx().process([data])
+        assert st == 0
+        assert_same(out, oracle.jpeg_decode(data))
+
+
+def test_empty_batch():
+    assert ctx().process([]) == []
