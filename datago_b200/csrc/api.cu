@@ -109,6 +109,7 @@ struct dg_ctx {
     std::mutex mu;
     BlockCache dev{false}, pin{true};
     size_t wave_bytes = (size_t)8 << 30;  // coefficient bytes per wave
+    size_t l2_group_bytes = (size_t)64 << 20;  // plane bytes per IDCT + colour launch pair
 };
 
 static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool have_stream, dg_ctx** out) {
@@ -137,6 +138,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
         if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return fail(DG_E_CUDA, "cudaStreamCreate failed"); }
         c->own_stream = true;
     }
+    if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
     return DG_OK;
@@ -276,6 +278,7 @@ struct WavePlan {
     int first_item = 0, last_item = 0;  // [first, last)
     std::vector<JpegDesc> descs;
     std::vector<uint32_t> spec_list, restart_list, restart_first, block_first, color_first;
+    std::vector<std::array<uint32_t, 4>> groups;  // (first block, block count, first colour tile, tile count) per L2 group
     std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
     std::vector<uint32_t> pass_first[4];
     std::vector<CopyJob> copies;
@@ -324,7 +327,7 @@ struct Planner {
     dg_batch* b;
     std::unordered_map<std::string, uint32_t> huff_ids, qt_ids;
     std::vector<HuffTable> huff_pool;
-    std::vector<uint16_t> qt_pool;
+    std::vector<uint32_t> qt_pool;  // 32 words per table, the layout JpegWave::qt32 documents
     std::map<std::array<uint64_t, 4>, std::pair<size_t, FilterTable*>> table_ids;  // key -> (word offset, table)
     std::vector<FilterTable*> tables;
     std::vector<uint32_t> table_words;
@@ -347,8 +350,8 @@ struct Planner {
         std::string key((const char*)q, 128);
         auto it = qt_ids.find(key);
         if (it != qt_ids.end()) return it->second;
-        uint32_t id = (uint32_t)(qt_pool.size() / 64);
-        qt_pool.insert(qt_pool.end(), q, q + 64);
+        uint32_t id = (uint32_t)(qt_pool.size() / 32);
+        for (int i = 0; i < 32; ++i) qt_pool.push_back((uint32_t)q[2 * i] | ((uint32_t)q[2 * i + 1] << 24));
         qt_ids.emplace(std::move(key), id);
         return id;
     }
@@ -563,9 +566,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     size_t scratch_max = 0, blob_off = 0;
     for (WavePlan& wv : b->waves) {
         size_t us = 0, planes = 0, decoded = 0, mids = 0, blocks = 0, segs = 0;
-        uint32_t color_tiles_total = 0, restart_total = 0;
+        uint32_t color_total = 0, restart_total = 0;
+        size_t group_bytes = 0;
         wv.block_first.push_back(0);
         wv.color_first.push_back(0);
+        wv.groups.push_back({0, 0, 0, 0});
         wv.restart_first.push_back(0);
         for (int i = wv.first_item; i < wv.last_item; ++i) {
             ItemPlan& it = b->items[i];
@@ -577,6 +582,9 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             memset(&d, 0, sizeof d);
             for (uint32_t c = 0; c < 3 && !it.status; ++c) {
                 const uint32_t cc = c < h.ncomp ? c : 0;
+                for (int k = 0; k < 64; ++k)  // the dequantiser multiplies by one byte: 16-bit tables are not on this path
+                    if (h.qt[h.comp_tq[cc]][k] > 255) it.status = DG_E_UNSUPPORTED;
+                if (it.status) break;
                 d.qt[c] = pl.qt_id(h.qt[h.comp_tq[cc]]);
                 int rc = pl.huff_id(h.dc[h.comp_td[cc]], &d.dc_tab[c]);
                 if (!rc) rc = pl.huff_id(h.ac[h.comp_ta[cc]], &d.ac_tab[c]);
@@ -609,8 +617,18 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             else wv.spec_list.push_back((uint32_t)wv.descs.size());
             wv.descs.push_back(d);
             wv.block_first.push_back((uint32_t)blocks);
-            color_tiles_total += color_tiles(h.width, h.height);
-            wv.color_first.push_back(color_tiles_total);
+            const uint32_t ntiles = color_tiles(h.width, h.mcuy);
+            color_total += ntiles;
+            wv.color_first.push_back(color_total);
+            // images whose planes fit the L2 budget together share one IDCT launch and one colour launch
+            const size_t pbytes = (size_t)it.nblocks * 64;
+            if (wv.groups.back()[1] && group_bytes + pbytes > ctx->l2_group_bytes) {
+                wv.groups.push_back({(uint32_t)(blocks - it.nblocks), 0, color_total - ntiles, 0});
+                group_bytes = 0;
+            }
+            group_bytes += pbytes;
+            wv.groups.back()[1] += it.nblocks;
+            wv.groups.back()[3] += ntiles;
         }
         wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
         size_t o = 0;
@@ -813,7 +831,7 @@ extern "C" int dg_batch_run(dg_batch* b) {
             w.out = transform ? sc + wv.off_decoded : b->d_persist + b->off_out;
             w.status = (uint32_t*)(b->d_persist + b->off_status);
             w.huff = (const HuffTable*)(meta + b->m_huff);
-            w.qt = (const uint16_t*)(meta + b->m_qt);
+            w.qt32 = (const uint32_t*)(meta + b->m_qt);
             w.spec_list = (const uint32_t*)(meta + wv.m_spec);
             w.n_spec = (uint32_t)wv.spec_list.size();
             w.restart_list = (const uint32_t*)(meta + wv.m_restart_list);
@@ -839,14 +857,16 @@ extern "C" int dg_batch_run(dg_batch* b) {
                 ++b->launches;
                 CU(mark(DG_STAGE_HUFF_SPEC, false));
             }
-            CU(mark(DG_STAGE_IDCT, true));
-            launch_idct(w, s);
-            ++b->launches;
-            CU(mark(DG_STAGE_IDCT, false));
-            CU(mark(DG_STAGE_COLOR, true));
-            launch_color(w, s);
-            ++b->launches;
-            CU(mark(DG_STAGE_COLOR, false));
+            for (const auto& g : wv.groups) {
+                CU(mark(DG_STAGE_IDCT, true));
+                launch_idct(w, g[0], g[1], s);
+                ++b->launches;
+                CU(mark(DG_STAGE_IDCT, false));
+                CU(mark(DG_STAGE_COLOR, true));
+                launch_color(w, g[2], g[3], s);
+                ++b->launches;
+                CU(mark(DG_STAGE_COLOR, false));
+            }
         }
         if (transform) {
             const uint32_t* tables = (const uint32_t*)(meta + b->m_tables);

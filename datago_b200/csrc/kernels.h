@@ -27,7 +27,7 @@ struct JpegWave {
     uint8_t* out;            // decoded images
     uint32_t* status;        // [items of the batch]
     const HuffTable* huff;   // table pool
-    const uint16_t* qt;      // quantisation pool, 64 entries each, natural order
+    const uint32_t* qt32;    // quantisation pool, 32 words per table: word i holds q[2i] in byte 0 and q[2i+1] in byte 3
     // speculative (no restart marker) images and restart-interval images of this wave
     const uint32_t* spec_list; uint32_t n_spec;
     OwnerMap restart_segs;   // owner = index into restart_list
@@ -39,12 +39,14 @@ struct JpegWave {
 void launch_unstuff(const JpegWave& w, cudaStream_t s);
 void launch_huff_restart(const JpegWave& w, cudaStream_t s);
 void launch_huff_spec(const JpegWave& w, cudaStream_t s);
-void launch_idct(const JpegWave& w, cudaStream_t s);
-void launch_color(const JpegWave& w, cudaStream_t s);
+// blocks [first, first + count) of the wave / colour tiles [first, first + count): callers launch them in groups of a
+// few images so that the planes written by the IDCT are still in L2 when the colour kernel reads them
+void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s);
+void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s);
 
-// tiles of the colour kernel for a w x h image
-constexpr uint32_t kColorTileW = 128, kColorTileH = 8;
-inline uint32_t color_tiles(uint32_t w, uint32_t h) { return ((w + kColorTileW - 1) / kColorTileW) * ((h + kColorTileH - 1) / kColorTileH); }
+// The colour kernel gives one CTA 256 pixels of one MCU row.
+constexpr uint32_t kColorTileW = 256;
+inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) { return ((width + kColorTileW - 1) / kColorTileW) * mcuy; }
 
 // ---- resize ---------------------------------------------------------------------------------------------------------
 constexpr uint32_t kConvTileW = 64, kConvTileH = 4;     // horizontal pass: output pixels per CTA

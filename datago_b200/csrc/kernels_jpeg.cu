@@ -382,35 +382,78 @@ void launch_huff_spec(const JpegWave& w, cudaStream_t s) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// K2  dequantise + 8x8 inverse DCT (the 13-bit fixed-point "islow" factorisation), +128, clamp.
-//     One thread per block; coefficients are read as eight 16-byte words, rows are written as 8-byte words into the
-//     component plane.
+// K2  dequantise + 8x8 inverse DCT (the 13-bit fixed-point "islow" factorisation: columns, round to 2 fractional
+//     bits, rows, round, +128, clamp) for every block of a wave, written to 8-bit component planes.
+//
+//     The stage is bound by integer instruction issue, not by HBM, so the kernel is built to execute few
+//     instructions: one thread per block (no exchange between lanes), dequantisation and 16-bit unpacking in one
+//     dp2a per coefficient, rounding constants folded into the even part of each butterfly, saturating pack
+//     instructions, and a reduced butterfly when every block of the warp keeps its energy in the top-left 4x4.
+//     All arithmetic is exact in 32-bit integers, so regrouping the butterflies cannot change a result.
 // ---------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void idct_1d(int32_t (&x)[8], int32_t (&o)[8]) {
-    constexpr int32_t F_0_298 = 2446, F_0_390 = 3196, F_0_541 = 4433, F_0_765 = 6270, F_0_899 = 7373, F_1_175 = 9633,
-                      F_1_501 = 12299, F_1_847 = 15137, F_1_961 = 16069, F_2_053 = 16819, F_2_562 = 20995, F_3_072 = 25172;
-    int32_t z2 = x[2], z3 = x[6];
-    int32_t z1 = (z2 + z3) * F_0_541;
-    int32_t t2 = z1 - z3 * F_1_847, t3 = z1 + z2 * F_0_765;
-    int32_t t0 = (int32_t)((uint32_t)(x[0] + x[4]) << 13), t1 = (int32_t)((uint32_t)(x[0] - x[4]) << 13);
+constexpr int32_t F_0_298 = 2446, F_0_390 = 3196, F_0_541 = 4433, F_0_765 = 6270, F_0_899 = 7373, F_1_175 = 9633,
+                  F_1_501 = 12299, F_1_847 = 15137, F_1_961 = 16069, F_2_053 = 16819, F_2_562 = 20995, F_3_072 = 25172;
+
+// o[k] = (butterfly(x)[k] + RND) >> SHIFT
+template <int32_t RND, int SHIFT>
+__device__ __forceinline__ void idct8(int32_t x0, int32_t x1, int32_t x2, int32_t x3, int32_t x4, int32_t x5, int32_t x6,
+                                      int32_t x7, int32_t (&o)[8]) {
+    const int32_t z1e = (x2 + x6) * F_0_541;
+    const int32_t t2 = z1e - x6 * F_1_847, t3 = z1e + x2 * F_0_765;
+    const int32_t t0 = (x0 + x4) * 8192 + RND, t1 = (x0 - x4) * 8192 + RND;
     const int32_t t10 = t0 + t3, t13 = t0 - t3, t11 = t1 + t2, t12 = t1 - t2;
-    t0 = x[7]; t1 = x[5]; t2 = x[3]; t3 = x[1];
-    z1 = t0 + t3; z2 = t1 + t2; z3 = t0 + t2;
-    int32_t z4 = t1 + t3;
+    int32_t z1 = x7 + x1, z2 = x5 + x3, z3 = x7 + x3, z4 = x5 + x1;
     const int32_t z5 = (z3 + z4) * F_1_175;
-    t0 *= F_0_298; t1 *= F_2_053; t2 *= F_3_072; t3 *= F_1_501;
-    z1 *= -F_0_899; z2 *= -F_2_562; z3 *= -F_1_961; z4 *= -F_0_390;
-    z3 += z5; z4 += z5;
-    t0 += z1 + z3; t1 += z2 + z4; t2 += z2 + z3; t3 += z1 + z4;
-    o[0] = t10 + t3; o[7] = t10 - t3; o[1] = t11 + t2; o[6] = t11 - t2;
-    o[2] = t12 + t1; o[5] = t12 - t1; o[3] = t13 + t0; o[4] = t13 - t0;
+    z3 = z5 - z3 * F_1_961;
+    z4 = z5 - z4 * F_0_390;
+    z1 *= -F_0_899;
+    z2 *= -F_2_562;
+    const int32_t o0 = x7 * F_0_298 + z1 + z3, o1 = x5 * F_2_053 + z2 + z4, o2 = x3 * F_3_072 + z2 + z3,
+                  o3 = x1 * F_1_501 + z1 + z4;
+    o[0] = (t10 + o3) >> SHIFT; o[7] = (t10 - o3) >> SHIFT; o[1] = (t11 + o2) >> SHIFT; o[6] = (t11 - o2) >> SHIFT;
+    o[2] = (t12 + o1) >> SHIFT; o[5] = (t12 - o1) >> SHIFT; o[3] = (t13 + o0) >> SHIFT; o[4] = (t13 - o0) >> SHIFT;
 }
 
+// The same butterfly with x4 = x5 = x6 = x7 = 0 (constants merged; exact because the arithmetic is a ring).
+template <int32_t RND, int SHIFT>
+__device__ __forceinline__ void idct8_lo4(int32_t x0, int32_t x1, int32_t x2, int32_t x3, int32_t (&o)[8]) {
+    const int32_t t2 = x2 * F_0_541, t3 = x2 * (F_0_541 + F_0_765);
+    const int32_t t0 = x0 * 8192 + RND;
+    const int32_t t10 = t0 + t3, t13 = t0 - t3, t11 = t0 + t2, t12 = t0 - t2;
+    const int32_t o0 = x1 * (F_1_175 - F_0_899) + x3 * (F_1_175 - F_1_961);
+    const int32_t o1 = x1 * (F_1_175 - F_0_390) + x3 * (F_1_175 - F_2_562);
+    const int32_t o2 = x1 * F_1_175 + x3 * (F_3_072 - F_2_562 - F_1_961 + F_1_175);
+    const int32_t o3 = x1 * (F_1_501 - F_0_899 - F_0_390 + F_1_175) + x3 * F_1_175;
+    o[0] = (t10 + o3) >> SHIFT; o[7] = (t10 - o3) >> SHIFT; o[1] = (t11 + o2) >> SHIFT; o[6] = (t11 - o2) >> SHIFT;
+    o[2] = (t12 + o1) >> SHIFT; o[5] = (t12 - o1) >> SHIFT; o[3] = (t13 + o0) >> SHIFT; o[4] = (t13 - o0) >> SHIFT;
+}
+
+// packs sat_u8 of four ints into one word, first argument in the lowest byte
+__device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, int32_t c, int32_t d) {
+    uint32_t hi, r;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return r;
+}
+
+// coefficient pair (low half, high half of cw) times the two quantisers in bytes 0 and 3 of qw
+__device__ __forceinline__ void dequant_pair(uint32_t cw, uint32_t qw, int32_t& lo, int32_t& hi) {
+    asm("dp2a.lo.s32.u32 %0, %1, %2, 0;" : "=r"(lo) : "r"(cw), "r"(qw));
+    asm("dp2a.hi.s32.u32 %0, %1, %2, 0;" : "=r"(hi) : "r"(cw), "r"(qw));
+}
+
+constexpr int32_t kRound1 = 1 << 10, kRound2 = (1 << 17) + (128 << 18);
 constexpr int kIdctThreads = 128;
 
-__global__ void __launch_bounds__(kIdctThreads) k_idct(JpegWave w) {
-    const uint32_t g = blockIdx.x * kIdctThreads + threadIdx.x;
-    if (g >= w.blocks.total) return;
+__global__ void __launch_bounds__(kIdctThreads, 7) k_idct(JpegWave w, uint32_t first, uint32_t count) {
+    const uint32_t local = blockIdx.x * kIdctThreads + threadIdx.x;
+    const bool valid = local < count;
+    const uint32_t g = first + (valid ? local : 0);
+    // the coefficient address depends on the block index alone: start these loads before the descriptor look-ups
+    const uint4* src = reinterpret_cast<const uint4*>(w.coef + (size_t)g * 64);
+    uint4 c[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c[r] = __ldcs(src + r);  // read once: do not keep in L2
     const uint32_t img = owner_of(w.blocks, g);
     const JpegDesc& d = w.descs[img];
     const uint32_t blk = g - (uint32_t)d.block_off;
@@ -418,60 +461,112 @@ __global__ void __launch_bounds__(kIdctThreads) k_idct(JpegWave w) {
     const uint32_t my = mcu / d.mcux, mx = mcu - my * d.mcux;
     const uint32_t luma = d.hs * d.vs;
     uint32_t comp, bx, by;
-    if (k < luma) { comp = 0; bx = mx * d.hs + k % d.hs; by = my * d.vs + k / d.hs; }
+    if (k < luma) { comp = 0; const uint32_t ky = k / d.hs; bx = mx * d.hs + (k - ky * d.hs); by = my * d.vs + ky; }
     else { comp = k - luma + 1; bx = mx; by = my; }
-    const uint4* src = reinterpret_cast<const uint4*>(w.coef + (size_t)g * 64);
-    const uint4* qq = reinterpret_cast<const uint4*>(w.qt + (size_t)d.qt[comp] * 64);
-
-    int32_t ws[8][8];  // [row][col]
+    const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
+                             c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
+    const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
+    const bool sparse = __all_sync(0xFFFFFFFFu, (hi_rows | hi_cols) == 0);
+    const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[comp] * 32);
+    uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
+    const uint32_t pitch = d.plane_pitch[comp];
+    if (sparse) {
+        int32_t x[4][4], ws[8][4];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        const uint4 cv = src[r];
-        const uint4 qv = __ldg(qq + r);
-        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w}, qw[4] = {qv.x, qv.y, qv.z, qv.w};
+        for (int r = 0; r < 4; ++r) {
+            const uint4 qv = __ldg(qq + r);
+            dequant_pair(c[r].x, qv.x, x[r][0], x[r][1]);
+            dequant_pair(c[r].y, qv.y, x[r][2], x[r][3]);
+        }
+#pragma unroll
+        for (int col = 0; col < 4; ++col) {
+            int32_t o[8];
+            idct8_lo4<kRound1, 11>(x[0][col], x[1][col], x[2][col], x[3][col], o);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int32_t o[8];
+            idct8_lo4<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], o);
+            if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
+        }
+    } else {
+        int32_t ws[8][8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint4 qv = __ldg(qq + r);
+            dequant_pair(c[r].x, qv.x, ws[r][0], ws[r][1]);
+            dequant_pair(c[r].y, qv.y, ws[r][2], ws[r][3]);
+            dequant_pair(c[r].z, qv.z, ws[r][4], ws[r][5]);
+            dequant_pair(c[r].w, qv.w, ws[r][6], ws[r][7]);
+        }
+#pragma unroll
+        for (int col = 0; col < 8; ++col) {
+            int32_t o[8];
+            idct8<kRound1, 11>(ws[0][col], ws[1][col], ws[2][col], ws[3][col], ws[4][col], ws[5][col], ws[6][col], ws[7][col], o);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int32_t o[8];
+            idct8<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], ws[r][4], ws[r][5], ws[r][6], ws[r][7], o);
+            if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
+        }
+    }
+}
+
+void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s) {
+    if (count) k_idct<<<(count + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w, first, count);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// K3  chroma upsampling + YCbCr -> RGB (16-bit fixed point constants 1.402, 0.34414, 0.71414, 1.772), interleaved
+//     RGB8 out.  A CTA owns 256 x (8 * vs) pixels, a thread 8 pixels of a row (and the same 8 of row + 8).
+//       4:2:0  triangle filter: every output sample is (9a + 3b + 3c + d + bias) >> 4 over its 2x2 chroma
+//              neighbourhood -- one dp4a on bytes gathered from a shared-memory tile (1-sample halo, clamped to the
+//              real plane extent, which is what the edge rules of the filter amount to);
+//       4:4:4  and grayscale: straight from the planes;
+//       other samplings and chroma planes at most two samples wide: a plain per-pixel path.
+//     The +128 offsets and the rounding term are folded into one constant per channel; the luma byte is added with a
+//     one-hot dp4a; results are saturated and packed four at a time.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kColorThreads = 256;
+constexpr int kCTileCols = kColorTileW / 2 + 8;  // 4 bytes of left margin (halo in the last one), halo + slack right
+
+__device__ __forceinline__ uint32_t dp4a_u(uint32_t a, uint32_t b, uint32_t c) { return __dp4a(a, b, c); }
+
+// 8 pixels: luma words y0, y1; chroma values cb[i], cr[i]; out: 24 bytes
+__device__ __forceinline__ void ycc_to_rgb8(uint32_t y0, uint32_t y1, const int32_t (&cb)[8], const int32_t (&cr)[8], uint32_t (&out)[6]) {
+    constexpr int32_t kR = 32768 - 91881 * 128, kG = 32768 + 22554 * 128 + 46802 * 128, kB = 32768 - 116130 * 128;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // four pixels at a time keeps fewer values live
+        const uint32_t yw = h ? y1 : y0;
+        int32_t v[12];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            ws[r][2 * i] = (int32_t)(int16_t)(cw[i] & 0xFFFFu) * (int32_t)(qw[i] & 0xFFFFu);
-            ws[r][2 * i + 1] = (int32_t)(int16_t)(cw[i] >> 16) * (int32_t)(qw[i] >> 16);
+            const uint32_t sel = 1u << (8 * i);
+            const int32_t b = cb[4 * h + i], r = cr[4 * h + i];
+            v[3 * i] = (int32_t)dp4a_u(yw, sel, (uint32_t)((r * 91881 + kR) >> 16));
+            v[3 * i + 1] = (int32_t)dp4a_u(yw, sel, (uint32_t)((b * -22554 + (r * -46802 + kG)) >> 16));
+            v[3 * i + 2] = (int32_t)dp4a_u(yw, sel, (uint32_t)((b * 116130 + kB) >> 16));
         }
-    }
-    // columns
 #pragma unroll
-    for (int cidx = 0; cidx < 8; ++cidx) {
-        int32_t x[8], o[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) x[r] = ws[r][cidx];
-        idct_1d(x, o);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) ws[r][cidx] = (o[r] + (1 << 10)) >> 11;
-    }
-    // rows
-    uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        int32_t o[8];
-        idct_1d(ws[r], o);
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            int32_t v = ((o[i] + (1 << 17)) >> 18) + 128;
-            v = min(max(v, 0), 255);
-            if (i < 4) lo |= (uint32_t)v << (8 * i); else hi |= (uint32_t)v << (8 * (i - 4));
-        }
-        *reinterpret_cast<uint2*>(dst + (size_t)r * d.plane_pitch[comp]) = make_uint2(lo, hi);
+        for (int j = 0; j < 3; ++j) out[3 * h + j] = pack_sat_u8(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
     }
 }
 
-void launch_idct(const JpegWave& w, cudaStream_t s) {
-    if (w.blocks.total) k_idct<<<(w.blocks.total + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w);
+__device__ __forceinline__ void store_rgb8(uint8_t* o, const uint32_t (&px)[6], int npx) {
+    if (npx == 8 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
+        uint2* o2 = reinterpret_cast<uint2*>(o);
+        __stcs(o2, make_uint2(px[0], px[1])); __stcs(o2 + 1, make_uint2(px[2], px[3])); __stcs(o2 + 2, make_uint2(px[4], px[5]));
+    } else {
+        for (int i = 0; i < npx * 3; ++i) o[i] = (uint8_t)(px[i >> 2] >> (8 * (i & 3)));
+    }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// K3  chroma upsampling (triangle filter with replicated edges; plain replication when the chroma plane is at most
-//     two samples wide) + YCbCr -> RGB in 16-bit fixed point, interleaved RGB8 out.  Grayscale: rows are copied.
-//     One thread per 2x2 output quad.
-// ---------------------------------------------------------------------------------------------------------------
-struct ChromaPlane {
+struct ChromaPlane {  // per-pixel path
     const uint8_t* p;
     uint32_t pitch;
     int dw, dh, hs, vs;
@@ -498,49 +593,135 @@ struct ChromaPlane {
     }
 };
 
-__device__ __forceinline__ uint8_t clamp_u8(int v) { return (uint8_t)min(max(v, 0), 255); }
-
-constexpr int kColorThreads = (kColorTileW / 2) * (kColorTileH / 2);
-
-__global__ void __launch_bounds__(kColorThreads) k_color(JpegWave w) {
-    const uint32_t img = owner_of(w.color_tiles, blockIdx.x);
+__global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t first_tile) {
+    __shared__ __align__(16) uint8_t s_c[2][10][kCTileCols];
+    __shared__ uint32_t s_img;
+    if (threadIdx.x == 0) s_img = owner_of(w.color_tiles, first_tile + blockIdx.x);
+    __syncthreads();
+    const uint32_t img = s_img;
     const JpegDesc& d = w.descs[img];
-    const uint32_t tile = blockIdx.x - w.color_tiles.first[img];
+    const uint32_t tile = first_tile + blockIdx.x - w.color_tiles.first[img];
+    const int W = (int)d.width, H = (int)d.height, hs = (int)d.hs, vs = (int)d.vs;
     const uint32_t tiles_x = (d.width + kColorTileW - 1) / kColorTileW;
     const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
-    const int x0 = (int)(tx * kColorTileW + (threadIdx.x % (kColorTileW / 2)) * 2);
-    const int y0 = (int)(ty * kColorTileH + (threadIdx.x / (kColorTileW / 2)) * 2);
-    const int W = (int)d.width, H = (int)d.height;
-    if (x0 >= W || y0 >= H) return;
+    const int lane = threadIdx.x & 31, rowi = threadIdx.x >> 5;  // 32 column groups x 8 rows
+    const int x = (int)tx * (int)kColorTileW + lane * 8;
+    const int y_base = (int)ty * 8 * vs;
+    uint8_t* out = w.out + d.out_off;
     const uint8_t* yp = w.planes + d.plane_off[0];
     const uint32_t ypitch = d.plane_pitch[0];
-    if (d.ncomp == 1) {
-        uint8_t* o = w.out + d.out_off;
-        for (int dy = 0; dy < 2 && y0 + dy < H; ++dy)
-            for (int dx = 0; dx < 2 && x0 + dx < W; ++dx)
-                o[(size_t)(y0 + dy) * W + x0 + dx] = __ldg(yp + (size_t)(y0 + dy) * ypitch + x0 + dx);
+
+    if (d.ncomp == 1) {  // grayscale: copy the real extent of the luma plane
+        const int y = y_base + rowi;
+        if (x < W && y < H) {
+            const uint2 v = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
+            uint8_t* o = out + (size_t)y * W + x;
+            const int npx = min(8, W - x);
+            if (npx == 8 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) __stcs(reinterpret_cast<uint2*>(o), v);
+            else for (int i = 0; i < npx; ++i) o[i] = (uint8_t)((i < 4 ? v.x : v.y) >> (8 * (i & 3)));
+        }
         return;
     }
-    const int dw = (W * 1 + (int)d.hs - 1) / (int)d.hs, dh = (H + (int)d.vs - 1) / (int)d.vs;
-    const ChromaPlane cbp{w.planes + d.plane_off[1], d.plane_pitch[1], dw, dh, (int)d.hs, (int)d.vs};
-    const ChromaPlane crp{w.planes + d.plane_off[2], d.plane_pitch[2], dw, dh, (int)d.hs, (int)d.vs};
-    uint8_t* o = w.out + d.out_off;
-    for (int dy = 0; dy < 2 && y0 + dy < H; ++dy) {
-        const int y = y0 + dy;
-        for (int dx = 0; dx < 2 && x0 + dx < W; ++dx) {
-            const int x = x0 + dx;
-            const int Y = __ldg(yp + (size_t)y * ypitch + x);
-            const int cb = cbp.at(x, y) - 128, cr = crp.at(x, y) - 128;
-            uint8_t* px = o + ((size_t)y * W + x) * 3;
-            px[0] = clamp_u8(Y + ((91881 * cr + 32768) >> 16));
-            px[1] = clamp_u8(Y + ((-22554 * cb - 46802 * cr + 32768) >> 16));
-            px[2] = clamp_u8(Y + ((116130 * cb + 32768) >> 16));
+    const int dw = (W + hs - 1) / hs, dh = (H + vs - 1) / vs;
+    if (hs == 2 && vs == 2 && dw > 2) {
+        // chroma tile: rows cy0-1 .. cy0+8, columns cx0-4 .. cx0+131 as aligned words; s_c column = chroma column - cx0 + 4
+        const int cx0 = (int)tx * (int)(kColorTileW / 2), cy0 = (int)ty * 8;
+        constexpr int kWords = kCTileCols / 4;
+        for (int i = threadIdx.x; i < 2 * 10 * kWords; i += kColorThreads) {
+            const int comp = i / (10 * kWords), rem = i - comp * (10 * kWords);
+            const int r = rem / kWords, wi = rem - r * kWords;
+            const int gy = min(max(cy0 + r - 1, 0), dh - 1);
+            const uint32_t cpitch = d.plane_pitch[1 + comp];
+            const int gw = min(max(cx0 / 4 - 1 + wi, 0), (int)(cpitch / 4) - 1);
+            reinterpret_cast<uint32_t*>(s_c[comp][r])[wi] =
+                __ldg(reinterpret_cast<const uint32_t*>(w.planes + d.plane_off[1 + comp] + (size_t)gy * cpitch) + gw);
+        }
+        __syncthreads();
+        // replicate the plane's first / last real column into the halo positions
+        if (threadIdx.x < 20) {
+            const int comp = threadIdx.x / 10, r = threadIdx.x - comp * 10;
+            if (cx0 == 0) s_c[comp][r][3] = s_c[comp][r][4];
+            const int last = dw - 1 - cx0;  // tile-local index of the last real column
+            if (last >= 0 && last < (int)(kColorTileW / 2)) s_c[comp][r][4 + last + 1] = s_c[comp][r][4 + last];
+        }
+        __syncthreads();
+        if (x >= W) return;
+        const int cl = lane * 4 + 4;  // s_c column of this thread's first chroma sample (a word boundary)
+        const int npx = min(8, W - x);
+        uint2 yv2[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int y = min(y_base + rowi + 8 * half, H - 1);
+            yv2[half] = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int yl = rowi + 8 * half, y = y_base + yl;
+            if (y >= H) break;
+            const int cy = (yl >> 1) + 1, far = (yl & 1) ? cy + 1 : cy - 1;
+            int32_t cbv[8], crv[8];
+#pragma unroll
+            for (int comp = 0; comp < 2; ++comp) {
+                const uint32_t* nr = reinterpret_cast<const uint32_t*>(&s_c[comp][cy][cl]);
+                const uint32_t* fr = reinterpret_cast<const uint32_t*>(&s_c[comp][far][cl]);
+                const uint32_t Ln = nr[-1], Mn = nr[0], Nn = nr[1], Lf = fr[-1], Mf = fr[0], Nf = fr[1];
+                // interleaved pairs of columns: bytes (near a, far a, near b, far b)
+                const uint32_t I0 = __byte_perm(Mn, Mf, 0x5140), J = __byte_perm(Mn, Mf, 0x6251), I1 = __byte_perm(Mn, Mf, 0x7362);
+                const uint32_t Lp = __byte_perm(__byte_perm(Ln, Lf, 0x0073), I0, 0x5410);  // (c-1, c)
+                const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
+                constexpr uint32_t kEven = 0x03090103u, kOdd = 0x01030309u;  // weights per byte: even pixel / odd pixel
+                int32_t* dst = comp ? crv : cbv;
+                dst[0] = (int32_t)(dp4a_u(Lp, kEven, 8) >> 4); dst[1] = (int32_t)(dp4a_u(I0, kOdd, 7) >> 4);
+                dst[2] = (int32_t)(dp4a_u(I0, kEven, 8) >> 4); dst[3] = (int32_t)(dp4a_u(J, kOdd, 7) >> 4);
+                dst[4] = (int32_t)(dp4a_u(J, kEven, 8) >> 4);  dst[5] = (int32_t)(dp4a_u(I1, kOdd, 7) >> 4);
+                dst[6] = (int32_t)(dp4a_u(I1, kEven, 8) >> 4); dst[7] = (int32_t)(dp4a_u(Rp, kOdd, 7) >> 4);
+            }
+            uint32_t px[6];
+            ycc_to_rgb8(yv2[half].x, yv2[half].y, cbv, crv, px);
+            store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
+        }
+        return;
+    }
+    if (x >= W) return;
+    const int npx = min(8, W - x);
+    if (hs == 1 && vs == 1) {
+        const int y = y_base + rowi;
+        if (y >= H) return;
+        const uint2 b = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[1] + (size_t)y * d.plane_pitch[1] + x));
+        const uint2 r = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[2] + (size_t)y * d.plane_pitch[2] + x));
+        int32_t cbv[8], crv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            cbv[i] = (int32_t)(((i < 4 ? b.x : b.y) >> (8 * (i & 3))) & 255u);
+            crv[i] = (int32_t)(((i < 4 ? r.x : r.y) >> (8 * (i & 3))) & 255u);
+        }
+        const uint2 yv = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
+        uint32_t px[6];
+        ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
+        store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
+        return;
+    }
+    // remaining samplings (4:2:2, 4:4:0, chroma planes at most two samples wide): one pixel at a time
+    const ChromaPlane cbp{w.planes + d.plane_off[1], d.plane_pitch[1], dw, dh, hs, vs};
+    const ChromaPlane crp{w.planes + d.plane_off[2], d.plane_pitch[2], dw, dh, hs, vs};
+#pragma unroll 1
+    for (int half = 0; half < vs; ++half) {
+        const int y = y_base + rowi + 8 * half;
+        if (y >= H) break;
+#pragma unroll 1
+        for (int i = 0; i < npx; ++i) {
+            const int Y = __ldg(yp + (size_t)y * ypitch + x + i);
+            const int cb = cbp.at(x + i, y) - 128, cr = crp.at(x + i, y) - 128;
+            uint8_t* o = out + ((size_t)y * W + x + i) * 3;
+            o[0] = (uint8_t)min(max(Y + ((91881 * cr + 32768) >> 16), 0), 255);
+            o[1] = (uint8_t)min(max(Y + ((-22554 * cb - 46802 * cr + 32768) >> 16), 0), 255);
+            o[2] = (uint8_t)min(max(Y + ((116130 * cb + 32768) >> 16), 0), 255);
         }
     }
 }
 
-void launch_color(const JpegWave& w, cudaStream_t s) {
-    if (w.color_tiles.total) k_color<<<w.color_tiles.total, kColorThreads, 0, s>>>(w);
+void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s) {
+    if (count) k_color<<<count, kColorThreads, 0, s>>>(w, first_tile);
 }
 
 }  // namespace dg
