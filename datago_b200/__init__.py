@@ -108,6 +108,7 @@ def lib():
         "dg_batch_result": (C.c_int, [vp, C.c_int, C.POINTER(Result)]),
         "dg_batch_stage_ms": (C.c_int, [vp, C.POINTER(C.c_float)]),
         "dg_batch_counters": (C.c_int, [vp, u64p, u64p, u32p]),
+        "dg_batch_huffman_stats": (C.c_int, [vp, u64p]),
         "dg_batch_debug": (C.c_int, [vp, C.c_int, C.POINTER(vp), u64p, C.POINTER(vp)]),
         "dg_batch_destroy": (None, [vp]),
         "dg_process": (C.c_int, [vp, C.POINTER(Item), C.c_int, C.c_uint32, C.POINTER(vp), C.POINTER(Result)]),
@@ -124,7 +125,7 @@ def lib():
 EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
            "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
-           "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_debug dg_batch_destroy dg_process "
+           "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_huffman_stats dg_batch_debug dg_batch_destroy dg_process "
            "dg_copy_to_host").split()
 
 
@@ -332,6 +333,11 @@ class Batch:
         h2d, d2h, k = C.c_uint64(), C.c_uint64(), C.c_uint32()
         _check(lib().dg_batch_counters(self._h, C.byref(h2d), C.byref(d2h), C.byref(k)))
         return dict(h2d_bytes=int(h2d.value), d2h_bytes=int(d2h.value), kernel_launches=int(k.value))
+
+    def huffman_stats(self):
+        out = (C.c_uint64 * 3)()
+        _check(lib().dg_batch_huffman_stats(self._h, out))
+        return dict(chunks=int(out[0]), rounds=int(out[1]), subsequence_decodes=int(out[2]))
 
     def debug_coefficients(self, i):
         """int16 [blocks, 64] coefficients of JPEG item i in scan order (single-wave batches, after sync)."""

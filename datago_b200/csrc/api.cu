@@ -651,8 +651,8 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     if (rc) return abandon(b, rc);
     b->d_scratch = (uint8_t*)ctx->dev.blocks[b->blk_scratch].ptr;
 
-    b->off_status = 0;
-    b->off_blob = align_up((size_t)n * 4, 256);
+    b->off_status = 0;  // n status words, then 4 counters of the speculative Huffman kernel
+    b->off_blob = align_up((size_t)n * 4 + 32, 256);
     b->off_rawin = b->off_blob + align_up(blob, 256);
     b->off_out = b->off_rawin + align_up(rawin, 256);
     const size_t fixed_bytes = b->off_out + align_up(outb, 256);
@@ -813,7 +813,7 @@ extern "C" int dg_batch_run(dg_batch* b) {
         return cudaEventRecord(b->events[ev++].b, s);
     };
     b->launches = 0;
-    if (b->ran) CU(cudaMemsetAsync(b->d_persist + b->off_status, 0, (size_t)b->n * 4, s));  // status words of the previous run
+    if (b->ran) CU(cudaMemsetAsync(b->d_persist + b->off_status, 0, align_up((size_t)b->n * 4, 8) + 32, s));  // status words of the previous run
     for (WavePlan& wv : b->waves) {
         uint8_t* sc = b->d_scratch;
         if (!wv.descs.empty()) {
@@ -830,6 +830,7 @@ extern "C" int dg_batch_run(dg_batch* b) {
             w.planes = sc + wv.off_planes;
             w.out = transform ? sc + wv.off_decoded : b->d_persist + b->off_out;
             w.status = (uint32_t*)(b->d_persist + b->off_status);
+            w.spec_stats = (unsigned long long*)(b->d_persist + b->off_status + align_up((size_t)b->n * 4, 8));
             w.huff = (const HuffTable*)(meta + b->m_huff);
             w.qt32 = (const uint32_t*)(meta + b->m_qt);
             w.spec_list = (const uint32_t*)(meta + wv.m_spec);
@@ -966,6 +967,16 @@ extern "C" int dg_batch_counters(const dg_batch* b, uint64_t* h2d, uint64_t* d2h
     if (h2d) *h2d = b->h2d;
     if (d2h) *d2h = b->d2h;
     if (launches) *launches = b->launches;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_huffman_stats(dg_batch* b, uint64_t out[3]) {
+    if (!b || !out) return fail(DG_E_INVALID, "NULL argument");
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    CU(cudaMemcpyAsync(out, b->d_persist + b->off_status + align_up((size_t)b->n * 4, 8), 24, cudaMemcpyDeviceToHost, ctx->stream));
+    CU(cudaStreamSynchronize(ctx->stream));
     return DG_OK;
 }
 

@@ -26,6 +26,7 @@ struct JpegWave {
     uint8_t* planes;         // component planes after the IDCT
     uint8_t* out;            // decoded images
     uint32_t* status;        // [items of the batch]
+    unsigned long long* spec_stats;  // [0] chunks, [1] synchronisation rounds, [2] subsequence decodes (all passes)
     const HuffTable* huff;   // table pool
     const uint32_t* qt32;    // quantisation pool, 32 words per table: word i holds q[2i] in byte 0 and q[2i+1] in byte 3
     // speculative (no restart marker) images and restart-interval images of this wave

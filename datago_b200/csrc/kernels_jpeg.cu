@@ -314,7 +314,10 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
         uint32_t n = 0;
         int32_t a = 0, b = 0, c = 0;
         bool redo = active;
+        uint32_t rounds = 0, decodes = 0;
         for (int round = 0; round <= kSpecThreads + 1; ++round) {
+            ++rounds;
+            decodes += __syncthreads_count(redo);
             if (redo) {
                 uint32_t p = entry_p, sm = entry_sm, dummy = 0;
                 n = 0; a = 0; b = 0; c = 0;
@@ -361,6 +364,9 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
         }
         __syncthreads();
         if (tid == 0) {
+            atomicAdd(w.spec_stats, 1ull);
+            atomicAdd(w.spec_stats + 1, (unsigned long long)rounds);
+            atomicAdd(w.spec_stats + 2, (unsigned long long)decodes + min((uint32_t)kSpecThreads, nsub - chunk));
             const uint32_t last = min((uint32_t)kSpecThreads, nsub - chunk) - 1;
             s_carry_p = s_exit_p[last];
             s_carry_slot += tot.n;

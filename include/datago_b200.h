@@ -162,6 +162,9 @@ DG_API int dg_batch_result(const dg_batch* b, int i, dg_result* out);
 DG_API int dg_batch_stage_ms(const dg_batch* b, float ms[DG_STAGE_COUNT]);
 /* Bytes copied host->device by upload, and kernels launched by one run. */
 DG_API int dg_batch_counters(const dg_batch* b, uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint32_t* kernel_launches);
+/* Counters of the speculative entropy decoder over the last run: chunks of subsequences processed, synchronisation
+ * rounds, subsequence decodes (guess + re-decodes + write pass).  Synchronises the stream. */
+DG_API int dg_batch_huffman_stats(dg_batch* b, uint64_t out[3]);
 /* Intermediate device buffers, for stage-by-stage parity tests: coefficient words (int16, scan order) and, for
  * decode+resize batches, the full-size decoded image of item i. */
 DG_API int dg_batch_debug(const dg_batch* b, int i, const int16_t** coef, uint64_t* nblocks, const uint8_t** decoded);
