@@ -113,6 +113,7 @@ def lib():
         "dg_batch_destroy": (None, [vp]),
         "dg_process": (C.c_int, [vp, C.POINTER(Item), C.c_int, C.c_uint32, C.POINTER(vp), C.POINTER(Result)]),
         "dg_copy_to_host": (C.c_int, [vp, vp, vp, C.c_uint64]),
+        "dg_resize_device_static": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, vp, C.POINTER(Plan)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -126,7 +127,7 @@ EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ct
            "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
            "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_huffman_stats dg_batch_debug dg_batch_destroy dg_process "
-           "dg_copy_to_host").split()
+           "dg_copy_to_host dg_resize_device_static").split()
 
 
 def _check(rc):
@@ -234,6 +235,15 @@ class Context:
             b.sync()
             res = [b.result(i) for i in range(len(b))]
         return [(r.status, o if r.status == 0 else None, r) for r, o in zip(res, outs)]
+
+    def resize_device_static(self, src_ptr, w, h, channels, dst_ptr, forced_key=None):
+        """crop_and_resize of one device-resident image using only the library's built-in scratch array: for hosts
+        that must not allocate device memory while running.  src_ptr / dst_ptr are device addresses owned by the
+        caller (dst sized from plan_geometry).  Returns the plan.  Raises too_large beyond the 32 MiB scratch."""
+        p = Plan()
+        _check(lib().dg_resize_device_static(self._h, C.c_void_p(src_ptr), w, h, channels,
+                                             forced_key.encode() if forced_key else None, C.c_void_p(dst_ptr), C.byref(p)))
+        return p
 
     def copy_to_host(self, device_ptr, nbytes):
         out = np.empty(nbytes, np.uint8)

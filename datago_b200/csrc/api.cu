@@ -1029,3 +1029,124 @@ extern "C" int dg_copy_to_host(dg_ctx* ctx, void* dst, const void* src, uint64_t
     CU(cudaStreamSynchronize(ctx->stream));
     return DG_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free crop_and_resize of one device-resident image.
+//
+// Some hosts cannot let a library allocate device memory once they are running: a training process whose framework
+// allocator has already reserved all of HBM (a cudaMalloc would fail, or force that allocator to give its cache
+// back), a latency-critical loop that cannot take the device-wide synchronisation an allocation may imply, or a
+// service with a "no allocation after start-up" rule.  For them this entry point does the same work as a one-image
+// batch -- same planner, same convolution kernels -- but takes everything it needs beyond the caller's input and
+// output buffers (pass descriptors, filter tables, the intermediate images between passes) from one fixed array that
+// is part of the library image.  Every GPU that loads the library holds those kStaticScratchBytes until the
+// process exits.
+// ---------------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a kernel can use; the device
+// address is looked up once per device, with that device current.
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_ptr[kMaxDevices] = {nullptr};
+
+int static_scratch_for(int device, unsigned char** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(DG_E_INVALID, "device ordinal %d not supported here", device);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) return fail(DG_E_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+        g_static_ptr[device] = (unsigned char*)p;
+    }
+    *out = g_static_ptr[device];
+    return DG_OK;
+}
+
+}  // namespace
+
+extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, uint32_t w, uint32_t h, uint32_t channels,
+                                       const char* forced_key, uint8_t* device_dst, dg_plan* plan_out) {
+    if (!ctx || !device_src || !device_dst || w == 0 || h == 0 || (channels != 1 && channels != 3))
+        return fail(DG_E_INVALID, "NULL argument, empty image, or channels not 1 / 3");
+    if (ctx->device == DG_DEVICE_NONE) return fail(DG_E_INVALID, "planning-only context: pixel work needs a CUDA device");
+    if (!ctx->has_tfm) return fail(DG_E_NO_TRANSFORM, "ctx has no crop_and_resize transform");
+    dg_plan plan;
+    int rc = plan_geometry(ctx->tfm, w, h, channels, forced_key, &plan);
+    if (rc) return fail(rc, "aspect ratio key '%s' is not in the bucket table", forced_key ? forced_key : "");
+    if (plan_out) *plan_out = plan;
+
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    unsigned char* scratch = nullptr;
+    rc = static_scratch_for(ctx->device, &scratch);  // first call on a device: symbol look-up
+    if (rc) return rc;
+
+    // intermediates go to the top part of the array, metadata to the bottom part
+    const size_t mid_bound = align_up(resize_mid_bound(plan, channels), 256);
+    if (mid_bound + 65536 > kStaticScratchBytes)
+        return fail(DG_E_TOO_LARGE, "image needs %zu bytes of intermediates; the static scratch holds %zu in total", mid_bound, kStaticScratchBytes);
+    unsigned char* mid_base = scratch + (kStaticScratchBytes - mid_bound);
+    const size_t meta_cap = kStaticScratchBytes - mid_bound;
+
+    Planner pl{ctx, nullptr};
+    WavePlan wv;
+    size_t mid_used = 0;
+    plan_resize(pl, wv, plan, channels, device_src, device_dst, mid_base, &mid_used);
+    if (mid_used > mid_bound) return fail(DG_E_TOO_LARGE, "internal: intermediates exceed their bound");
+    Meta m;
+    const size_t m_tables = m.put(pl.table_words, 16);
+    size_t m_passes[4];
+    OwnerMapOff m_pass[4], m_copy;
+    for (int s = 0; s < 4; ++s) {
+        uint32_t t = 0;
+        wv.pass_first[s].push_back(0);
+        for (ConvPass& cp : wv.passes[s]) {
+            cp.tile_first = t;
+            t += (s & 1) ? conv_v_tiles(cp.out_w * cp.channels, cp.out_h) : conv_h_tiles(cp.out_w, cp.out_h);
+            wv.pass_first[s].push_back(t);
+        }
+        m_passes[s] = m.put(wv.passes[s], 16);
+        m_pass[s] = put_owner_map(m, wv.pass_first[s]);
+    }
+    {
+        uint32_t t = 0;
+        wv.copy_first.push_back(0);
+        for (CopyJob& j : wv.copies) {
+            j.tile_first = t;
+            t += (uint32_t)(((uint64_t)j.row_bytes * j.rows + kCopyTileBytes - 1) / kCopyTileBytes);
+            wv.copy_first.push_back(t);
+        }
+    }
+    const size_t m_copies = m.put(wv.copies, 16);
+    m_copy = put_owner_map(m, wv.copy_first);
+    if (m.bytes.size() > meta_cap)
+        return fail(DG_E_TOO_LARGE, "filter tables (%zu bytes) and intermediates (%zu bytes) exceed the %zu-byte static scratch",
+                    m.bytes.size(), mid_bound, kStaticScratchBytes);
+
+    cudaStream_t s = ctx->stream;
+    // nothing in the array has to start at zero: the metadata is overwritten here and every intermediate pixel is
+    // written by a pass before the next pass reads it
+    CU(cudaMemcpyAsync(scratch, m.bytes.data(), m.bytes.size(), cudaMemcpyHostToDevice, s));
+    auto map_at = [&](const OwnerMapOff& o) {
+        OwnerMap r;
+        r.first = (const uint32_t*)(scratch + o.first);
+        r.coarse = (const uint32_t*)(scratch + o.coarse);
+        r.n = o.n; r.shift = o.shift; r.total = o.total;
+        return r;
+    };
+    const uint32_t* tables = (const uint32_t*)(scratch + m_tables);
+    for (int st = 0; st < 4; ++st) {
+        if (wv.passes[st].empty()) continue;
+        const ConvPass* passes = (const ConvPass*)(scratch + m_passes[st]);
+        if (st & 1) launch_conv_v(passes, map_at(m_pass[st]), tables, s);
+        else launch_conv_h(passes, map_at(m_pass[st]), tables, s);
+    }
+    if (!wv.copies.empty()) launch_copy((const CopyJob*)(scratch + m_copies), map_at(m_copy), s);
+    CU(cudaGetLastError());
+    CU(cudaStreamSynchronize(s));  // the host-side metadata image dies with this frame
+    return DG_OK;
+}

@@ -174,6 +174,23 @@ DG_API void dg_batch_destroy(dg_batch* b);
  * (device_data is NULL there: the batch is gone). */
 DG_API int dg_process(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, uint8_t* const* host_out, dg_result* results);
 
+/* crop_and_resize of ONE image that is already in device memory, without any device allocation.
+ * No counterpart in datago: it exists for hosts that must not let a library allocate device memory while they run
+ * (a training process whose framework allocator owns all of HBM, a loop that cannot afford the device-wide
+ * synchronisation an allocation can imply, a service with a no-allocation-after-start-up rule).
+ * device_src: w * h * channels interleaved 8-bit pixels; device_dst: room for the bucket's target_w * target_h *
+ * channels bytes (learn the size first with dg_plan_geometry).  Descriptors, filter tables and the images between
+ * passes live in one 32 MiB array inside the library image, held by every GPU that loads the library until exit.
+ * Limit: intermediates + tables must fit those 32 MiB; the intermediates are bounded by
+ * new_w * channels * (max(src_h, new_h) + 2 * new_h) bytes (new_w, new_h from dg_plan_geometry), e.g. a 4096 x 4096
+ * RGB source into a 1024-class bucket needs about 19 MiB.  Larger inputs get DG_E_TOO_LARGE and nothing is launched.
+ * The first call on a device looks up the array's device address; make that call before any stream capture.
+ * All calls share the array and it keeps whatever the last call left (nothing in it needs clearing: every byte is
+ * written before it is read), so two calls that overlap on the same GPU -- two contexts, two streams -- race; calls
+ * on one ctx are serialised and the function returns after its work has completed. */
+DG_API int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, uint32_t w, uint32_t h, uint32_t channels,
+                            const char* forced_key, uint8_t* device_dst, dg_plan* plan_out);
+
 /* Device -> host copy helper for callers without a CUDA binding (tests). */
 DG_API int dg_copy_to_host(dg_ctx* ctx, void* dst, const void* device_src, uint64_t nbytes);
 
