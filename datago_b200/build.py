@@ -25,6 +25,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-Xcompiler", "-fPIC,-fvisibility=hidden,-O3", "-o", OUT]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("DATAGO_B200_NVCC_FLAGS", "").split()
     cmd += [os.path.join(CSRC, f) for f in SOURCES]
     subprocess.run(cmd, check=True)
     return OUT

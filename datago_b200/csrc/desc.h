@@ -6,9 +6,20 @@ namespace dg {
 
 constexpr int kLutBits = 9;  // Huffman fast-lookup width
 
+// A decoded Huffman symbol as the entropy decoder wants it: code length, the number of extra bits s (low nibble of
+// the symbol), the zero run r (high nibble; 0 for DC categories) and the total bits consumed.
+//   bits 0-5: length + s   bits 6-10: length   bits 11-14: s   bits 15-18: r
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+constexpr uint32_t huff_pack(uint32_t len, uint32_t sym) {
+    return (len + (sym & 15u)) | (len << 6) | ((sym & 15u) << 11) | ((sym >> 4) << 15);
+}
+
 // One Huffman table (DC or AC) prepared for the device (T.81 Annex C code assignment).
 struct HuffTable {
-    uint16_t lut[1 << kLutBits];  // next 9 bits -> (length << 8) | symbol; 0 = longer code
+    // next 9 bits -> packed symbol (see huff_pack), 0 = the code is longer than 9 bits
+    uint32_t lut[1 << kLutBits];
     int32_t maxcode[18];          // [l], l = 1..16: largest code of length l, -1 if none; [17] = INT_MAX
     int32_t valoff[17];           // [l]: index of the first symbol of length l minus its first code
     uint8_t vals[256];

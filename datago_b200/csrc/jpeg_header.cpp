@@ -161,7 +161,7 @@ bool build_huff_table(const JpegHeader::RawHuff& raw, HuffTable& out) {
             for (int j = 0; j < raw.bits[l]; ++j, ++k, ++code) {
                 if (l <= kLutBits) {
                     const int span = 1 << (kLutBits - l);
-                    for (int f = 0; f < span; ++f) out.lut[(code << (kLutBits - l)) | f] = (uint16_t)((l << 8) | raw.vals[k]);
+                    for (int f = 0; f < span; ++f) out.lut[(code << (kLutBits - l)) | f] = huff_pack((uint32_t)l, raw.vals[k]);
                 }
             }
             out.maxcode[l] = code - 1;

@@ -131,104 +131,86 @@ void launch_unstuff(const JpegWave& w, cudaStream_t s) {
 //    pass writes the coefficients.  One CTA walks one image in chunks of kSpecThreads subsequences, carrying
 //    the exact state across chunks, so no CTA ever waits on another.
 // ---------------------------------------------------------------------------------------------------------------
-struct BitReader {
-    const uint32_t* words;
-    uint32_t nwords;
-    uint64_t buf;
-    int avail;
-    uint32_t wi;
-    __device__ __forceinline__ uint32_t load(uint32_t i) const { return i < nwords ? __byte_perm(__ldg(words + i), 0, 0x0123) : 0u; }
-    __device__ __forceinline__ void seek(uint32_t bitpos) {
-        wi = bitpos >> 5;
-        const int sh = bitpos & 31;
-        buf = (((uint64_t)load(wi) << 32) | load(wi + 1)) << sh;
-        avail = 64 - sh;
-        wi += 2;
-    }
-    __device__ __forceinline__ void refill() {
-        if (avail <= 32) { buf |= (uint64_t)load(wi++) << (32 - avail); avail += 32; }
-    }
-    __device__ __forceinline__ uint32_t peek() const { return (uint32_t)(buf >> 32); }
-    __device__ __forceinline__ void skip(uint32_t n) { buf <<= n; avail -= (int)n; }
-};
-
 struct HuffCtx {
-    const HuffTable* dc0; const HuffTable* dc1; const HuffTable* dc2;
-    const HuffTable* ac0; const HuffTable* ac1; const HuffTable* ac2;
+    const char* base;  // tables are addressed as base + byte offset (shared memory or the global pool)
+    uint32_t dc_off0, dc_off1, dc_off2, ac_off0, ac_off1, ac_off2;
     uint32_t luma_blocks;  // blocks of component 0 per MCU
     uint32_t mcu_slots;    // 64 * blocks per MCU
 };
 
-// Decodes symbols that start in [p, end_bit) while fewer than max_slots slots have been consumed.
-// dc0..2: sums of DC differences (WRITE == false) or running DC predictors (WRITE == true).
+__device__ __forceinline__ uint32_t shr_clamp(uint32_t x, uint32_t n) {  // shift counts >= 32 give 0
+    uint32_t r;
+    asm("shr.b32 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(n));
+    return r;
+}
+
+// codes longer than the fast table: canonical search over the remaining lengths
 template <bool WRITE>
-__device__ __forceinline__ void decode_span(BitReader& br, uint32_t& p, const uint32_t end_bit, const uint32_t total_bits,
-                                            uint32_t& slotmod, uint32_t& nslots, const uint32_t max_slots, int32_t& dc0,
-                                            int32_t& dc1, int32_t& dc2, const HuffCtx& hc, int16_t* __restrict__ coef,
-                                            const uint32_t slot_abs, uint32_t& err) {
+__device__ __noinline__ uint32_t huff_long_code(const HuffTable* t, uint32_t top, uint32_t& err) {
+    uint32_t len = kLutBits + 1;
+    while (len <= 16 && (int32_t)(top >> (32 - len)) > t->maxcode[len]) ++len;
+    if (len > 16) { if (WRITE) err |= kStBadCode; return huff_pack(16, 0); }
+    return huff_pack(len, t->vals[(int32_t)(top >> (32 - len)) + t->valoff[len]]);
+}
+
+// Decodes the symbols that start in [p, end_bit) while fewer than max_slots slots have been consumed.
+// dc0..2: sums of DC differences (WRITE == false) or running DC predictors (WRITE == true).
+// One code path for DC and AC symbols (selects instead of branches): the lanes of a warp are at unrelated places of
+// their streams, so every branch taken by one lane is paid by all of them.
+template <bool WRITE>
+__device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, const uint32_t nwords, uint32_t& p,
+                                            const uint32_t end_bit, const uint32_t total_bits, uint32_t& slotmod,
+                                            uint32_t& nslots, const uint32_t max_slots, int32_t& dc0, int32_t& dc1,
+                                            int32_t& dc2, const HuffCtx& hc, int16_t* __restrict__ coef,
+                                            const uint32_t slot_abs, const uint8_t* __restrict__ natural, uint32_t& err) {
+    auto word = [&](uint32_t i) -> uint32_t { return i < nwords ? __byte_perm(__ldg(words + i), 0, 0x0123) : 0u; };
+    uint32_t wi = p >> 5;
+    uint32_t w0 = word(wi), w1 = word(wi + 1);
     while (p < end_bit && nslots < max_slots) {
-        br.refill();
-        const uint32_t top = br.peek();
+        const uint32_t top = __funnelshift_l(w1, w0, p & 31u);
         const uint32_t z = slotmod & 63u, c = slotmod >> 6;
-        const int comp = c < hc.luma_blocks ? 0 : (int)(c - hc.luma_blocks) + 1;
-        const HuffTable* t = z == 0 ? (comp == 0 ? hc.dc0 : comp == 1 ? hc.dc1 : hc.dc2)
-                                    : (comp == 0 ? hc.ac0 : comp == 1 ? hc.ac1 : hc.ac2);
-        const uint32_t e = t->lut[top >> (32 - kLutBits)];
-        uint32_t len, sym;
-        if (e) {
-            len = e >> 8; sym = e & 255u;
-        } else {
-            len = kLutBits + 1;
-            while (len <= 16 && (int32_t)(top >> (32 - len)) > t->maxcode[len]) ++len;
-            if (len > 16) { len = 16; sym = 0; if (WRITE) err |= kStBadCode; }
-            else sym = t->vals[(int32_t)(top >> (32 - len)) + t->valoff[len]];
-        }
-        const uint32_t s = sym & 15u, used = len + s;
+        const bool isdc = z == 0;
+        const uint32_t comp = c < hc.luma_blocks ? 0u : c - hc.luma_blocks + 1u;
+        const uint32_t toff = isdc ? (comp == 0 ? hc.dc_off0 : comp == 1 ? hc.dc_off1 : hc.dc_off2)
+                                   : (comp == 0 ? hc.ac_off0 : comp == 1 ? hc.ac_off1 : hc.ac_off2);
+        const HuffTable* t = reinterpret_cast<const HuffTable*>(hc.base + toff);
+        uint32_t e = t->lut[top >> (32 - kLutBits)];
+        if (e == 0) e = huff_long_code<WRITE>(t, top, err);
+        const uint32_t used = e & 63u, len = (e >> 6) & 31u, s = (e >> 11) & 15u, r = (e >> 15) & 15u;
         if (p + used > total_bits) { p = total_bits; break; }  // the stream ends inside this symbol
-        int32_t v = 0;
-        if (s) {
-            const uint32_t raw = (top << len) >> (32 - s);
-            v = raw < (1u << (s - 1)) ? (int32_t)raw - (int32_t)(1u << s) + 1 : (int32_t)raw;
-        }
-        uint32_t adv;
-        if (z == 0) {
-            int32_t now;
-            if (comp == 0) now = (dc0 += v); else if (comp == 1) now = (dc1 += v); else now = (dc2 += v);
-            if (WRITE) coef[(size_t)(slot_abs + nslots)] = (int16_t)now;  // slot of a DC code is 64 * block
-            adv = 1;
-        } else {
-            const uint32_t r = sym >> 4;
-            if (s == 0) {
-                adv = (r == 15u && z + 16u <= 64u) ? 16u : 64u - z;  // ZRL, or end of block
-            } else {
+        const uint32_t raw = shr_clamp(top << len, 32u - s);   // the s extra bits (0 when s == 0)
+        const int32_t v = (int32_t)raw - (int32_t)((shr_clamp(raw, s - 1u) ^ 1u) * ((1u << s) - 1u));  // T.81 EXTEND
+        uint32_t adv = (s != 0u || r == 15u) ? r + 1u : 64u;   // coefficient after a run, ZRL, or end of block
+        adv = isdc ? 1u : min(adv, 64u - z);
+        const int32_t dv = isdc ? v : 0;
+        dc0 += comp == 0 ? dv : 0;
+        dc1 += comp == 1 ? dv : 0;
+        dc2 += comp == 2 ? dv : 0;
+        if (WRITE) {
+            if (isdc) {
+                coef[(size_t)(slot_abs + nslots)] = (int16_t)(comp == 0 ? dc0 : comp == 1 ? dc1 : dc2);  // slot of a DC code = 64 * block
+            } else if (s != 0u) {
                 const uint32_t zz = z + r;
-                if (zz > 63u) { adv = 64u - z; if (WRITE) err |= kStCoefRange; }
-                else {
-                    if (WRITE) coef[(size_t)(slot_abs + nslots - z) + kNatural[zz]] = (int16_t)v;
-                    adv = r + 1u;
-                }
+                if (zz <= 63u) coef[(size_t)(slot_abs + nslots - z) + natural[zz]] = (int16_t)v;
+                else err |= kStCoefRange;
             }
         }
-        br.skip(used);
         p += used;
         nslots += adv;
         slotmod += adv;
         if (slotmod >= hc.mcu_slots) slotmod -= hc.mcu_slots;
+        const uint32_t nwi = p >> 5;
+        if (nwi != wi) { w0 = w1; w1 = word(nwi + 1); wi = nwi; }
     }
-}
-
-__device__ __forceinline__ void load_ctx(HuffCtx& hc, const JpegDesc& d, const HuffTable* pool) {
-    hc.dc0 = pool + d.dc_tab[0]; hc.ac0 = pool + d.ac_tab[0];
-    hc.dc1 = pool + d.dc_tab[1]; hc.ac1 = pool + d.ac_tab[1];
-    hc.dc2 = pool + d.dc_tab[2]; hc.ac2 = pool + d.ac_tab[2];
-    hc.luma_blocks = d.hs * d.vs;
-    hc.mcu_slots = d.bpm * 64u;
 }
 
 // ---- restart-interval images: one thread per segment -----------------------------------------------------------
 constexpr int kRestartThreads = 128;
 
 __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
+    __shared__ uint8_t s_nat[64];
+    if (threadIdx.x < 64) s_nat[threadIdx.x] = kNatural[threadIdx.x];
+    __syncthreads();
     const uint32_t g = blockIdx.x * kRestartThreads + threadIdx.x;
     if (g >= w.restart_segs.total) return;
     const uint32_t r = owner_of(w.restart_segs, g);
@@ -244,40 +226,59 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
     const uint32_t mcus = d.mcux * d.mcuy;
     const uint32_t m0 = k * d.restart, m1 = min(m0 + d.restart, mcus);
     HuffCtx hc;
-    load_ctx(hc, d, w.huff);
-    BitReader br;
-    br.words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
-    br.nwords = (us_len + 3) / 4 + 2;
+    hc.base = reinterpret_cast<const char*>(w.huff);
+    hc.dc_off0 = d.dc_tab[0] * (uint32_t)sizeof(HuffTable); hc.ac_off0 = d.ac_tab[0] * (uint32_t)sizeof(HuffTable);
+    hc.dc_off1 = d.dc_tab[1] * (uint32_t)sizeof(HuffTable); hc.ac_off1 = d.ac_tab[1] * (uint32_t)sizeof(HuffTable);
+    hc.dc_off2 = d.dc_tab[2] * (uint32_t)sizeof(HuffTable); hc.ac_off2 = d.ac_tab[2] * (uint32_t)sizeof(HuffTable);
+    hc.luma_blocks = d.hs * d.vs;
+    hc.mcu_slots = d.bpm * 64u;
     uint32_t p = b0 * 8u, slotmod = 0, nslots = 0, err = 0;
     int32_t dc0 = 0, dc1 = 0, dc2 = 0;
-    br.seek(p);
     const uint32_t want = (m1 - m0) * hc.mcu_slots;
-    decode_span<true>(br, p, b1 * 8u, b1 * 8u, slotmod, nslots, want, dc0, dc1, dc2, hc, w.coef + d.block_off * 64,
-                      m0 * hc.mcu_slots, err);
+    decode_span<true>(reinterpret_cast<const uint32_t*>(w.us + d.us_off), (us_len + 3) / 4 + 2, p, b1 * 8u, b1 * 8u, slotmod,
+                      nslots, want, dc0, dc1, dc2, hc, w.coef + d.block_off * 64, m0 * hc.mcu_slots, s_nat, err);
     if (nslots < want) err |= kStTruncated;
     if (err) atomicOr(w.status + d.item, err);
 }
 
 // ---- images without restart markers: speculative subsequences, one CTA per image ---------------------------------
-constexpr int kSpecThreads = 512;
-constexpr uint32_t kSubseqBits = 1024;
+#ifndef DG_SPEC_THREADS
+#define DG_SPEC_THREADS 256
+#endif
+#ifndef DG_SUBSEQ_BITS
+#define DG_SUBSEQ_BITS 1024
+#endif
+#ifndef DG_SPEC_MIN_CTAS
+#define DG_SPEC_MIN_CTAS 6
+#endif
+constexpr int kSpecThreads = DG_SPEC_THREADS;
+constexpr uint32_t kSubseqBits = DG_SUBSEQ_BITS;
 
 struct Scan4 { uint32_t n; int32_t a, b, c; };
 
-__global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
+// Per-subsequence state of the chunk being synchronised (shared memory).
+struct SpecState {
+    uint32_t entry_p[kSpecThreads], entry_sm[kSpecThreads];  // decoder state at the start of the subsequence
+    uint32_t exit_p[kSpecThreads], exit_sm[kSpecThreads];    // ... after its last symbol
+    uint32_t n[kSpecThreads];                                // slots consumed
+    int32_t dc[3][kSpecThreads];                             // sums of DC differences per component
+    uint32_t list[kSpecThreads];                             // subsequences to re-decode this round
+};
+
+__global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(JpegWave w) {
     const uint32_t img = w.spec_list[blockIdx.x];
     const JpegDesc& d = w.descs[img];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     __shared__ HuffTable s_tab[6];
-    __shared__ uint32_t s_exit_p[kSpecThreads];
-    __shared__ uint32_t s_exit_sm[kSpecThreads];
+    __shared__ uint8_t s_nat[64];
+    __shared__ SpecState st;
     __shared__ Scan4 s_warp[kSpecThreads / 32];
+    __shared__ uint32_t s_wcount[kSpecThreads / 32];
     __shared__ uint32_t s_carry_p, s_carry_slot;
     __shared__ int32_t s_carry_dc[3];
 
-    // stage the image's Huffman tables in shared memory (word copies)
-    {
+    {   // stage the image's Huffman tables in shared memory (word copies)
         const uint32_t ids[6] = {d.dc_tab[0], d.dc_tab[1], d.dc_tab[2], d.ac_tab[0], d.ac_tab[1], d.ac_tab[2]};
         constexpr int kWords = sizeof(HuffTable) / 4;
         for (int t = 0; t < 6; ++t) {
@@ -285,12 +286,14 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
             uint32_t* dst = reinterpret_cast<uint32_t*>(&s_tab[t]);
             for (int i = tid; i < kWords; i += kSpecThreads) dst[i] = __ldg(src + i);
         }
+        if (tid < 64) s_nat[tid] = kNatural[tid];
         if (tid == 0) { s_carry_p = 0; s_carry_slot = 0; s_carry_dc[0] = s_carry_dc[1] = s_carry_dc[2] = 0; }
     }
     __syncthreads();
     HuffCtx hc;
-    hc.dc0 = &s_tab[0]; hc.dc1 = &s_tab[1]; hc.dc2 = &s_tab[2];
-    hc.ac0 = &s_tab[3]; hc.ac1 = &s_tab[4]; hc.ac2 = &s_tab[5];
+    hc.base = reinterpret_cast<const char*>(&s_tab[0]);
+    hc.dc_off0 = 0; hc.dc_off1 = sizeof(HuffTable); hc.dc_off2 = 2 * sizeof(HuffTable);
+    hc.ac_off0 = 3 * sizeof(HuffTable); hc.ac_off1 = 4 * sizeof(HuffTable); hc.ac_off2 = 5 * sizeof(HuffTable);
     hc.luma_blocks = d.hs * d.vs;
     hc.mcu_slots = d.bpm * 64u;
 
@@ -298,45 +301,57 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
     const uint32_t total_bits = us_len * 8u;
     const uint32_t total_slots = d.nblocks * 64u;
     const uint32_t nsub = (total_bits + kSubseqBits - 1) / kSubseqBits;
-    BitReader br;
-    br.words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
-    br.nwords = (us_len + 3) / 4 + 2;
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
+    const uint32_t nwords = (us_len + 3) / 4 + 2;
     int16_t* coef = w.coef + d.block_off * 64;
     uint32_t err = 0;
 
-    for (uint32_t chunk = 0; chunk < nsub; chunk += kSpecThreads) {
-        const uint32_t j = chunk + tid;
-        const bool active = j < nsub;
-        const uint32_t end_bit = min((j + 1) * kSubseqBits, total_bits);
-        // entry state: exact for the first subsequence of the chunk, a guess (AC code of the first block) elsewhere
-        uint32_t entry_p = tid == 0 ? s_carry_p : j * kSubseqBits;
-        uint32_t entry_sm = tid == 0 ? s_carry_slot % hc.mcu_slots : 1u;
-        uint32_t n = 0;
+    // decode subsequence j of the chunk from its recorded entry state and record exit state and sums
+    auto decode_into_state = [&](uint32_t chunk, int j) {
+        uint32_t p = st.entry_p[j], sm = st.entry_sm[j], n = 0, dummy = 0;
         int32_t a = 0, b = 0, c = 0;
-        bool redo = active;
-        uint32_t rounds = 0, decodes = 0;
+        const uint32_t end_bit = min((chunk + j + 1) * kSubseqBits, total_bits);
+        decode_span<false>(words, nwords, p, end_bit, total_bits, sm, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, s_nat, dummy);
+        st.exit_p[j] = p; st.exit_sm[j] = sm; st.n[j] = n;
+        st.dc[0][j] = a; st.dc[1][j] = b; st.dc[2][j] = c;
+    };
+
+    for (uint32_t chunk = 0; chunk < nsub; chunk += kSpecThreads) {
+        const int cnt = (int)min((uint32_t)kSpecThreads, nsub - chunk);
+        const bool active = tid < cnt;
+        // entry state: exact for the first subsequence of the chunk, a guess (AC code of the first block) elsewhere
+        st.entry_p[tid] = tid == 0 ? s_carry_p : (chunk + tid) * kSubseqBits;
+        st.entry_sm[tid] = tid == 0 ? s_carry_slot % hc.mcu_slots : 1u;
+        if (active) decode_into_state(chunk, tid);
+        __syncthreads();
+        uint32_t rounds = 1, decodes = (uint32_t)cnt;
+        // Re-decode every subsequence whose entry state differs from its left neighbour's exit state until none
+        // does.  After round r the first r subsequences are final, so the loop ends within cnt rounds.  The
+        // subsequences to redo are compacted so that a late round with a handful of them occupies one warp.
         for (int round = 0; round <= kSpecThreads + 1; ++round) {
-            ++rounds;
-            decodes += __syncthreads_count(redo);
-            if (redo) {
-                uint32_t p = entry_p, sm = entry_sm, dummy = 0;
-                n = 0; a = 0; b = 0; c = 0;
-                br.seek(p);
-                decode_span<false>(br, p, end_bit, total_bits, sm, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, dummy);
-                s_exit_p[tid] = p;
-                s_exit_sm[tid] = sm;
-            }
-            __syncthreads();
-            redo = false;
+            bool need = false;
             if (active && tid > 0) {
-                const uint32_t pp = s_exit_p[tid - 1], ps = s_exit_sm[tid - 1];
-                if (pp != entry_p || ps != entry_sm) { entry_p = pp; entry_sm = ps; redo = true; }
+                const uint32_t pp = st.exit_p[tid - 1], ps = st.exit_sm[tid - 1];
+                need = pp != st.entry_p[tid] || ps != st.entry_sm[tid];
+                if (need) { st.entry_p[tid] = pp; st.entry_sm[tid] = ps; }
             }
-            if (!__syncthreads_or(redo)) break;
+            const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, need);
+            if (lane == 0) s_wcount[warp] = __popc(ballot);
+            __syncthreads();
+            uint32_t before = 0, total = 0;
+#pragma unroll
+            for (int i = 0; i < kSpecThreads / 32; ++i) { const uint32_t v = s_wcount[i]; if (i < warp) before += v; total += v; }
+            if (total == 0) break;
+            if (need) st.list[before + __popc(ballot & ((1u << lane) - 1))] = (uint32_t)tid;
+            __syncthreads();
+            if ((uint32_t)tid < total) decode_into_state(chunk, (int)st.list[tid]);
+            ++rounds;
+            decodes += total;
+            __syncthreads();
             if (round == kSpecThreads + 1) err |= kStSyncLimit;
         }
         // exclusive prefix over (slots, DC sums) of the chunk
-        Scan4 inc{active ? n : 0u, active ? a : 0, active ? b : 0, active ? c : 0};
+        Scan4 inc{active ? st.n[tid] : 0u, active ? st.dc[0][tid] : 0, active ? st.dc[1][tid] : 0, active ? st.dc[2][tid] : 0};
         const Scan4 mine = inc;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -348,6 +363,7 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
         if (lane == 31) s_warp[warp] = inc;
         __syncthreads();
         Scan4 pre{0, 0, 0, 0}, tot{0, 0, 0, 0};
+#pragma unroll
         for (int i = 0; i < kSpecThreads / 32; ++i) {
             const Scan4 t = s_warp[i];
             if (i < warp) { pre.n += t.n; pre.a += t.a; pre.b += t.b; pre.c += t.c; }
@@ -358,17 +374,16 @@ __global__ void __launch_bounds__(kSpecThreads) k_huff_spec(JpegWave w) {
                 p2 = s_carry_dc[2] + pre.c + inc.c - mine.c;
         // write pass
         if (active && slot0 < total_slots) {
-            uint32_t p = entry_p, sm = entry_sm, nn = 0;
-            br.seek(p);
-            decode_span<true>(br, p, end_bit, total_bits, sm, nn, total_slots - slot0, p0, p1, p2, hc, coef, slot0, err);
+            uint32_t p = st.entry_p[tid], sm = st.entry_sm[tid], nn = 0;
+            const uint32_t end_bit = min((chunk + tid + 1) * kSubseqBits, total_bits);
+            decode_span<true>(words, nwords, p, end_bit, total_bits, sm, nn, total_slots - slot0, p0, p1, p2, hc, coef, slot0, s_nat, err);
         }
         __syncthreads();
         if (tid == 0) {
             atomicAdd(w.spec_stats, 1ull);
             atomicAdd(w.spec_stats + 1, (unsigned long long)rounds);
-            atomicAdd(w.spec_stats + 2, (unsigned long long)decodes + min((uint32_t)kSpecThreads, nsub - chunk));
-            const uint32_t last = min((uint32_t)kSpecThreads, nsub - chunk) - 1;
-            s_carry_p = s_exit_p[last];
+            atomicAdd(w.spec_stats + 2, (unsigned long long)decodes + (uint32_t)cnt);
+            s_carry_p = st.exit_p[cnt - 1];
             s_carry_slot += tot.n;
             s_carry_dc[0] += tot.a; s_carry_dc[1] += tot.b; s_carry_dc[2] += tot.c;
         }
