@@ -64,7 +64,7 @@ class Item(C.Structure):
 class Result(C.Structure):
     _fields_ = [("status", C.c_int32), ("original_width", C.c_uint32), ("original_height", C.c_uint32),
                 ("width", C.c_uint32), ("height", C.c_uint32), ("channels", C.c_uint32), ("bit_depth", C.c_uint32),
-                ("nbytes", C.c_uint64), ("device_data", C.c_void_p), ("plan", Plan)]
+                ("nbytes", C.c_uint64), ("device_data", C.c_void_p), ("plan", Plan), ("packed_offset", C.c_uint64)]
 
 
 _lib = None
@@ -104,6 +104,8 @@ def lib():
         "dg_batch_upload": (C.c_int, [vp]),
         "dg_batch_run": (C.c_int, [vp]),
         "dg_batch_download": (C.c_int, [vp, C.POINTER(vp)]),
+        "dg_batch_download_packed": (C.c_int, [vp, vp, C.c_uint64]),
+        "dg_batch_packed_bytes": (C.c_uint64, [vp]),
         "dg_batch_sync": (C.c_int, [vp]),
         "dg_batch_result": (C.c_int, [vp, C.c_int, C.POINTER(Result)]),
         "dg_batch_stage_ms": (C.c_int, [vp, C.POINTER(C.c_float)]),
@@ -126,6 +128,7 @@ def lib():
 EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
            "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
+           "dg_batch_download_packed dg_batch_packed_bytes "
            "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_huffman_stats dg_batch_debug dg_batch_destroy dg_process "
            "dg_copy_to_host dg_resize_device_static").split()
 
@@ -333,6 +336,15 @@ class Batch:
         self._outs = outs
         _check(lib().dg_batch_download(self._h, ptrs))
         return outs
+
+    def packed_bytes(self):
+        return int(lib().dg_batch_packed_bytes(self._h))
+
+    def download_packed(self, host_buffer):
+        """Queue ONE device->host copy of every payload into `host_buffer` (a writable uint8 numpy array, ideally
+        pinned); payload i then sits at result(i).packed_offset.  Valid after sync()."""
+        self._outs = host_buffer
+        _check(lib().dg_batch_download_packed(self._h, host_buffer.ctypes.data, host_buffer.nbytes))
 
     def stage_ms(self):
         ms = (C.c_float * len(STAGES))()

@@ -909,6 +909,19 @@ extern "C" int dg_batch_download(dg_batch* b, uint8_t* const* host_out) {
     return DG_OK;
 }
 
+extern "C" uint64_t dg_batch_packed_bytes(const dg_batch* b) { return b ? b->out_bytes : 0; }
+
+extern "C" int dg_batch_download_packed(dg_batch* b, uint8_t* host_base, uint64_t capacity) {
+    if (!b || !host_base) return fail(DG_E_INVALID, "NULL argument");
+    if (capacity < b->out_bytes) return fail(DG_E_INVALID, "packed download needs %zu bytes, the buffer holds %llu", b->out_bytes, (unsigned long long)capacity);
+    dg_ctx* ctx = b->ctx;
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    CU(cudaSetDevice(ctx->device));
+    if (b->out_bytes) CU(cudaMemcpyAsync(host_base, b->d_persist + b->off_out, b->out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    b->d2h = b->out_bytes;
+    return DG_OK;
+}
+
 static int device_status_to_code(uint32_t bits) {
     if (bits == 0) return DG_OK;
     if (bits & kStSyncLimit) return DG_E_SYNC_LIMIT;
@@ -951,6 +964,7 @@ extern "C" int dg_batch_result(const dg_batch* b, int i, dg_result* out) {
         out->width = it.out_w; out->height = it.out_h; out->channels = it.c; out->bit_depth = 8;
         out->nbytes = it.out_bytes;
         out->device_data = b->d_persist + b->off_out + it.out_off;
+        out->packed_offset = it.out_off;
     }
     out->plan = it.plan;
     return DG_OK;

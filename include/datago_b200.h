@@ -90,6 +90,7 @@ typedef struct dg_result {
     uint64_t nbytes;              /* width * height * channels */
     const uint8_t* device_data;   /* HWC, row-major, tightly packed, in device memory owned by the batch */
     dg_plan plan;                 /* valid when the ctx has a transform */
+    uint64_t packed_offset;       /* where dg_batch_download_packed puts this payload, from its host base */
 } dg_result;
 
 typedef struct dg_ctx dg_ctx;
@@ -156,6 +157,11 @@ DG_API int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_t fl
 DG_API int dg_batch_upload(dg_batch* b);
 DG_API int dg_batch_run(dg_batch* b);
 DG_API int dg_batch_download(dg_batch* b, uint8_t* const* host_out);
+/* One device -> host copy for the whole batch: payload i lands at host_base + result.packed_offset (256-byte aligned
+ * slots).  dg_batch_packed_bytes gives the size the buffer needs.  Prefer this for large batches: thousands of separate
+ * asynchronous copies fill the driver's submission queue and stall the calling thread. */
+DG_API int dg_batch_download_packed(dg_batch* b, uint8_t* host_base, uint64_t capacity);
+DG_API uint64_t dg_batch_packed_bytes(const dg_batch* b);
 DG_API int dg_batch_sync(dg_batch* b);
 DG_API int dg_batch_result(const dg_batch* b, int i, dg_result* out);
 /* Milliseconds per stage of the last dg_batch_run of a DG_BATCH_TIMING batch (after dg_batch_sync). */

@@ -132,3 +132,21 @@ def test_stage_timers_and_counters():
         c = b.counters()
         assert c["kernel_launches"] >= 6 and c["h2d_bytes"] > sum(len(d) for d in datas) // 2
         assert ms["huff_spec"] > 0 and ms["huff_restart"] > 0 and ms["idct"] > 0 and ms["color"] > 0
+
+
+def test_packed_download_matches_per_item_download():
+    rng = np.random.default_rng(33)
+    datas = [jpeg(rng, 300, 200), jpeg(rng, 640, 480, rst=4), b"junk", jpeg(rng, 100, 333, None, 80, 0, True)]
+    c = ctx(C0)
+    per_item = c.process(datas)
+    with c.batch(datas) as b:
+        b.upload(); b.run()
+        buf = np.zeros(b.packed_bytes(), np.uint8)
+        b.download_packed(buf)
+        b.sync()
+        for i, (st, want, _) in enumerate(per_item):
+            r = b.result(i)
+            assert r.status == st
+            if st == 0:
+                assert r.packed_offset % 256 == 0
+                assert np.array_equal(buf[r.packed_offset:r.packed_offset + r.nbytes], want.reshape(-1))
