@@ -74,10 +74,9 @@ class ClockSampler:
             self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def window(self, t0, t1):
-        """Keep the samples taken inside [t0, t1]; when the window is too short to hold three, keep all of them
+        """Samples inside [t0, t1] are the ones reported; when the window is too short to hold three, all samples are
         (the sampler runs from the first warm-up pass on, so they are all under load)."""
-        inside = [r for (t, r) in self.rows if t0 <= t <= t1]
-        self.rows = inside if len(inside) >= 3 else [r for (_, r) in self.rows]
+        self.t0, self.t1 = t0, t1
 
     def stop(self):
         if not self.proc:
@@ -87,8 +86,10 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        if self.rows and isinstance(self.rows[0], tuple):
-            self.rows = [r for (_, r) in self.rows]
+        self.thread.join(timeout=2)
+        rows = list(self.rows)
+        inside = [r for (t, r) in rows if getattr(self, "t0", 0) <= t <= getattr(self, "t1", float("inf"))]
+        self.rows = inside if len(inside) >= 3 else [r for (_, r) in rows]
         sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
         mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]

@@ -16,6 +16,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -355,23 +356,64 @@ struct Planner {
         qt_ids.emplace(std::move(key), id);
         return id;
     }
-    // returns the table and its word offset in the pool
-    const FilterTable* table(int in_size, double in0, double in1, int out_size, size_t* word_off) {
+    static std::array<uint64_t, 4> table_key(int in_size, double in0, double in1, int out_size) {
         std::array<uint64_t, 4> key;
         key[0] = (uint64_t)in_size << 32 | (uint32_t)out_size;
         memcpy(&key[1], &in0, 8);
         memcpy(&key[2], &in1, 8);
         key[3] = 0;
-        auto it = table_ids.find(key);
-        if (it != table_ids.end()) { *word_off = it->second.first; return it->second.second; }
-        FilterTable* t = new FilterTable(make_filter_table(in_size, in0, in1, out_size));
+        return key;
+    }
+    void adopt(const std::array<uint64_t, 4>& key, FilterTable* t) {
         tables.push_back(t);
         size_t off = align_up(table_words.size(), 4);
         table_words.resize(off + t->words());
         t->pack(table_words.data() + off);
         table_ids.emplace(key, std::make_pair(off, t));
-        *word_off = off;
-        return t;
+    }
+    // returns the table and its word offset in the pool
+    const FilterTable* table(int in_size, double in0, double in1, int out_size, size_t* word_off) {
+        const auto key = table_key(in_size, in0, in1, out_size);
+        auto it = table_ids.find(key);
+        if (it == table_ids.end()) {
+            adopt(key, new FilterTable(make_filter_table(in_size, in0, in1, out_size)));
+            it = table_ids.find(key);
+        }
+        *word_off = it->second.first;
+        return it->second.second;
+    }
+    // Builds the filter tables a set of plans will ask for on all host cores (the weights cost a sin() each).
+    void prebuild_tables(const std::vector<const dg_plan*>& plans) {
+        struct Req { std::array<uint64_t, 4> key; int in_size; double in0, in1; int out_size; FilterTable* t; };
+        std::vector<Req> reqs;
+        std::map<std::array<uint64_t, 4>, int> seen;
+        auto want = [&](int in_size, double in0, double in1, int out_size) {
+            const auto key = table_key(in_size, in0, in1, out_size);
+            if (table_ids.count(key) || seen.count(key)) return;
+            seen[key] = 1;
+            reqs.push_back(Req{key, in_size, in0, in1, out_size, nullptr});
+        };
+        for (const dg_plan* pp : plans) {
+            const dg_plan& p = *pp;
+            if (p.identity) continue;
+            if (p.new_w != p.src_w) want((int)p.src_w, 0.0, (double)p.src_w, (int)p.new_w);
+            if (p.new_h != p.src_h) want((int)p.src_h, 0.0, (double)p.src_h, (int)p.new_h);
+            if ((double)p.target_w != p.crop_w || p.crop_left != std::round(p.crop_left))
+                want((int)p.new_w, p.crop_left, p.crop_left + p.crop_w, (int)p.target_w);
+            if ((double)p.target_h != p.crop_h || p.crop_top != std::round(p.crop_top))
+                want((int)p.new_h, p.crop_top, p.crop_top + p.crop_h, (int)p.target_h);
+        }
+        if (reqs.empty()) return;
+        const unsigned hw = std::thread::hardware_concurrency();
+        const size_t nthreads = std::min<size_t>(reqs.size() / 4 + 1, hw ? std::min(hw, 32u) : 4);
+        std::vector<std::thread> pool;
+        for (size_t w = 0; w < nthreads; ++w)
+            pool.emplace_back([&, w]() {
+                for (size_t i = w; i < reqs.size(); i += nthreads)
+                    reqs[i].t = new FilterTable(make_filter_table(reqs[i].in_size, reqs[i].in0, reqs[i].in1, reqs[i].out_size));
+            });
+        for (auto& th : pool) th.join();
+        for (Req& r : reqs) adopt(r.key, r.t);
     }
 };
 
@@ -433,7 +475,14 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         cp.src = s; cp.dst = d; cp.src_pitch = spitch; cp.dst_pitch = dpitch; cp.out_w = out_w; cp.out_h = out_h;
         cp.channels = C; cp.src_origin = origin; cp.t0 = t0; cp.tab_n = (uint32_t)T->n; cp.window = (uint32_t)T->window;
         cp.precision = (uint32_t)T->precision; cp.tab_off = tab_off;
-        cp.tiles_x = horizontal ? conv_h_tiles_x(out_w) : conv_v_tiles_x(out_w * C);
+        if (horizontal) {
+            cp.fast = 1;
+        } else {
+            const uintptr_t bits = (uintptr_t)s | (uintptr_t)d | spitch | dpitch;
+            cp.fast = (bits & 15) == 0 && (uint32_t)T->window <= kVFastMaxWindow && (size_t)align_up((size_t)out_w * C, 16) <= spitch &&
+                      (size_t)align_up((size_t)out_w * C, 16) <= dpitch;
+        }
+        cp.tiles_x = conv_tiles_x(cp, !horizontal);
         wv.passes[stage].push_back(cp);
         ++done;
     };
@@ -661,6 +710,12 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     // contains them.  So the passes are planned twice: once against a stand-in base to size the metadata (filter
     // tables are cached, the second round is cheap), once with the real base address.
     uint8_t* const kBaseS = b->d_scratch;
+    if (transform) {
+        std::vector<const dg_plan*> plans;
+        for (const ItemPlan& it : b->items)
+            if (!it.status && it.wave >= 0) plans.push_back(&it.plan);
+        pl.prebuild_tables(plans);
+    }
     for (int round = 0; round < 2; ++round) {
         uint8_t* baseP = round == 0 ? kBaseS : b->d_persist;
         for (WavePlan& wv : b->waves) {
@@ -681,7 +736,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                 wv.pass_first[s].push_back(0);
                 for (ConvPass& cp : wv.passes[s]) {
                     cp.tile_first = t;
-                    t += (s & 1) ? conv_v_tiles(cp.out_w * cp.channels, cp.out_h) : conv_h_tiles(cp.out_w, cp.out_h);
+                    t += conv_tiles(cp, (s & 1) != 0);
                     wv.pass_first[s].push_back(t);
                 }
             }
@@ -1120,7 +1175,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
         wv.pass_first[s].push_back(0);
         for (ConvPass& cp : wv.passes[s]) {
             cp.tile_first = t;
-            t += (s & 1) ? conv_v_tiles(cp.out_w * cp.channels, cp.out_h) : conv_h_tiles(cp.out_w, cp.out_h);
+            t += conv_tiles(cp, (s & 1) != 0);
             wv.pass_first[s].push_back(t);
         }
         m_passes[s] = m.put(wv.passes[s], 16);

@@ -72,6 +72,8 @@ struct ConvPass {
     uint64_t tab_off;               // word offset in the table pool: start[tab_n] | size[tab_n] | int16 k[window][tab_n]
     uint32_t tile_first;            // first CTA tile of this pass in the launch (prefix sum)
     uint32_t tiles_x;               // tiles per row of tiles
+    uint32_t fast;                  // 1: the staged / vectorised kernel path applies (see kernels_resize.cu)
+    uint32_t pad;
 };
 
 struct CopyJob {  // identity payloads / pitch removal

@@ -50,12 +50,19 @@ constexpr uint32_t kColorTileW = 256;
 inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) { return ((width + kColorTileW - 1) / kColorTileW) * mcuy; }
 
 // ---- resize ---------------------------------------------------------------------------------------------------------
-constexpr uint32_t kConvTileW = 64, kConvTileH = 4;     // horizontal pass: output pixels per CTA
-constexpr uint32_t kVTileBytes = 256, kVTileH = 4;      // vertical pass: output bytes x rows per CTA
-inline uint32_t conv_h_tiles_x(uint32_t out_w) { return (out_w + kConvTileW - 1) / kConvTileW; }
-inline uint32_t conv_h_tiles(uint32_t out_w, uint32_t out_h) { return conv_h_tiles_x(out_w) * ((out_h + kConvTileH - 1) / kConvTileH); }
-inline uint32_t conv_v_tiles_x(uint32_t row_bytes) { return (row_bytes + kVTileBytes - 1) / kVTileBytes; }
-inline uint32_t conv_v_tiles(uint32_t row_bytes, uint32_t out_h) { return conv_v_tiles_x(row_bytes) * ((out_h + kVTileH - 1) / kVTileH); }
+constexpr uint32_t kConvTileW = 64, kConvTileH = 16;    // horizontal pass: output pixels x rows per CTA
+constexpr uint32_t kVTileBytes = 256, kVTileH = 4;      // vertical pass, plain path: output bytes x rows per CTA
+constexpr uint32_t kVFastBytes = 1024, kVFastRows = 32; // vertical pass, vector path: 64 x 16-byte columns, 4 x 8 rows
+constexpr uint32_t kVFastMaxWindow = 128;
+inline uint32_t conv_tiles_x(const ConvPass& p, bool vertical) {
+    if (!vertical) return (p.out_w + kConvTileW - 1) / kConvTileW;
+    const uint32_t row_bytes = p.out_w * p.channels;
+    return p.fast ? (row_bytes + kVFastBytes - 1) / kVFastBytes : (row_bytes + kVTileBytes - 1) / kVTileBytes;
+}
+inline uint32_t conv_tiles(const ConvPass& p, bool vertical) {
+    const uint32_t rows = !vertical ? kConvTileH : p.fast ? kVFastRows : kVTileH;
+    return conv_tiles_x(p, vertical) * ((p.out_h + rows - 1) / rows);
+}
 constexpr uint32_t kCopyTileBytes = 4096;
 
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);

@@ -1,9 +1,17 @@
 // Separable Lanczos3 convolution passes on 8-bit interleaved images (1 or 3 channels), batched over images.
 // Replaces the two fast_image_resize::Resizer::resize calls of datago's crop_and_resize
 // (src/image_processing.rs:288-323): whole-image resize, then the centred crop (a copy for an integral offset,
-// a 6-tap half-pixel shift along one axis otherwise).  Every pass rounds to 8 bits exactly as the CPU library does.
+// a 6-tap half-pixel shift along one axis otherwise).  Every pass rounds to 8 bits exactly as the CPU library does:
+// int16 weights, int32 accumulation started at half an LSB, arithmetic shift, clamp.
 //
-// HBM-bound byte work: one launch covers one pass of every image of a batch; a CTA owns one output tile.
+// One launch covers one pass of every image of a wave; a CTA owns one output tile.  Two taps are applied per
+// instruction: dp2a multiplies a pair of 16-bit weights with a pair of 8-bit samples and accumulates in 32 bits,
+// which is exactly the reference arithmetic.
+//   horizontal: one thread per output pixel column and 4 rows; windows are read as aligned words from global memory
+//               (neighbouring lanes overlap almost completely, so L1 serves them) and realigned in registers.
+//   vertical:   one thread per 16-byte column chunk and 8 output rows, 128-bit loads and stores; weights of the
+//               tile's rows are staged in shared memory as ready-made pairs.
+// Vertical passes over unaligned or unpadded rows take the plain 4-byte path.
 #include <cstdint>
 
 #include "kernels.h"
@@ -21,67 +29,130 @@ __device__ __forceinline__ uint32_t clip8(int32_t v, uint32_t precision) {
     return (uint32_t)min(max(v, 0), 255);
 }
 
-// ---- horizontal pass: one thread per output pixel ---------------------------------------------------------------
-constexpr int kConvHThreads = kConvTileW * kConvTileH;
+__device__ __forceinline__ int32_t dp2a_lo(uint32_t weights, uint32_t samples, int32_t acc) {
+    int32_t d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(weights), "r"(samples), "r"(acc));
+    return d;
+}
+__device__ __forceinline__ int32_t dp2a_hi(uint32_t weights, uint32_t samples, int32_t acc) {
+    int32_t d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(weights), "r"(samples), "r"(acc));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_sat4(int32_t a, int32_t b, int32_t c, int32_t d) {  // a in the lowest byte
+    uint32_t hi, r;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+    return r;
+}
+
+struct Table {
+    const int32_t* start;
+    const int32_t* size;
+    const int16_t* k;  // [tap][tab_n]
+};
+__device__ __forceinline__ Table table_of(const ConvPass& p, const uint32_t* tables) {
+    Table t;
+    t.start = reinterpret_cast<const int32_t*>(tables + p.tab_off);
+    t.size = t.start + p.tab_n;
+    t.k = reinterpret_cast<const int16_t*>(t.size + p.tab_n);
+    return t;
+}
+
+// ---- horizontal pass ---------------------------------------------------------------------------------------------------
+// One thread per output pixel column and kHRowsPerThread rows.  The window of an output pixel is taps * C consecutive
+// bytes of a source row: it is fetched four taps at a time as aligned 32-bit words, realigned with funnel shifts, and
+// the (tap, tap + 1) byte pairs of each channel are gathered with byte permutes and fed to dp2a.  Weights beyond a
+// window are zero in the table, so the bytes read past it (at most 15, inside the buffer's slack) do not matter.
+constexpr int kHRowsPerThread = kConvTileH / 4;
+constexpr int kConvHThreads = kConvTileW * 4;
 
 template <int C>
-__device__ __forceinline__ void conv_h_pixel(const ConvPass& p, const uint32_t* tab, uint32_t x, uint32_t y) {
+__device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, uint32_t x, uint32_t y0) {
     const uint32_t t = p.t0 + x;
-    const int32_t* start = reinterpret_cast<const int32_t*>(tab);
-    const int32_t* size = start + p.tab_n;
-    const int16_t* k = reinterpret_cast<const int16_t*>(size + p.tab_n) + t;
-    const int32_t first = __ldg(start + t) - p.src_origin;
-    const int32_t taps = __ldg(size + t);
-    const uint8_t* s = p.src + (size_t)y * p.src_pitch + (size_t)first * C;
-    int32_t acc[C];
+    const int32_t first = __ldg(tb.start + t) - p.src_origin;
+    const int32_t taps = __ldg(tb.size + t);
+    const int16_t* k = tb.k + t;
+    const uint32_t nrows = min((uint32_t)kHRowsPerThread, p.out_h - y0);
+    const uint32_t* base[kHRowsPerThread];
+    uint32_t shift[kHRowsPerThread];
+    int32_t acc[kHRowsPerThread][C];
 #pragma unroll
-    for (int c = 0; c < C; ++c) acc[c] = 1 << (p.precision - 1);
-    for (int32_t i = 0; i < taps; ++i) {
-        const int32_t kv = __ldg(k + (size_t)i * p.tab_n);
+    for (int r = 0; r < kHRowsPerThread; ++r) {
+        const uint8_t* g = p.src + (size_t)(y0 + min((uint32_t)r, nrows - 1)) * p.src_pitch + (size_t)first * C;
+        const uint32_t m = (uint32_t)(reinterpret_cast<uintptr_t>(g) & 3u);
+        base[r] = reinterpret_cast<const uint32_t*>(g - m);
+        shift[r] = m * 8;
 #pragma unroll
-        for (int c = 0; c < C; ++c) acc[c] += kv * (int32_t)__ldg(s + i * C + c);
+        for (int c = 0; c < C; ++c) acc[r][c] = 1 << (p.precision - 1);
     }
-    uint8_t* o = p.dst + (size_t)y * p.dst_pitch + (size_t)x * C;
+    for (int32_t i = 0; i < taps; i += 4) {
+        // weights of taps i..i+3 as two pairs (entries past the window are zero; past the table they are not read)
+        uint32_t kw[4];
 #pragma unroll
-    for (int c = 0; c < C; ++c) o[c] = (uint8_t)clip8(acc[c], p.precision);
+        for (int j = 0; j < 4; ++j) kw[j] = (uint32_t)(i + j) < p.window ? (uint16_t)__ldg(k + (size_t)(i + j) * p.tab_n) : 0u;
+        const uint32_t k01 = kw[0] | (kw[1] << 16), k23 = kw[2] | (kw[3] << 16);
+#pragma unroll
+        for (int r = 0; r < kHRowsPerThread; ++r) {
+            const uint32_t* w = base[r] + (i * C) / 4;  // i is a multiple of 4: i * C bytes is a whole number of words
+            if (C == 3) {
+                const uint32_t a0 = __ldg(w), a1 = __ldg(w + 1), a2 = __ldg(w + 2), a3 = __ldg(w + 3);
+                const uint32_t w0 = __funnelshift_r(a0, a1, shift[r]), w1 = __funnelshift_r(a1, a2, shift[r]),
+                               w2 = __funnelshift_r(a2, a3, shift[r]);
+                // byte 3 * tap + channel
+                acc[r][0] = dp2a_lo(k01, __byte_perm(w0, w0, 0x0030), acc[r][0]);
+                acc[r][1] = dp2a_lo(k01, __byte_perm(w0, w1, 0x0041), acc[r][1]);
+                acc[r][2] = dp2a_lo(k01, __byte_perm(w0, w1, 0x0052), acc[r][2]);
+                acc[r][0] = dp2a_lo(k23, __byte_perm(w1, w2, 0x0052), acc[r][0]);
+                acc[r][1] = dp2a_lo(k23, __byte_perm(w1, w2, 0x0063), acc[r][1]);
+                acc[r][2] = dp2a_lo(k23, __byte_perm(w2, w2, 0x0030), acc[r][2]);
+            } else {
+                const uint32_t a0 = __ldg(w), a1 = __ldg(w + 1);
+                const uint32_t w0 = __funnelshift_r(a0, a1, shift[r]);
+                acc[r][0] = dp2a_hi(k23, w0, dp2a_lo(k01, w0, acc[r][0]));
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kHRowsPerThread; ++r) {
+        if ((uint32_t)r >= nrows) break;
+        uint8_t* o = p.dst + (size_t)(y0 + r) * p.dst_pitch + (size_t)x * C;
+#pragma unroll
+        for (int c = 0; c < C; ++c) o[c] = (uint8_t)clip8(acc[r][c], p.precision);
+    }
 }
 
 __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables) {
-    const uint32_t pi = owner_of_tile(map, blockIdx.x);
-    const ConvPass& p = passes[pi];
+    const ConvPass& p = passes[owner_of_tile(map, blockIdx.x)];
     const uint32_t tile = blockIdx.x - p.tile_first;
     const uint32_t ty = tile / p.tiles_x, tx = tile - ty * p.tiles_x;
     const uint32_t x = tx * kConvTileW + threadIdx.x % kConvTileW;
-    const uint32_t y = ty * kConvTileH + threadIdx.x / kConvTileW;
-    if (x >= p.out_w || y >= p.out_h) return;
-    const uint32_t* tab = tables + p.tab_off;
-    if (p.channels == 3) conv_h_pixel<3>(p, tab, x, y);
-    else conv_h_pixel<1>(p, tab, x, y);
+    const uint32_t y0 = ty * kConvTileH + (threadIdx.x / kConvTileW) * kHRowsPerThread;
+    if (x >= p.out_w || y0 >= p.out_h) return;
+    const Table tb = table_of(p, tables);
+    if (p.channels == 3) conv_h_rows<3>(p, tb, x, y0);
+    else conv_h_rows<1>(p, tb, x, y0);
 }
 
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s) {
     if (map.total) k_conv_h<<<map.total, kConvHThreads, 0, s>>>(passes, map, tables);
 }
 
-// ---- vertical pass: one thread per 4 consecutive bytes of an output row ----------------------------------------------
-constexpr int kConvVThreads = (kVTileBytes / 4) * kVTileH;
+// ---- vertical pass -----------------------------------------------------------------------------------------------------
+constexpr int kConvVThreads = 256;
+constexpr int kVFastCols = kVFastBytes / 16;          // 64 column chunks
+constexpr int kVFastGroups = kConvVThreads / kVFastCols;  // 4 groups of rows
+constexpr int kVRowsPerThread = kVFastRows / kVFastGroups;  // 8
 
-__global__ void __launch_bounds__(kConvVThreads) k_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables) {
-    const uint32_t pi = owner_of_tile(map, blockIdx.x);
-    const ConvPass& p = passes[pi];
-    const uint32_t tile = blockIdx.x - p.tile_first;
-    const uint32_t ty = tile / p.tiles_x, tx = tile - ty * p.tiles_x;
+__device__ __forceinline__ void conv_v_plain(const ConvPass& p, const Table& tb, uint32_t tx, uint32_t ty) {
     const uint32_t row_bytes = p.out_w * p.channels;
     const uint32_t xb = tx * kVTileBytes + (threadIdx.x % (kVTileBytes / 4)) * 4;
     const uint32_t y = ty * kVTileH + threadIdx.x / (kVTileBytes / 4);
     if (xb >= row_bytes || y >= p.out_h) return;
-    const uint32_t* tab = tables + p.tab_off;
     const uint32_t t = p.t0 + y;
-    const int32_t* start = reinterpret_cast<const int32_t*>(tab);
-    const int32_t* size = start + p.tab_n;
-    const int16_t* k = reinterpret_cast<const int16_t*>(size + p.tab_n) + t;
-    const int32_t first = __ldg(start + t) - p.src_origin;
-    const int32_t taps = __ldg(size + t);
+    const int16_t* k = tb.k + t;
+    const int32_t first = __ldg(tb.start + t) - p.src_origin;
+    const int32_t taps = __ldg(tb.size + t);
     const uint8_t* s = p.src + (size_t)first * p.src_pitch + xb;
     const int32_t half = 1 << (p.precision - 1);
     int32_t a0 = half, a1 = half, a2 = half, a3 = half;
@@ -114,6 +185,77 @@ __global__ void __launch_bounds__(kConvVThreads) k_conv_v(const ConvPass* passes
         if (nb > 2) o[2] = (uint8_t)r2;
         if (nb > 3) o[3] = (uint8_t)r3;
     }
+}
+
+// 16-byte columns.  Source and destination rows are 16-byte aligned and padded, so the last chunk of a row may be
+// read and written in full.
+__device__ __forceinline__ void conv_v_vector(const ConvPass& p, const Table& tb, uint32_t tx, uint32_t ty,
+                                              uint32_t (*s_k)[kVFastMaxWindow / 2], int32_t* s_first, int32_t* s_taps) {
+    const uint32_t y0 = ty * kVFastRows;
+    const uint32_t nrows = min((uint32_t)kVFastRows, p.out_h - y0);
+    // stage start, size and paired weights of the tile's rows
+    for (uint32_t i = threadIdx.x; i < nrows; i += kConvVThreads) {
+        s_first[i] = __ldg(tb.start + p.t0 + y0 + i) - p.src_origin;
+        s_taps[i] = __ldg(tb.size + p.t0 + y0 + i);
+    }
+    const uint32_t pairs = (p.window + 1) / 2;
+    for (uint32_t i = threadIdx.x; i < nrows * pairs; i += kConvVThreads) {
+        const uint32_t r = i / pairs, j = i - r * pairs;
+        const int16_t* k = tb.k + p.t0 + y0 + r;
+        const uint32_t lo = (uint16_t)__ldg(k + (size_t)(2 * j) * p.tab_n);
+        const uint32_t hi = 2 * j + 1 < p.window ? (uint16_t)__ldg(k + (size_t)(2 * j + 1) * p.tab_n) : 0u;
+        s_k[r][j] = lo | (hi << 16);
+    }
+    __syncthreads();
+    const uint32_t col = threadIdx.x % kVFastCols, grp = threadIdx.x / kVFastCols;
+    const uint32_t xb = tx * kVFastBytes + col * 16;
+    if (xb >= p.out_w * p.channels) return;
+    const int32_t half = 1 << (p.precision - 1);
+#pragma unroll 1
+    for (uint32_t rr = 0; rr < (uint32_t)kVRowsPerThread; ++rr) {
+        const uint32_t r = grp * kVRowsPerThread + rr;
+        if (r >= nrows) break;
+        const int32_t taps = s_taps[r];
+        const uint8_t* s = p.src + (size_t)s_first[r] * p.src_pitch + xb;
+        int32_t acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[i] = half;
+        for (int32_t i = 0; i < taps; i += 2) {
+            const uint32_t kp = s_k[r][i >> 1];  // the weight after the last tap of an odd window is zero
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(s + (size_t)i * p.src_pitch));
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(s + (size_t)min(i + 1, taps - 1) * p.src_pitch));
+            const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int wq = 0; wq < 4; ++wq) {
+                const uint32_t p01 = __byte_perm(aw[wq], bw[wq], 0x5140), p23 = __byte_perm(aw[wq], bw[wq], 0x7362);
+                acc[4 * wq] = dp2a_lo(kp, p01, acc[4 * wq]);
+                acc[4 * wq + 1] = dp2a_hi(kp, p01, acc[4 * wq + 1]);
+                acc[4 * wq + 2] = dp2a_lo(kp, p23, acc[4 * wq + 2]);
+                acc[4 * wq + 3] = dp2a_hi(kp, p23, acc[4 * wq + 3]);
+            }
+        }
+        uint4 o;
+        const uint32_t sh = p.precision;
+        o.x = pack_sat4(acc[0] >> sh, acc[1] >> sh, acc[2] >> sh, acc[3] >> sh);
+        o.y = pack_sat4(acc[4] >> sh, acc[5] >> sh, acc[6] >> sh, acc[7] >> sh);
+        o.z = pack_sat4(acc[8] >> sh, acc[9] >> sh, acc[10] >> sh, acc[11] >> sh);
+        o.w = pack_sat4(acc[12] >> sh, acc[13] >> sh, acc[14] >> sh, acc[15] >> sh);
+        *reinterpret_cast<uint4*>(p.dst + (size_t)(y0 + r) * p.dst_pitch + xb) = o;
+    }
+}
+
+__global__ void __launch_bounds__(kConvVThreads) k_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables) {
+    __shared__ uint32_t s_k[kVFastRows][kVFastMaxWindow / 2];
+    __shared__ int32_t s_first[kVFastRows], s_taps[kVFastRows];
+    __shared__ uint32_t s_pass;
+    if (threadIdx.x == 0) s_pass = owner_of_tile(map, blockIdx.x);
+    __syncthreads();
+    const ConvPass& p = passes[s_pass];
+    const uint32_t tile = blockIdx.x - p.tile_first;
+    const uint32_t ty = tile / p.tiles_x, tx = tile - ty * p.tiles_x;
+    const Table tb = table_of(p, tables);
+    if (p.fast) conv_v_vector(p, tb, tx, ty, s_k, s_first, s_taps);
+    else conv_v_plain(p, tb, tx, ty);
 }
 
 void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s) {
