@@ -1,0 +1,76 @@
+"""Host-side pieces of the DatagoClient harness that need no GPU: config checks, file enumeration with rank slices,
+local tar (webdataset) reading, sample grouping and key-hash sharding.  Mirrors the assertions of datago's own
+multi-rank tests (src/generator_files.rs:362-424, src/generator_wds.rs:651-706): ranks are disjoint and cover."""
+import io
+import json
+import os
+import tarfile
+
+import pytest
+
+import oracle
+from datago_b200 import client
+
+
+def _tar(path, entries):
+    with tarfile.open(path, "w") as tf:
+        for name, payload in entries:
+            ti = tarfile.TarInfo(name)
+            ti.size = len(payload)
+            tf.addfile(ti, io.BytesIO(payload))
+
+
+def test_check_config_mirrors_reference_rules():
+    ok = dict(source_type="file", source_config=dict(root_path="/tmp", rank=0, world_size=1), limit=10, samples_buffer_size=4)
+    assert client.DatagoClient._check_config(json.dumps(ok)) is not None
+    for bad in (dict(ok, limit=0), dict(ok, samples_buffer_size=0),
+                dict(ok, source_config=dict(root_path="/tmp", rank=2, world_size=2)),
+                dict(ok, source_config=dict(root_path="/tmp", rank=0, world_size=0))):
+        assert client.DatagoClient._check_config(json.dumps(bad)) is None
+    assert client.DatagoClient._check_config("not json") is None
+    assert client.DatagoClient._check_config(json.dumps(dict(limit=1))) is None
+
+
+def test_enumerate_files_filters_limits_and_slices(tmp_path):
+    for i in range(23):
+        (tmp_path / f"img_{i:02d}.jpg").write_bytes(b"x")
+    (tmp_path / "notes.txt").write_bytes(b"x")
+    (tmp_path / "sub").mkdir()
+    (tmp_path / "sub" / "deep.PNG").write_bytes(b"x")
+    files = client.enumerate_files(str(tmp_path), 100)
+    assert len(files) == 24 and not any(f.endswith(".txt") for f in files)
+    assert len(client.enumerate_files(str(tmp_path), 5)) == 6        # ceil(1.1 * 5)
+    r0 = client.enumerate_files(str(tmp_path), 100, 0, 2)
+    r1 = client.enumerate_files(str(tmp_path), 100, 1, 2)
+    assert len(r0) == 12 and len(r1) == 12 and not set(r0) & set(r1) and set(r0) | set(r1) == set(files)
+
+
+def test_expand_shards(tmp_path):
+    for i in range(3):
+        (tmp_path / f"shard-{i:03d}.tar").write_bytes(b"")
+    want = [str(tmp_path / f"shard-{i:03d}.tar") for i in range(3)]
+    assert client.expand_shards(str(tmp_path / "shard-{000..002}.tar")) == want
+    assert client.expand_shards(str(tmp_path / "shard-*.tar")) == want
+
+
+def test_tar_samples_group_by_key_and_put_the_reference_image_first(tmp_path):
+    path = str(tmp_path / "s.tar")
+    _tar(path, [("a.json", b"{}"), ("a.mask.png", b"m"), ("a.jpg", b"J"), ("b.jpg", b"K"), ("b.txt", b"t"), ("c.cls", b"3")])
+    got = [[n for n, _ in files] for _, files in client.tar_samples(path)]
+    # key = basename without the LAST extension: "a.mask" is its own key (src/generator_wds.rs:133-138)
+    assert got == [["a.json"], ["a.mask.png"], ["a.jpg"], ["b.jpg", "b.txt"], ["c.cls"]]
+    _tar(path, [("x.json", b"{}"), ("x.png", b"m"), ("x.jpg", b"J"), ("y.txt", b"t"), ("y.jpg", b"K")])
+    got = [[n for n, _ in files] for _, files in client.tar_samples(path)]
+    assert got == [["x.jpg", "x.json", "x.png"], ["y.jpg", "y.txt"]]
+
+
+def test_tar_key_hash_sharding_is_disjoint_and_covers(tmp_path):
+    path = str(tmp_path / "s.tar")
+    keys = ["%06d_%04d" % (0, i) for i in range(200)]
+    _tar(path, [(k + ext, b"p") for k in keys for ext in (".jpg", ".json")])
+    seen = []
+    for rank in range(4):
+        mine = [os.path.splitext(files[0][0])[0] for _, files in client.tar_samples(path, "jpg", rank, 4)]
+        assert all(oracle.key_hash(k) % 4 == rank for k in mine)
+        seen += mine
+    assert sorted(seen) == keys
