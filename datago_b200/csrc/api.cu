@@ -102,14 +102,16 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct dg_ctx {
     int device = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;   // everything the caller can observe is ordered on this stream
+    cudaStream_t stream2 = nullptr;  // odd waves of a batch run here, concurrently with the even ones
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool own_stream = false;
     bool has_tfm = false;
     dg_image_config cfg{};
     Transform tfm;
     std::mutex mu;
     BlockCache dev{false}, pin{true};
-    size_t wave_bytes = (size_t)8 << 30;  // coefficient bytes per wave
+    size_t wave_bytes = (size_t)13 << 30;  // coefficient bytes per wave (upper bound; waves are balanced below it)
     size_t l2_group_bytes = (size_t)64 << 20;  // plane bytes per IDCT + colour launch pair
 };
 
@@ -139,6 +141,12 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
         if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return fail(DG_E_CUDA, "cudaStreamCreate failed"); }
         c->own_stream = true;
     }
+    if (cudaStreamCreateWithFlags(&c->stream2, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        delete c;
+        return fail(DG_E_CUDA, "creating the second stream failed");
+    }
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
@@ -153,8 +161,12 @@ extern "C" void dg_ctx_destroy(dg_ctx* c) {
     if (c->device == DG_DEVICE_NONE) { delete c; return; }
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
+    cudaStreamSynchronize(c->stream2);
     c->dev.clear();
     c->pin.clear();
+    cudaEventDestroy(c->ev_fork);
+    cudaEventDestroy(c->ev_join);
+    cudaStreamDestroy(c->stream2);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
 }
@@ -305,9 +317,10 @@ struct dg_batch {
     std::vector<WavePlan> waves;
     Meta meta;
     // persistent device block: [meta | status | blob | raw inputs | outputs]
-    int blk_persist = -1, blk_scratch = -1, blk_pin = -1, blk_pin_status = -1;
+    int blk_persist = -1, blk_scratch = -1, blk_scratch2 = -1, blk_pin = -1, blk_pin_status = -1;
     uint8_t* d_persist = nullptr;
-    uint8_t* d_scratch = nullptr;
+    uint8_t* d_scratch = nullptr;   // scratch of the even waves
+    uint8_t* d_scratch2 = nullptr;  // scratch of the odd waves (same block when the batch has one wave)
     uint8_t* h_pin = nullptr;       // pinned image of [meta | status zeros | blob]
     uint32_t* h_status = nullptr;   // pinned, n words
     size_t off_meta = 0, off_status = 0, off_blob = 0, off_rawin = 0, off_out = 0, persist_bytes = 0;
@@ -530,6 +543,7 @@ static int abandon(dg_batch* b, int rc) {
     dg_ctx* ctx = b->ctx;
     ctx->dev.release(b->blk_persist);
     ctx->dev.release(b->blk_scratch);
+    ctx->dev.release(b->blk_scratch2);
     ctx->pin.release(b->blk_pin);
     ctx->pin.release(b->blk_pin_status);
     delete b;
@@ -585,27 +599,40 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     b->blob_bytes = blob; b->rawin_bytes = rawin; b->out_bytes = outb;
 
     // ---- pass 2: waves ----------------------------------------------------------------------------------------------------
+    // Few, large, equally sized waves: large because the entropy kernels fill the GPU only with hundreds of images per
+    // launch, at least two (when there is enough work) so that the two streams of dg_batch_run overlap them.
     {
+        std::vector<size_t> need_coef(n, 0), need_big(n, 0);
+        size_t total_coef = 0, total_big = 0;
+        for (int i = 0; i < n; ++i) {
+            ItemPlan& it = b->items[i];
+            if (it.status) continue;
+            if (it.is_jpeg) {
+                const JpegHeader& h = *it.hdr;
+                it.nblocks = h.mcux * h.mcuy * (h.ncomp == 1 ? 1 : h.hs * h.vs + 2);
+                need_coef[i] = (size_t)it.nblocks * 128;
+                if (transform) need_big[i] += align_up((size_t)it.w * it.h * it.c, 256);
+            }
+            if (transform) need_big[i] += resize_mid_bound(it.plan, it.c);
+            total_coef += need_coef[i];
+            total_big += need_big[i];
+        }
+        size_t n_waves = std::max<size_t>(1, std::max((total_coef + ctx->wave_bytes - 1) / ctx->wave_bytes,
+                                                      (total_big + 2 * ctx->wave_bytes - 1) / (2 * ctx->wave_bytes)));
+        if (n_waves == 1 && total_coef + total_big > ((size_t)1 << 30)) n_waves = 2;
+        const size_t coef_cap = total_coef / n_waves + 1, big_cap = total_big / n_waves + 1;
         WavePlan* wv = nullptr;
         size_t coef_bytes = 0, big_bytes = 0;
         for (int i = 0; i < n; ++i) {
             ItemPlan& it = b->items[i];
             if (it.status) continue;
-            size_t need_coef = 0, need_big = 0;
-            if (it.is_jpeg) {
-                const JpegHeader& h = *it.hdr;
-                it.nblocks = h.mcux * h.mcuy * (h.ncomp == 1 ? 1 : h.hs * h.vs + 2);
-                need_coef = (size_t)it.nblocks * 128;
-                if (transform) need_big += align_up((size_t)it.w * it.h * it.c, 256);
-            }
-            if (transform) need_big += resize_mid_bound(it.plan, it.c);
-            if (!wv || (coef_bytes + need_coef > ctx->wave_bytes && coef_bytes > 0) || (big_bytes + need_big > 2 * ctx->wave_bytes && big_bytes > 0)) {
+            if (!wv || (coef_bytes >= coef_cap && coef_cap > 1) || (big_bytes >= big_cap && big_cap > 1 && total_coef == 0)) {
                 b->waves.emplace_back();
                 wv = &b->waves.back();
                 wv->first_item = i;
                 coef_bytes = big_bytes = 0;
             }
-            coef_bytes += need_coef; big_bytes += need_big;
+            coef_bytes += need_coef[i]; big_bytes += need_big[i];
             it.wave = (int)b->waves.size() - 1;
             wv->last_item = i + 1;
         }
@@ -699,6 +726,12 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     int rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch);
     if (rc) return abandon(b, rc);
     b->d_scratch = (uint8_t*)ctx->dev.blocks[b->blk_scratch].ptr;
+    b->d_scratch2 = b->d_scratch;
+    if (b->waves.size() > 1) {
+        rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch2);
+        if (rc) return abandon(b, rc);
+        b->d_scratch2 = (uint8_t*)ctx->dev.blocks[b->blk_scratch2].ptr;
+    }
 
     b->off_status = 0;  // n status words, then 4 counters of the speculative Huffman kernel
     b->off_blob = align_up((size_t)n * 4 + 32, 256);
@@ -709,7 +742,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     // Resize descriptors hold device addresses inside the persistent block, whose size depends on the metadata that
     // contains them.  So the passes are planned twice: once against a stand-in base to size the metadata (filter
     // tables are cached, the second round is cheap), once with the real base address.
-    uint8_t* const kBaseS = b->d_scratch;
     if (transform) {
         std::vector<const dg_plan*> plans;
         for (const ItemPlan& it : b->items)
@@ -717,8 +749,10 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         pl.prebuild_tables(plans);
     }
     for (int round = 0; round < 2; ++round) {
-        uint8_t* baseP = round == 0 ? kBaseS : b->d_persist;
-        for (WavePlan& wv : b->waves) {
+        uint8_t* baseP = round == 0 ? b->d_scratch : b->d_persist;
+        for (size_t wi = 0; wi < b->waves.size(); ++wi) {
+            WavePlan& wv = b->waves[wi];
+            uint8_t* const kBaseS = (wi & 1) ? b->d_scratch2 : b->d_scratch;
             for (int s = 0; s < 4; ++s) { wv.passes[s].clear(); wv.pass_first[s].clear(); }
             wv.copies.clear(); wv.copy_first.clear();
             if (!transform) continue;
@@ -850,6 +884,10 @@ extern "C" int dg_batch_run(dg_batch* b) {
     cudaStream_t s = ctx->stream;
     const uint8_t* meta = b->d_persist + b->off_meta;
     const bool timing = (b->flags & DG_BATCH_TIMING) != 0;
+    // Waves alternate between two streams and two scratch blocks, so the serial, latency-bound entropy decoding of one
+    // wave overlaps the bandwidth-hungry reconstruction of the other.  A timing batch stays on one stream: its stage
+    // events then bracket kernels that ran alone.
+    const bool two_lanes = !timing && b->waves.size() > 1;
     const bool transform = ctx->has_tfm && !(b->flags & DG_BATCH_DECODE_ONLY);
     size_t ev = 0;
     auto mark = [&](int stage, bool begin) -> cudaError_t {
@@ -869,8 +907,16 @@ extern "C" int dg_batch_run(dg_batch* b) {
     };
     b->launches = 0;
     if (b->ran) CU(cudaMemsetAsync(b->d_persist + b->off_status, 0, align_up((size_t)b->n * 4, 8) + 32, s));  // status words of the previous run
-    for (WavePlan& wv : b->waves) {
-        uint8_t* sc = b->d_scratch;
+    if (two_lanes) {
+        CU(cudaEventRecord(ctx->ev_fork, ctx->stream));
+        CU(cudaStreamWaitEvent(ctx->stream2, ctx->ev_fork, 0));
+    }
+    for (size_t wi = 0; wi < b->waves.size(); ++wi) {
+        WavePlan& wv = b->waves[wi];
+        uint8_t* sc = (wi & 1) ? b->d_scratch2 : b->d_scratch;
+        // the scratch block belongs to the lane, so in one-stream mode an odd wave must wait for nothing extra:
+        // stream order already serialises the waves
+        s = (two_lanes && (wi & 1)) ? ctx->stream2 : ctx->stream;
         if (!wv.descs.empty()) {
             JpegWave w;
             memset(&w, 0, sizeof w);
@@ -943,6 +989,10 @@ extern "C" int dg_batch_run(dg_batch* b) {
                 CU(mark(DG_STAGE_RESIZE_SHIFT, false));
             }
         }
+    }
+    if (two_lanes) {
+        CU(cudaEventRecord(ctx->ev_join, ctx->stream2));
+        CU(cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
     }
     CU(cudaGetLastError());
     b->ran = true;
@@ -1071,6 +1121,7 @@ extern "C" void dg_batch_destroy(dg_batch* b) {
     for (StageEvent& se : b->events) { cudaEventDestroy(se.a); cudaEventDestroy(se.b); }
     ctx->dev.release(b->blk_persist);
     ctx->dev.release(b->blk_scratch);
+    ctx->dev.release(b->blk_scratch2);
     ctx->pin.release(b->blk_pin);
     ctx->pin.release(b->blk_pin_status);
     delete b;
