@@ -544,7 +544,7 @@ void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t
 
 // ---------------------------------------------------------------------------------------------------------------
 // K3  chroma upsampling + YCbCr -> RGB (16-bit fixed point constants 1.402, 0.34414, 0.71414, 1.772), interleaved
-//     RGB8 out.  A CTA owns 256 x (8 * vs) pixels, a thread 8 pixels of a row (and the same 8 of row + 8).
+//     RGB8 out.  A CTA owns 256 pixels of two MCU rows, a thread 8 pixels of every eighth row of the tile.
 //       4:2:0  triangle filter: every output sample is (9a + 3b + 3c + d + bias) >> 4 over its 2x2 chroma
 //              neighbourhood -- one dp4a on bytes gathered from a shared-memory tile (1-sample halo, clamped to the
 //              real plane extent, which is what the edge rules of the filter amount to);
@@ -614,8 +614,10 @@ struct ChromaPlane {  // per-pixel path
     }
 };
 
+constexpr int kCTileRows = 8 * (int)kColorMcuRows + 2;  // chroma rows of a 4:2:0 tile plus one halo row above and below
+
 __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t first_tile) {
-    __shared__ __align__(16) uint8_t s_c[2][10][kCTileCols];
+    __shared__ __align__(16) uint8_t s_c[2][kCTileRows][kCTileCols];
     __shared__ uint32_t s_img;
     if (threadIdx.x == 0) s_img = owner_of(w.color_tiles, first_tile + blockIdx.x);
     __syncthreads();
@@ -627,17 +629,20 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
     const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
     const int lane = threadIdx.x & 31, rowi = threadIdx.x >> 5;  // 32 column groups x 8 rows
     const int x = (int)tx * (int)kColorTileW + lane * 8;
-    const int y_base = (int)ty * 8 * vs;
+    const int y_base = (int)ty * 8 * vs * (int)kColorMcuRows;
+    const int nsteps = vs * (int)kColorMcuRows;  // a thread converts rows rowi, rowi + 8, ... of the tile
     uint8_t* out = w.out + d.out_off;
     const uint8_t* yp = w.planes + d.plane_off[0];
     const uint32_t ypitch = d.plane_pitch[0];
 
     if (d.ncomp == 1) {  // grayscale: copy the real extent of the luma plane
-        const int y = y_base + rowi;
-        if (x < W && y < H) {
+        if (x >= W) return;
+        const int npx = min(8, W - x);
+        for (int k = 0; k < nsteps; ++k) {
+            const int y = y_base + rowi + 8 * k;
+            if (y >= H) break;
             const uint2 v = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
             uint8_t* o = out + (size_t)y * W + x;
-            const int npx = min(8, W - x);
             if (npx == 8 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) __stcs(reinterpret_cast<uint2*>(o), v);
             else for (int i = 0; i < npx; ++i) o[i] = (uint8_t)((i < 4 ? v.x : v.y) >> (8 * (i & 3)));
         }
@@ -645,22 +650,37 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
     }
     const int dw = (W + hs - 1) / hs, dh = (H + vs - 1) / vs;
     if (hs == 2 && vs == 2 && dw > 2) {
-        // chroma tile: rows cy0-1 .. cy0+8, columns cx0-4 .. cx0+131 as aligned words; s_c column = chroma column - cx0 + 4
-        const int cx0 = (int)tx * (int)(kColorTileW / 2), cy0 = (int)ty * 8;
-        constexpr int kWords = kCTileCols / 4;
-        for (int i = threadIdx.x; i < 2 * 10 * kWords; i += kColorThreads) {
-            const int comp = i / (10 * kWords), rem = i - comp * (10 * kWords);
-            const int r = rem / kWords, wi = rem - r * kWords;
-            const int gy = min(max(cy0 + r - 1, 0), dh - 1);
-            const uint32_t cpitch = d.plane_pitch[1 + comp];
-            const int gw = min(max(cx0 / 4 - 1 + wi, 0), (int)(cpitch / 4) - 1);
-            reinterpret_cast<uint32_t*>(s_c[comp][r])[wi] =
-                __ldg(reinterpret_cast<const uint32_t*>(w.planes + d.plane_off[1 + comp] + (size_t)gy * cpitch) + gw);
+        // chroma tile: rows cy0-1 .. cy0+16, columns cx0-4 .. cx0+131 as aligned words; s_c column = chroma column - cx0 + 4.
+        // Warp q loads tile rows q, q + 8, ... of both components; a lane loads word `lane` and, for two lanes, word 32 + lane.
+        const int cx0 = (int)tx * (int)(kColorTileW / 2), cy0 = (int)ty * 8 * (int)kColorMcuRows;
+        constexpr int kWords = kCTileCols / 4;  // 34
+        const uint32_t cpitch = d.plane_pitch[1];
+        const int wmax = (int)(cpitch / 4) - 1, w0 = cx0 / 4 - 1;
+        const uint8_t* cb_base = w.planes + d.plane_off[1];
+        const uint8_t* cr_base = w.planes + d.plane_off[2];
+#pragma unroll
+        for (int rr = 0; rr < (kCTileRows + 7) / 8; ++rr) {
+            const int r = rowi + 8 * rr;
+            if (r < kCTileRows) {
+                const int gy = min(max(cy0 + r - 1, 0), dh - 1);
+                const uint32_t* gb = reinterpret_cast<const uint32_t*>(cb_base + (size_t)gy * cpitch);
+                const uint32_t* gr = reinterpret_cast<const uint32_t*>(cr_base + (size_t)gy * cpitch);
+                uint32_t* sb = reinterpret_cast<uint32_t*>(s_c[0][r]);
+                uint32_t* sr = reinterpret_cast<uint32_t*>(s_c[1][r]);
+                const int g0 = min(max(w0 + lane, 0), wmax);
+                sb[lane] = __ldg(gb + g0);
+                sr[lane] = __ldg(gr + g0);
+                if (lane < kWords - 32) {
+                    const int g1 = min(max(w0 + 32 + lane, 0), wmax);
+                    sb[32 + lane] = __ldg(gb + g1);
+                    sr[32 + lane] = __ldg(gr + g1);
+                }
+            }
         }
         __syncthreads();
         // replicate the plane's first / last real column into the halo positions
-        if (threadIdx.x < 20) {
-            const int comp = threadIdx.x / 10, r = threadIdx.x - comp * 10;
+        if (threadIdx.x < 2 * kCTileRows) {
+            const int comp = threadIdx.x / kCTileRows, r = threadIdx.x - comp * kCTileRows;
             if (cx0 == 0) s_c[comp][r][3] = s_c[comp][r][4];
             const int last = dw - 1 - cx0;  // tile-local index of the last real column
             if (last >= 0 && last < (int)(kColorTileW / 2)) s_c[comp][r][4 + last + 1] = s_c[comp][r][4 + last];
@@ -669,16 +689,18 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
         if (x >= W) return;
         const int cl = lane * 4 + 4;  // s_c column of this thread's first chroma sample (a word boundary)
         const int npx = min(8, W - x);
-        uint2 yv2[2];
+        uint2 yv4[2 * kColorMcuRows];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int y = min(y_base + rowi + 8 * half, H - 1);
-            yv2[half] = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
+        for (int k = 0; k < 2 * (int)kColorMcuRows; ++k) {
+            const int y = min(y_base + rowi + 8 * k, H - 1);
+            yv4[k] = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
         }
+        uint8_t* orow = out + ((size_t)(y_base + rowi) * W + x) * 3;
+        const size_t ostep = (size_t)8 * W * 3;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int yl = rowi + 8 * half, y = y_base + yl;
-            if (y >= H) break;
+        for (int k = 0; k < 2 * (int)kColorMcuRows; ++k) {
+            const int yl = rowi + 8 * k;
+            if (y_base + yl >= H) break;
             const int cy = (yl >> 1) + 1, far = (yl & 1) ? cy + 1 : cy - 1;
             int32_t cbv[8], crv[8];
 #pragma unroll
@@ -698,36 +720,38 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
                 dst[6] = (int32_t)(dp4a_u(I1, kEven, 8) >> 4); dst[7] = (int32_t)(dp4a_u(Rp, kOdd, 7) >> 4);
             }
             uint32_t px[6];
-            ycc_to_rgb8(yv2[half].x, yv2[half].y, cbv, crv, px);
-            store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
+            ycc_to_rgb8(yv4[k].x, yv4[k].y, cbv, crv, px);
+            store_rgb8(orow + k * ostep, px, npx);
         }
         return;
     }
     if (x >= W) return;
     const int npx = min(8, W - x);
     if (hs == 1 && vs == 1) {
-        const int y = y_base + rowi;
-        if (y >= H) return;
-        const uint2 b = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[1] + (size_t)y * d.plane_pitch[1] + x));
-        const uint2 r = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[2] + (size_t)y * d.plane_pitch[2] + x));
-        int32_t cbv[8], crv[8];
+        for (int k = 0; k < nsteps; ++k) {
+            const int y = y_base + rowi + 8 * k;
+            if (y >= H) break;
+            const uint2 b = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[1] + (size_t)y * d.plane_pitch[1] + x));
+            const uint2 r = __ldg(reinterpret_cast<const uint2*>(w.planes + d.plane_off[2] + (size_t)y * d.plane_pitch[2] + x));
+            int32_t cbv[8], crv[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            cbv[i] = (int32_t)(((i < 4 ? b.x : b.y) >> (8 * (i & 3))) & 255u);
-            crv[i] = (int32_t)(((i < 4 ? r.x : r.y) >> (8 * (i & 3))) & 255u);
+            for (int i = 0; i < 8; ++i) {
+                cbv[i] = (int32_t)(((i < 4 ? b.x : b.y) >> (8 * (i & 3))) & 255u);
+                crv[i] = (int32_t)(((i < 4 ? r.x : r.y) >> (8 * (i & 3))) & 255u);
+            }
+            const uint2 yv = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
+            uint32_t px[6];
+            ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
+            store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
         }
-        const uint2 yv = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
-        uint32_t px[6];
-        ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
-        store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
         return;
     }
     // remaining samplings (4:2:2, 4:4:0, chroma planes at most two samples wide): one pixel at a time
     const ChromaPlane cbp{w.planes + d.plane_off[1], d.plane_pitch[1], dw, dh, hs, vs};
     const ChromaPlane crp{w.planes + d.plane_off[2], d.plane_pitch[2], dw, dh, hs, vs};
 #pragma unroll 1
-    for (int half = 0; half < vs; ++half) {
-        const int y = y_base + rowi + 8 * half;
+    for (int k = 0; k < nsteps; ++k) {
+        const int y = y_base + rowi + 8 * k;
         if (y >= H) break;
 #pragma unroll 1
         for (int i = 0; i < npx; ++i) {
