@@ -466,15 +466,32 @@ __device__ __forceinline__ void dequant_pair(uint32_t cw, uint32_t qw, int32_t& 
 constexpr int32_t kRound1 = 1 << 10, kRound2 = (1 << 17) + (128 << 18);
 constexpr int kIdctThreads = 128;
 
-__global__ void __launch_bounds__(kIdctThreads, 7) k_idct(JpegWave w, uint32_t first, uint32_t count) {
+#ifndef DG_IDCT_MIN_CTAS
+#define DG_IDCT_MIN_CTAS 7
+#endif
+__global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWave w, uint32_t first, uint32_t count) {
     const uint32_t local = blockIdx.x * kIdctThreads + threadIdx.x;
     const bool valid = local < count;
     const uint32_t g = first + (valid ? local : 0);
-    // the coefficient address depends on the block index alone: start these loads before the descriptor look-ups
-    const uint4* src = reinterpret_cast<const uint4*>(w.coef + (size_t)g * 64);
-    uint4 c[8];
+    // A warp's 32 blocks are 4 KB of consecutive coefficients.  They are fetched with eight fully coalesced 16-byte
+    // asynchronous copies per lane into shared memory (one chunk = one block row) while the descriptor look-ups run;
+    // then every lane reads back the eight rows of its own block.  Row r of block b sits at chunk
+    // b * 8 + (r ^ (b & 7)): copy-in and read-back both touch eight different 16-byte bank groups per quarter warp.
+    // (One 16-byte load per lane and row straight from global memory makes every instruction touch 32 lines.)
+    __shared__ __align__(16) uint4 s_coef[kIdctThreads / 32][256];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {
+        const uint32_t warp_first = blockIdx.x * kIdctThreads + warp * 32;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) c[r] = __ldcs(src + r);  // read once: do not keep in L2
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t chunk = i * 32 + lane, bb = chunk >> 3, r = chunk & 7;
+            const uint32_t gb = first + min(warp_first + bb, count - 1);
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&s_coef[warp][bb * 8 + (r ^ (bb & 7))]);
+            const void* src = w.coef + (size_t)gb * 64 + r * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     const uint32_t img = owner_of(w.blocks, g);
     const JpegDesc& d = w.descs[img];
     const uint32_t blk = g - (uint32_t)d.block_off;
@@ -484,6 +501,11 @@ __global__ void __launch_bounds__(kIdctThreads, 7) k_idct(JpegWave w, uint32_t f
     uint32_t comp, bx, by;
     if (k < luma) { comp = 0; const uint32_t ky = k / d.hs; bx = mx * d.hs + (k - ky * d.hs); by = my * d.vs + ky; }
     else { comp = k - luma + 1; bx = mx; by = my; }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    uint4 c[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c[r] = s_coef[warp][lane * 8 + (r ^ (lane & 7))];
     const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
                              c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
     const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
