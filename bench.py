@@ -356,8 +356,15 @@ def main():
     roofline = None
     if top:
         achieved = stages[top].get("gbs")
+        # DRAM bytes per launch: dram__bytes_read + dram__bytes_write of one ncu capture on a 256 / 1024-image case of
+        # this workload (profiles/), expressed per algorithmic byte and scaled to this pass by the units it processes
+        # (traffic grows in proportion to the image count).  The entropy kernels move fewer bytes than the dense
+        # coefficient array they fill: only the sectors that hold non-zero coefficients are written.
+        ncu_bytes_per_algorithmic_byte = {"idct": 0.953, "color": 0.937, "huff_restart": 0.66, "huff_spec": 0.63}
+        ratio = ncu_bytes_per_algorithmic_byte.get(top)
         roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": round(achieved / peak, 4) if achieved else None, "traffic": None, "peak_source": peak_src}
+                    "frac": round(achieved / peak, 4) if achieved else None,
+                    "traffic": int(ratio * bytes_of[top]) if ratio and bytes_of.get(top) else None, "peak_source": peak_src}
     post_ms = stage_ms.get("idct", 0.0) + stage_ms.get("color", 0.0)
     post_bytes = stats["coef_bytes"] + stats["rgb_bytes"]
     post = {"ms": round(post_ms, 3), "bytes": post_bytes, "gbs": round(post_bytes / post_ms / 1e6, 1) if post_ms else None,

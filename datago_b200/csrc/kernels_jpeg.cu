@@ -123,7 +123,7 @@ void launch_unstuff(const JpegWave& w, cudaStream_t s) {
 //
 //  * images with restart intervals: one thread per restart segment; the segment's first MCU and the zero DC
 //    predictors are known, so coefficients are written in a single pass.
-//  * images without: the stream is cut into subsequences of kSubseqBits bits, one thread each.  Thread j decodes
+//  * images without: the stream is cut into subsequences of kSubseqBits (2048) bits, one thread each.  Thread j decodes
 //    from a guessed entry state, then re-decodes from the exit state of thread j-1 until entry(j) == exit(j-1)
 //    for every j (Huffman streams re-synchronise after a few symbols, so this takes 2-3 rounds; the loop is
 //    bounded by the thread count because thread j is final after round j).  A prefix sum over the slots and DC
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
 #define DG_SPEC_THREADS 256
 #endif
 #ifndef DG_SUBSEQ_BITS
-#define DG_SUBSEQ_BITS 1024
+#define DG_SUBSEQ_BITS 2048
 #endif
 #ifndef DG_SPEC_MIN_CTAS
 #define DG_SPEC_MIN_CTAS 6
