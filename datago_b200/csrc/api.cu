@@ -706,6 +706,9 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.groups.back()[1] += it.nblocks;
             wv.groups.back()[3] += ntiles;
         }
+        // longest streams first: one CTA decodes one image, and the launch ends with its slowest CTA
+        std::stable_sort(wv.spec_list.begin(), wv.spec_list.end(),
+                         [&](uint32_t a, uint32_t c) { return wv.descs[a].raw_len > wv.descs[c].raw_len; });
         wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
         size_t o = 0;
         wv.off_us = o; o += align_up(us, 256);
