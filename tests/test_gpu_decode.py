@@ -132,3 +132,42 @@ def test_unstuffing_of_ff_bytes():
 
 def test_empty_batch():
     assert ctx().process([]) == []
+
+
+def test_random_corruption_never_faults_and_never_leaks_into_neighbours():
+    # host-side fault injection only: flipped bits, cut streams, damaged headers.  Every item must end with a status
+    # (ok or an error code), the context must stay usable and intact neighbours must still decode bit-exactly.
+    rng = np.random.default_rng(77)
+    base = [jpeg(rng, 240, 160), jpeg(rng, 240, 160, rst=2), jpeg(rng, 200, 120, "4:4:4", 85), jpeg(rng, 150, 90, None, 80, 0, True)]
+    want = [oracle.jpeg_decode(d) for d in base]
+    items, kinds = [], []
+    for rep in range(60):
+        src = base[rep % len(base)]
+        d = bytearray(src)
+        kind = rep % 5
+        if kind == 0:      # bit flips in the entropy-coded data
+            for pos in rng.integers(len(d) // 3, len(d) - 2, 12):
+                d[pos] ^= 1 << int(rng.integers(0, 8))
+        elif kind == 1:    # truncation at a random point
+            d = d[: int(rng.integers(2, len(d)))]
+        elif kind == 2:    # flips in the headers (tables, frame, scan)
+            for pos in rng.integers(2, min(600, len(d) - 1), 4):
+                d[pos] ^= 1 << int(rng.integers(0, 8))
+        elif kind == 3:    # spurious markers / 0xFF bytes in the stream
+            for pos in rng.integers(len(d) // 2, len(d) - 2, 3):
+                d[pos] = 0xFF
+        items.append(bytes(d) if kind != 4 else src)   # kind 4: untouched control
+        kinds.append(kind)
+    res = ctx().process(items)
+    assert len(res) == len(items)
+    for i, (st, out, _) in enumerate(res):
+        assert 0 <= st <= 11
+        if kinds[i] == 4:
+            assert st == 0
+            assert_same(out, want[i % len(base)], f"control item {i}")
+        if st == 0:
+            assert out is not None and out.shape == want[i % len(base)].shape or kinds[i] == 2
+    # the context still works
+    (st, out, _), = ctx().process([base[0]])
+    assert st == 0
+    assert_same(out, want[0])

@@ -161,3 +161,16 @@ def test_sharding_matches_oracle_and_reference_asserts():
     for k in ["", "a", "000001_0002", "x" * 7, "y" * 8, "z" * 9, "sample/ünï"]:
         assert dg.key_hash(k) == oracle.key_hash(k)
         assert dg.key_rank(k, 8) == oracle.key_hash(k) % 8
+
+
+@settings(max_examples=300, deadline=None)
+@given(data=st.binary(min_size=0, max_size=400), splice=st.integers(0, 700))
+def test_header_parser_survives_garbage(data, splice):
+    # random bytes, and random bytes spliced into a real header: a status or a plan, never a crash
+    real = open(os.path.join(ROOT, "tests", "golden", "jpeg_420_q75_rst2.jpg"), "rb").read()
+    for blob in (data, real[:splice] + data + real[splice + len(data):], real[:splice]):
+        try:
+            info = dg.jpeg_probe(blob)
+            assert info.width > 0 and info.height > 0 and info.scan_offset + info.scan_len == len(blob)
+        except dg.DatagoB200Error as e:
+            assert e.code in (3, 4, 5, 6)
