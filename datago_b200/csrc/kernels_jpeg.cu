@@ -409,7 +409,8 @@ void launch_huff_spec(const JpegWave& w, cudaStream_t s) {
 //     The stage is bound by integer instruction issue, not by HBM, so the kernel is built to execute few
 //     instructions: one thread per block (no exchange between lanes), dequantisation and 16-bit unpacking in one
 //     dp2a per coefficient, rounding constants folded into the even part of each butterfly, saturating pack
-//     instructions, and a reduced butterfly when every block of the warp keeps its energy in the top-left 4x4.
+//     instructions, a reduced butterfly when every block of the warp keeps its energy in the top-left 4x4, and a
+//     constant fill when every block of the warp has nothing but a DC term.
 //     All arithmetic is exact in 32-bit integers, so regrouping the butterflies cannot change a result.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int32_t F_0_298 = 2446, F_0_390 = 3196, F_0_541 = 4433, F_0_765 = 6270, F_0_899 = 7373, F_1_175 = 9633,
@@ -510,10 +511,23 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWav
                              c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
     const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
     const bool sparse = __all_sync(0xFFFFFFFFu, (hi_rows | hi_cols) == 0);
+    const uint32_t ac = (c[0].x >> 16) | c[0].y | c[1].x | c[1].y | c[2].x | c[2].y | c[3].x | c[3].y;
+    const bool dc_only = sparse && __all_sync(0xFFFFFFFFu, ac == 0);
     const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[comp] * 32);
     uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
     const uint32_t pitch = d.plane_pitch[comp];
-    if (sparse) {
+    if (dc_only) {
+        // flat blocks (a quarter of the warps on smooth content): both passes reduce to shifts of the DC term
+        int32_t lo, hi;
+        dequant_pair(c[0].x, __ldg(reinterpret_cast<const uint32_t*>(qq)), lo, hi);
+        const int32_t wsv = (lo * 8192 + kRound1) >> 11;
+        const int32_t v = (wsv * 8192 + kRound2) >> 18;
+        const uint32_t px4 = pack_sat_u8(v, v, v, v);
+        if (valid) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(px4, px4);
+        }
+    } else if (sparse) {
         int32_t x[4][4], ws[8][4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
