@@ -45,8 +45,8 @@ void launch_huff_spec(const JpegWave& w, cudaStream_t s);
 void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s);
 void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s);
 
-// The colour kernel gives one CTA 256 pixels of two MCU rows.
-constexpr uint32_t kColorTileW = 256, kColorMcuRows = 2;
+// The colour kernel gives one CTA 256 pixels of four MCU rows.
+constexpr uint32_t kColorTileW = 256, kColorMcuRows = 4;
 inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) {
     return ((width + kColorTileW - 1) / kColorTileW) * ((mcuy + kColorMcuRows - 1) / kColorMcuRows);
 }

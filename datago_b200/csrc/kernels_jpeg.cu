@@ -725,18 +725,18 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
         if (x >= W) return;
         const int cl = lane * 4 + 4;  // s_c column of this thread's first chroma sample (a word boundary)
         const int npx = min(8, W - x);
-        uint2 yv4[2 * kColorMcuRows];
-#pragma unroll
-        for (int k = 0; k < 2 * (int)kColorMcuRows; ++k) {
-            const int y = min(y_base + rowi + 8 * k, H - 1);
-            yv4[k] = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
-        }
         uint8_t* orow = out + ((size_t)(y_base + rowi) * W + x) * 3;
         const size_t ostep = (size_t)8 * W * 3;
-#pragma unroll
+        const uint8_t* yrow = yp + (size_t)(y_base + rowi) * ypitch + x;
+        const size_t ystep = (size_t)8 * ypitch;
+        uint2 ynext = make_uint2(0, 0);
+        if (y_base + rowi < H) ynext = __ldg(reinterpret_cast<const uint2*>(yrow));
+#pragma unroll 2
         for (int k = 0; k < 2 * (int)kColorMcuRows; ++k) {
             const int yl = rowi + 8 * k;
             if (y_base + yl >= H) break;
+            const uint2 yv = ynext;
+            if (y_base + yl + 8 < H) ynext = __ldg(reinterpret_cast<const uint2*>(yrow + (size_t)(k + 1) * ystep));  // next row's luma in flight
             const int cy = (yl >> 1) + 1, far = (yl & 1) ? cy + 1 : cy - 1;
             int32_t cbv[8], crv[8];
 #pragma unroll
@@ -756,7 +756,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
                 dst[6] = (int32_t)(dp4a_u(I1, kEven, 8) >> 4); dst[7] = (int32_t)(dp4a_u(Rp, kOdd, 7) >> 4);
             }
             uint32_t px[6];
-            ycc_to_rgb8(yv4[k].x, yv4[k].y, cbv, crv, px);
+            ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
             store_rgb8(orow + k * ostep, px, npx);
         }
         return;
