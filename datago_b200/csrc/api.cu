@@ -104,7 +104,9 @@ struct dg_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;   // everything the caller can observe is ordered on this stream
     cudaStream_t stream2 = nullptr;  // odd waves of a batch run here, concurrently with the even ones
+    cudaStream_t aux[2] = {nullptr, nullptr};  // per lane: the restart-interval decoder runs beside the speculative one
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_aux_go[2] = {nullptr, nullptr}, ev_aux_done[2] = {nullptr, nullptr};
     bool own_stream = false;
     bool has_tfm = false;
     dg_image_config cfg{};
@@ -143,7 +145,13 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
     }
     if (cudaStreamCreateWithFlags(&c->stream2, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->aux[0], cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&c->aux[1], cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_aux_go[0], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_aux_go[1], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_aux_done[0], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_aux_done[1], cudaEventDisableTiming) != cudaSuccess) {
         delete c;
         return fail(DG_E_CUDA, "creating the second stream failed");
     }
@@ -166,6 +174,12 @@ extern "C" void dg_ctx_destroy(dg_ctx* c) {
     c->pin.clear();
     cudaEventDestroy(c->ev_fork);
     cudaEventDestroy(c->ev_join);
+    for (int i = 0; i < 2; ++i) {
+        cudaStreamSynchronize(c->aux[i]);
+        cudaEventDestroy(c->ev_aux_go[i]);
+        cudaEventDestroy(c->ev_aux_done[i]);
+        cudaStreamDestroy(c->aux[i]);
+    }
     cudaStreamDestroy(c->stream2);
     if (c->own_stream) cudaStreamDestroy(c->stream);
     delete c;
@@ -950,9 +964,20 @@ extern "C" int dg_batch_run(dg_batch* b) {
             CU(mark(DG_STAGE_COEF_CLEAR, true));
             CU(cudaMemsetAsync(w.coef, 0, wv.coef_blocks * 128, s));
             CU(mark(DG_STAGE_COEF_CLEAR, false));
+            // The two entropy kernels work on disjoint images and are both latency bound: outside timing mode they run
+            // side by side, the restart-interval one on the lane's auxiliary stream.
+            const bool side_by_side = !timing && w.restart_segs.total && w.n_spec;
+            const int lane = (int)(wi & 1);
             if (w.restart_segs.total) {
                 CU(mark(DG_STAGE_HUFF_RESTART, true));
-                launch_huff_restart(w, s);
+                if (side_by_side) {
+                    CU(cudaEventRecord(ctx->ev_aux_go[lane], s));
+                    CU(cudaStreamWaitEvent(ctx->aux[lane], ctx->ev_aux_go[lane], 0));
+                    launch_huff_restart(w, ctx->aux[lane]);
+                    CU(cudaEventRecord(ctx->ev_aux_done[lane], ctx->aux[lane]));
+                } else {
+                    launch_huff_restart(w, s);
+                }
                 ++b->launches;
                 CU(mark(DG_STAGE_HUFF_RESTART, false));
             }
@@ -962,6 +987,7 @@ extern "C" int dg_batch_run(dg_batch* b) {
                 ++b->launches;
                 CU(mark(DG_STAGE_HUFF_SPEC, false));
             }
+            if (side_by_side) CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
             for (const auto& g : wv.groups) {
                 CU(mark(DG_STAGE_IDCT, true));
                 launch_idct(w, g[0], g[1], s);
