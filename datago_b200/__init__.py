@@ -16,6 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 DG_DEVICE_NONE = -1
 BATCH_DECODE_ONLY = 1
 BATCH_TIMING = 2
+BATCH_KEEP_COEFFICIENTS = 4
 STAGES = ("unstuff", "coef_clear", "huff_restart", "huff_spec", "idct", "color", "resize_h", "resize_v", "resize_shift")
 STATUS_NAMES = {0: "ok", 1: "invalid", 2: "cuda", 3: "truncated", 4: "bad_marker", 5: "unsupported", 6: "bad_table",
                 7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large"}
@@ -362,7 +363,8 @@ class Batch:
         return dict(chunks=int(out[0]), rounds=int(out[1]), subsequence_decodes=int(out[2]))
 
     def debug_coefficients(self, i):
-        """int16 [blocks, 64] coefficients of JPEG item i in scan order (single-wave batches, after sync)."""
+        """int16 [blocks, 64] coefficients of JPEG item i in scan order (single-wave batches created with
+        BATCH_KEEP_COEFFICIENTS, after sync)."""
         coef, nb = C.c_void_p(), C.c_uint64()
         _check(lib().dg_batch_debug(self._h, i, C.byref(coef), C.byref(nb), None))
         raw = self.ctx.copy_to_host(coef.value, int(nb.value) * 128)

@@ -56,6 +56,7 @@ struct Block {
     void* ptr = nullptr;
     size_t size = 0;
     bool busy = false;
+    size_t zero_prefix = 0;  // scratch blocks: leading bytes known to be zero (the coefficient region, see dg_batch_run)
 };
 
 // Grow-only cache: a batch borrows blocks and hands them back; nothing is freed before the ctx goes away, so steady
@@ -64,7 +65,7 @@ struct BlockCache {
     bool pinned;
     std::vector<Block> blocks;
     explicit BlockCache(bool p) : pinned(p) {}
-    int acquire(size_t size, int* index) {
+    int acquire(size_t size, int* index, bool keep_zero_prefix = false) {
         if (size == 0) size = 256;
         int best = -1;
         for (size_t i = 0; i < blocks.size(); ++i)
@@ -86,6 +87,7 @@ struct BlockCache {
             else { blocks.push_back(nb); best = (int)blocks.size() - 1; }
         }
         blocks[best].busy = true;
+        if (!keep_zero_prefix) blocks[best].zero_prefix = 0;
         *index = best;
         return DG_OK;
     }
@@ -725,11 +727,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                          [&](uint32_t a, uint32_t c) { return wv.descs[a].raw_len > wv.descs[c].raw_len; });
         wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
         size_t o = 0;
+        wv.off_coef = o; o += align_up(blocks * 128, 256);  // first: the zero prefix of a scratch block is tracked from offset 0
         wv.off_us = o; o += align_up(us, 256);
         wv.off_uslen = o; o += align_up(wv.descs.size() * 4, 256);
         wv.off_segfound = o; o += align_up(wv.descs.size() * 4, 256);
         wv.off_segstart = o; o += align_up(segs * 4, 256);
-        wv.off_coef = o; o += align_up(blocks * 128, 256);
         wv.off_planes = o; o += align_up(planes, 256);
         wv.off_decoded = o; o += align_up(decoded, 256);
         wv.off_mid = o; o += align_up(mids, 256);
@@ -740,12 +742,12 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     // ---- device and pinned blocks (addresses are needed by the resize descriptors) ------------------------------------
     // persistent layout: [status | blob | raw inputs | outputs | meta]; meta size is known only after planning the
     // resize passes, so it gets a bound: descriptors + tables are small next to the pixel buffers.
-    int rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch);
+    int rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch, true);
     if (rc) return abandon(b, rc);
     b->d_scratch = (uint8_t*)ctx->dev.blocks[b->blk_scratch].ptr;
     b->d_scratch2 = b->d_scratch;
     if (b->waves.size() > 1) {
-        rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch2);
+        rc = ctx->dev.acquire(std::max<size_t>(scratch_max, 256), &b->blk_scratch2, true);
         if (rc) return abandon(b, rc);
         b->d_scratch2 = (uint8_t*)ctx->dev.blocks[b->blk_scratch2].ptr;
     }
@@ -892,11 +894,23 @@ static OwnerMap resolve(const dg_batch* b, const OwnerMapOff& o) {
     return m;
 }
 
+static int batch_run_locked(dg_batch* b);
+
 extern "C" int dg_batch_run(dg_batch* b) {
     if (!b) return fail(DG_E_INVALID, "NULL batch");
     if (!b->uploaded) return fail(DG_E_INVALID, "dg_batch_run before dg_batch_upload");
     dg_ctx* ctx = b->ctx;
     std::lock_guard<std::mutex> lock(ctx->mu);
+    const int rc = batch_run_locked(b);
+    if (rc != DG_OK) {  // a pass that stopped half-way leaves no guarantee about the scratch contents
+        if (b->blk_scratch >= 0) ctx->dev.blocks[b->blk_scratch].zero_prefix = 0;
+        if (b->blk_scratch2 >= 0) ctx->dev.blocks[b->blk_scratch2].zero_prefix = 0;
+    }
+    return rc;
+}
+
+static int batch_run_locked(dg_batch* b) {
+    dg_ctx* ctx = b->ctx;
     CU(cudaSetDevice(ctx->device));
     cudaStream_t s = ctx->stream;
     const uint8_t* meta = b->d_persist + b->off_meta;
@@ -931,6 +945,10 @@ extern "C" int dg_batch_run(dg_batch* b) {
     for (size_t wi = 0; wi < b->waves.size(); ++wi) {
         WavePlan& wv = b->waves[wi];
         uint8_t* sc = (wi & 1) ? b->d_scratch2 : b->d_scratch;
+        // everything of the scratch block beyond this wave's coefficient region is about to be overwritten
+        const size_t coef_bytes = wv.coef_blocks * 128;
+        Block& scratch_blk = ctx->dev.blocks[(wi & 1) ? b->blk_scratch2 : b->blk_scratch];
+        if (scratch_blk.zero_prefix > coef_bytes) scratch_blk.zero_prefix = coef_bytes;
         // the scratch block belongs to the lane, so in one-stream mode an odd wave must wait for nothing extra:
         // stream order already serialises the waves
         s = (two_lanes && (wi & 1)) ? ctx->stream2 : ctx->stream;
@@ -961,8 +979,14 @@ extern "C" int dg_batch_run(dg_batch* b) {
             launch_unstuff(w, s);
             ++b->launches;
             CU(mark(DG_STAGE_UNSTUFF, false));
+            // The entropy decoders write only non-zero coefficients, so the coefficient region must be zero beforehand.
+            // The IDCT zeroes the rows it found non-zero after reading them, which keeps the region zero from one wave
+            // to the next on the same scratch block; only a part that was not a coefficient region before is cleared.
+            const bool rezero = !(b->flags & DG_BATCH_KEEP_COEFFICIENTS);
             CU(mark(DG_STAGE_COEF_CLEAR, true));
-            CU(cudaMemsetAsync(w.coef, 0, wv.coef_blocks * 128, s));
+            if (coef_bytes > scratch_blk.zero_prefix)
+                CU(cudaMemsetAsync((uint8_t*)w.coef + scratch_blk.zero_prefix, 0, coef_bytes - scratch_blk.zero_prefix, s));
+            scratch_blk.zero_prefix = rezero ? coef_bytes : 0;
             CU(mark(DG_STAGE_COEF_CLEAR, false));
             // The two entropy kernels work on disjoint images and are both latency bound: outside timing mode they run
             // side by side, the restart-interval one on the lane's auxiliary stream.
@@ -990,7 +1014,7 @@ extern "C" int dg_batch_run(dg_batch* b) {
             if (side_by_side) CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
             for (const auto& g : wv.groups) {
                 CU(mark(DG_STAGE_IDCT, true));
-                launch_idct(w, g[0], g[1], s);
+                launch_idct(w, g[0], g[1], rezero, s);
                 ++b->launches;
                 CU(mark(DG_STAGE_IDCT, false));
                 CU(mark(DG_STAGE_COLOR, true));

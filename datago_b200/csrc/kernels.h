@@ -42,7 +42,9 @@ void launch_huff_restart(const JpegWave& w, cudaStream_t s);
 void launch_huff_spec(const JpegWave& w, cudaStream_t s);
 // blocks [first, first + count) of the wave / colour tiles [first, first + count): callers launch them in groups of a
 // few images so that the planes written by the IDCT are still in L2 when the colour kernel reads them
-void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s);
+// rezero: the kernel writes zeros back over every coefficient row it found non-zero, which leaves the coefficient
+// buffer all-zero again for the next wave that uses it (the entropy decoders only write non-zero coefficients)
+void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s);
 void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s);
 
 // The colour kernel gives one CTA 256 pixels of four MCU rows.

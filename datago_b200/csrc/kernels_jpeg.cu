@@ -470,7 +470,7 @@ constexpr int kIdctThreads = 128;
 #ifndef DG_IDCT_MIN_CTAS
 #define DG_IDCT_MIN_CTAS 7
 #endif
-__global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWave w, uint32_t first, uint32_t count) {
+__global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWave w, uint32_t first, uint32_t count, bool rezero) {
     const uint32_t local = blockIdx.x * kIdctThreads + threadIdx.x;
     const bool valid = local < count;
     const uint32_t g = first + (valid ? local : 0);
@@ -507,6 +507,22 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWav
     uint4 c[8];
 #pragma unroll
     for (int r = 0; r < 8; ++r) c[r] = s_coef[warp][lane * 8 + (r ^ (lane & 7))];
+    if (rezero) {
+        // zero the non-zero rows again, with the same lane <-> chunk assignment as the copy-in so that a warp's stores
+        // fall into its contiguous 4 KB: lane l of step i owns row l % 8 of block 4 * i + l / 8
+        uint32_t rowmask = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
+        if (!valid) rowmask = 0;
+        // base of the warp's 32 blocks, computed from the launch geometry (not from g: lanes past the end of the range
+        // carry a stand-in g); blocks past the end have an empty mask, so nothing outside the range is written
+        uint4* gwarp = reinterpret_cast<uint4*>(w.coef + (size_t)(first + blockIdx.x * kIdctThreads + warp * 32) * 64);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
+            if ((m >> (lane & 7)) & 1u) gwarp[i * 32 + lane] = make_uint4(0, 0, 0, 0);
+        }
+    }
     const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
                              c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
     const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
@@ -574,8 +590,8 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWav
     }
 }
 
-void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s) {
-    if (count) k_idct<<<(count + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w, first, count);
+void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s) {
+    if (count) k_idct<<<(count + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w, first, count, rezero);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

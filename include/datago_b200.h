@@ -98,7 +98,9 @@ typedef struct dg_batch dg_batch;
 
 enum {
     DG_BATCH_DECODE_ONLY = 1u,  /* ignore the ctx transform: payload = decoded image (image_to_payload with img_tfm None) */
-    DG_BATCH_TIMING = 2u        /* record CUDA events around each stage of dg_batch_run */
+    DG_BATCH_TIMING = 2u,       /* record CUDA events around each stage of dg_batch_run */
+    DG_BATCH_KEEP_COEFFICIENTS = 4u /* leave the decoded coefficients in place for dg_batch_debug (they are normally
+                                       zeroed again as they are consumed) */
 };
 
 /* Stages reported by dg_batch_stage_ms. */

@@ -51,7 +51,7 @@ def test_coefficients_bit_exact():
     rng = np.random.default_rng(6)
     datas = [jpeg(rng, 320, 240, "4:2:0", 90, 0), jpeg(rng, 320, 240, "4:2:0", 90, 3), jpeg(rng, 200, 120, "4:4:4", 80, 0),
              jpeg(rng, 150, 100, None, 85, 0, True), jpeg(rng, 1280, 960, "4:2:0", 95, 0, noise=12.0)]
-    with ctx().batch(datas) as b:
+    with ctx().batch(datas, None, dg.BATCH_KEEP_COEFFICIENTS) as b:
         b.upload(); b.run(); b.sync()
         for i, data in enumerate(datas):
             coefs, _, _ = oracle.jpeg_decode_stages(data)
