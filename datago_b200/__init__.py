@@ -17,9 +17,11 @@ DG_DEVICE_NONE = -1
 BATCH_DECODE_ONLY = 1
 BATCH_TIMING = 2
 BATCH_KEEP_COEFFICIENTS = 4
+BATCH_COLLATE = 8
 STAGES = ("unstuff", "coef_clear", "huff_restart", "huff_spec", "idct", "color", "resize_h", "resize_v", "resize_shift")
 STATUS_NAMES = {0: "ok", 1: "invalid", 2: "cuda", 3: "truncated", 4: "bad_marker", 5: "unsupported", 6: "bad_table",
-                7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large"}
+                7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large", 12: "timeout"}
+E_TIMEOUT = 12
 
 
 class DatagoB200Error(RuntimeError):
@@ -68,6 +70,35 @@ class Result(C.Structure):
                 ("nbytes", C.c_uint64), ("device_data", C.c_void_p), ("plan", Plan), ("packed_offset", C.c_uint64)]
 
 
+class Bucket(C.Structure):
+    _fields_ = [("key", C.c_char * 16), ("n", C.c_uint32), ("width", C.c_uint32), ("height", C.c_uint32),
+                ("channels", C.c_uint32), ("nbytes", C.c_uint64), ("device_data", C.c_void_p),
+                ("packed_offset", C.c_uint64), ("items", C.POINTER(C.c_int32))]
+
+
+class FeederConfig(C.Structure):
+    _fields_ = [("lanes", C.c_uint32), ("max_batch", C.c_uint32), ("max_wait_us", C.c_uint32),
+                ("queue_limit", C.c_uint32), ("batch_flags", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class FeederStats(C.Structure):
+    _fields_ = [("submitted", C.c_uint64), ("completed", C.c_uint64), ("failed", C.c_uint64), ("batches", C.c_uint64),
+                ("batched_items", C.c_uint64), ("largest_batch", C.c_uint32), ("queued", C.c_uint32),
+                ("open_tickets", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class DeviceArray:
+    """A dense uint8 array in device memory owned by a batch; speaks __cuda_array_interface__ (version 3), so
+    torch.as_tensor / cupy.asarray wrap it without a copy.  Keep the batch alive while it is in use."""
+
+    def __init__(self, ptr, shape, owner):
+        self.ptr, self.shape, self._owner = int(ptr), tuple(int(v) for v in shape), owner
+
+    @property
+    def __cuda_array_interface__(self):
+        return {"shape": self.shape, "typestr": "|u1", "data": (self.ptr, False), "version": 3, "strides": None}
+
+
 _lib = None
 
 
@@ -109,6 +140,8 @@ def lib():
         "dg_batch_packed_bytes": (C.c_uint64, [vp]),
         "dg_batch_sync": (C.c_int, [vp]),
         "dg_batch_result": (C.c_int, [vp, C.c_int, C.POINTER(Result)]),
+        "dg_batch_bucket_count": (C.c_int, [vp]),
+        "dg_batch_bucket": (C.c_int, [vp, C.c_int, C.POINTER(Bucket)]),
         "dg_batch_stage_ms": (C.c_int, [vp, C.POINTER(C.c_float)]),
         "dg_batch_counters": (C.c_int, [vp, u64p, u64p, u32p]),
         "dg_batch_huffman_stats": (C.c_int, [vp, u64p]),
@@ -116,6 +149,14 @@ def lib():
         "dg_batch_destroy": (None, [vp]),
         "dg_process": (C.c_int, [vp, C.POINTER(Item), C.c_int, C.c_uint32, C.POINTER(vp), C.POINTER(Result)]),
         "dg_copy_to_host": (C.c_int, [vp, vp, vp, C.c_uint64]),
+        "dg_feeder_create": (C.c_int, [C.c_int, C.POINTER(ImageConfig), C.POINTER(FeederConfig), C.POINTER(vp)]),
+        "dg_feeder_ctx": (vp, [vp]),
+        "dg_submit": (C.c_int, [vp, C.POINTER(Item), vp, C.c_uint64, u64p]),
+        "dg_wait": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]),
+        "dg_fetch": (C.c_int, [vp, C.c_uint64, vp, C.c_uint64]),
+        "dg_release": (C.c_int, [vp, C.c_uint64]),
+        "dg_feeder_get_stats": (C.c_int, [vp, C.POINTER(FeederStats)]),
+        "dg_feeder_destroy": (None, [vp]),
         "dg_resize_device_static": (C.c_int, [vp, vp, C.c_uint32, C.c_uint32, C.c_uint32, C.c_char_p, vp, C.POINTER(Plan)]),
     }
     for name, (res, args) in sig.items():
@@ -129,9 +170,10 @@ def lib():
 EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
            "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
-           "dg_batch_download_packed dg_batch_packed_bytes "
+           "dg_batch_download_packed dg_batch_packed_bytes dg_batch_bucket_count dg_batch_bucket "
            "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_huffman_stats dg_batch_debug dg_batch_destroy dg_process "
-           "dg_copy_to_host dg_resize_device_static").split()
+           "dg_copy_to_host dg_resize_device_static dg_feeder_create dg_feeder_ctx dg_submit dg_wait dg_fetch dg_release "
+           "dg_feeder_get_stats dg_feeder_destroy").split()
 
 
 def _check(rc):
@@ -347,6 +389,19 @@ class Batch:
         self._outs = host_buffer
         _check(lib().dg_batch_download_packed(self._h, host_buffer.ctypes.data, host_buffer.nbytes))
 
+    def buckets(self):
+        """Buckets of a BATCH_COLLATE batch: list of dicts with key, shape (n, h, w, c), items (batch indices in
+        storage order), packed_offset and `array`, a DeviceArray over the dense [n, h, w, c] block."""
+        out = []
+        for k in range(lib().dg_batch_bucket_count(self._h)):
+            bk = Bucket()
+            _check(lib().dg_batch_bucket(self._h, k, C.byref(bk)))
+            shape = (bk.n, bk.height, bk.width, bk.channels)
+            out.append(dict(key=bk.key.decode(), shape=shape, items=[int(bk.items[j]) for j in range(bk.n)],
+                            packed_offset=int(bk.packed_offset), nbytes=int(bk.nbytes),
+                            array=DeviceArray(bk.device_data, shape, self)))
+        return out
+
     def stage_ms(self):
         ms = (C.c_float * len(STAGES))()
         _check(lib().dg_batch_stage_ms(self._h, ms))
@@ -377,3 +432,86 @@ class Batch:
         n = r.original_width * r.original_height * r.channels
         raw = self.ctx.copy_to_host(dec.value, n)
         return raw.reshape((r.original_height, r.original_width, 3) if r.channels == 3 else (r.original_height, r.original_width))
+
+
+class Feeder:
+    """Submit / wait front end (dg_feeder): threads submit single samples, the library batches them for the GPU.
+    ctypes releases the GIL inside every call, so Python threads overlap the way datago's tokio workers do."""
+
+    def __init__(self, device=0, image_config=None, lanes=0, max_batch=0, max_wait_us=0, queue_limit=0, flags=0):
+        self._h = C.c_void_p()
+        cfg = ImageConfig.from_dict(image_config) if image_config else None
+        fc = FeederConfig(lanes, max_batch, max_wait_us, queue_limit, flags, 0)
+        _check(lib().dg_feeder_create(device, C.byref(cfg) if cfg is not None else None, C.byref(fc), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().dg_feeder_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def submit(self, x, forced_key=None, host_out=None):
+        """x: bytes (a JPEG file) or a numpy uint8 array HxW / HxWx3.  host_out: optional writable uint8 array the
+        payload is copied into by wait().  Returns the ticket."""
+        it = Item()
+        if isinstance(x, (bytes, bytearray, memoryview)):
+            keep = bytes(x)
+            it.data = C.cast(C.c_char_p(keep), C.c_void_p)
+            it.len = len(keep)
+        else:
+            keep = np.ascontiguousarray(x, np.uint8)
+            it.data = keep.ctypes.data
+            it.len = keep.nbytes
+            it.raw_h, it.raw_w = keep.shape[:2]
+            it.raw_c = 1 if keep.ndim == 2 else keep.shape[2]
+        if forced_key:
+            it.forced_key = forced_key.encode()
+        t = C.c_uint64()
+        _check(lib().dg_submit(self._h, C.byref(it), host_out.ctypes.data if host_out is not None else None,
+                               host_out.nbytes if host_out is not None else 0, C.byref(t)))
+        return int(t.value)
+
+    def wait(self, ticket, timeout_s=None):
+        """Result of the ticket, or None when timeout_s ran out first."""
+        r = Result()
+        ns = 0xFFFFFFFFFFFFFFFF if timeout_s is None else int(timeout_s * 1e9)
+        rc = lib().dg_wait(self._h, ticket, ns, C.byref(r))
+        if rc == E_TIMEOUT:
+            return None
+        _check(rc)
+        return r
+
+    def fetch(self, ticket, result):
+        """The payload of a finished ticket as a numpy array (H x W x 3, or H x W for one channel)."""
+        shape = (result.height, result.width, 3) if result.channels == 3 else (result.height, result.width)
+        out = np.empty(shape, np.uint8)
+        _check(lib().dg_fetch(self._h, ticket, out.ctypes.data, out.nbytes))
+        return out
+
+    def release(self, ticket):
+        _check(lib().dg_release(self._h, ticket))
+
+    def process_one(self, x, forced_key=None):
+        """submit + wait + fetch + release: (status, array or None, Result) -- the blocking call a worker thread makes."""
+        t = self.submit(x, forced_key)
+        try:
+            r = self.wait(t)
+            return r.status, (self.fetch(t, r) if r.status == 0 else None), r
+        finally:
+            self.release(t)
+
+    def stats(self):
+        st = FeederStats()
+        _check(lib().dg_feeder_get_stats(self._h, C.byref(st)))
+        return {k: int(getattr(st, k)) for k, _ in FeederStats._fields_ if k != "reserved"}

@@ -38,6 +38,8 @@ static int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+int dg::dg_set_error(int code, const char* msg) { return fail(code, "%s", msg); }
+
 #define CU(call)                                                                                         \
     do {                                                                                                 \
         cudaError_t e_ = (call);                                                                         \
@@ -322,6 +324,14 @@ struct WavePlan {
 
 struct StageEvent { int stage; cudaEvent_t a, b; };
 
+// One same-shape group of a DG_BATCH_COLLATE batch: its payloads sit back to back, i.e. they are one [n, h, w, c] array.
+struct BucketPlan {
+    char key[16] = {0};
+    uint32_t w = 0, h = 0, c = 0;
+    size_t off = 0;  // in the output arena
+    std::vector<int32_t> items;
+};
+
 }  // namespace
 
 struct dg_batch {
@@ -331,6 +341,7 @@ struct dg_batch {
     std::vector<ItemPlan> items;
     std::vector<JpegHeader> headers;
     std::vector<WavePlan> waves;
+    std::vector<BucketPlan> buckets;
     Meta meta;
     // persistent device block: [meta | status | blob | raw inputs | outputs]
     int blk_persist = -1, blk_scratch = -1, blk_scratch2 = -1, blk_pin = -1, blk_pin_status = -1;
@@ -612,6 +623,31 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         if (it.is_jpeg) blob += align_up(b->headers[i].scan_len, 16) + 16;
         else { it.raw_in_off = rawin; rawin += align_up((size_t)it.w * it.h * it.c, 256); b->raw_src[i] = src.data; }
     }
+    if (flags & DG_BATCH_COLLATE) {
+        // Re-lay the output arena bucket by bucket (buckets in order of first appearance, items in batch order):
+        // payloads of one bucket are packed without gaps, so the bucket is a dense [n, h, w, c] array on the device.
+        for (int i = 0; i < n; ++i) {
+            ItemPlan& it = b->items[i];
+            if (it.status) continue;
+            BucketPlan* bk = nullptr;
+            for (BucketPlan& cand : b->buckets)
+                if (cand.w == it.out_w && cand.h == it.out_h && cand.c == it.c && memcmp(cand.key, it.plan.key, 16) == 0) { bk = &cand; break; }
+            if (!bk) {
+                b->buckets.emplace_back();
+                bk = &b->buckets.back();
+                memcpy(bk->key, it.plan.key, 16);
+                bk->w = it.out_w; bk->h = it.out_h; bk->c = it.c;
+            }
+            bk->items.push_back(i);
+        }
+        outb = 0;
+        for (BucketPlan& bk : b->buckets) {
+            bk.off = outb;
+            const size_t each = (size_t)bk.w * bk.h * bk.c;
+            for (size_t k = 0; k < bk.items.size(); ++k) b->items[bk.items[k]].out_off = bk.off + k * each;
+            outb = align_up(bk.off + bk.items.size() * each, 256);
+        }
+    }
     b->blob_bytes = blob; b->rawin_bytes = rawin; b->out_bytes = outb;
 
     // ---- pass 2: waves ----------------------------------------------------------------------------------------------------
@@ -774,14 +810,18 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             uint8_t* const kBaseS = (wi & 1) ? b->d_scratch2 : b->d_scratch;
             for (int s = 0; s < 4; ++s) { wv.passes[s].clear(); wv.pass_first[s].clear(); }
             wv.copies.clear(); wv.copy_first.clear();
-            if (!transform) continue;
             size_t mid_used = 0;
             for (int i = wv.first_item; i < wv.last_item; ++i) {
                 ItemPlan& it = b->items[i];
                 if (it.status || it.wave < 0) continue;
                 const uint8_t* src = it.is_jpeg ? kBaseS + wv.off_decoded + it.decoded_off : baseP + b->off_rawin + it.raw_in_off;
                 uint8_t* dst = baseP + b->off_out + it.out_off;
-                plan_resize(pl, wv, it.plan, it.c, src, dst, kBaseS + wv.off_mid, &mid_used);
+                if (transform) plan_resize(pl, wv, it.plan, it.c, src, dst, kBaseS + wv.off_mid, &mid_used);
+                else if (!it.is_jpeg) {  // raw pixels, no transform: the payload is the input (JPEGs decode straight into dst)
+                    CopyJob j;
+                    j.src = src; j.dst = dst; j.src_pitch = it.w * it.c; j.row_bytes = it.w * it.c; j.rows = it.h; j.tile_first = 0;
+                    wv.copies.push_back(j);
+                }
             }
             if (mid_used > wv.mid_bytes) return abandon(b, fail(DG_E_INVALID, "internal: resize scratch bound exceeded"));
             for (int s = 0; s < 4; ++s) {
@@ -829,7 +869,9 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             rc = ctx->dev.acquire(b->persist_bytes, &b->blk_persist);
             if (rc) return abandon(b, rc);
             b->d_persist = (uint8_t*)ctx->dev.blocks[b->blk_persist].ptr;
-            if (!transform) break;  // no pointers inside the metadata
+            bool pointers = transform;  // resize passes and copy jobs carry device pointers: lay them out again for real
+            for (const WavePlan& wv : b->waves) pointers = pointers || !wv.copies.empty();
+            if (!pointers) break;
         }
     }
 
@@ -1035,12 +1077,12 @@ static int batch_run_locked(dg_batch* b) {
                 ++b->launches;
                 CU(mark(kStageOf[st], false));
             }
-            if (!wv.copies.empty()) {
-                CU(mark(DG_STAGE_RESIZE_SHIFT, true));
-                launch_copy((const CopyJob*)(meta + wv.m_copies), resolve(b, wv.m_copy), s);
-                ++b->launches;
-                CU(mark(DG_STAGE_RESIZE_SHIFT, false));
-            }
+        }
+        if (!wv.copies.empty()) {
+            CU(mark(DG_STAGE_RESIZE_SHIFT, true));
+            launch_copy((const CopyJob*)(meta + wv.m_copies), resolve(b, wv.m_copy), s);
+            ++b->launches;
+            CU(mark(DG_STAGE_RESIZE_SHIFT, false));
         }
     }
     if (two_lanes) {
@@ -1125,6 +1167,22 @@ extern "C" int dg_batch_result(const dg_batch* b, int i, dg_result* out) {
         out->packed_offset = it.out_off;
     }
     out->plan = it.plan;
+    return DG_OK;
+}
+
+extern "C" int dg_batch_bucket_count(const dg_batch* b) { return b ? (int)b->buckets.size() : 0; }
+
+extern "C" int dg_batch_bucket(const dg_batch* b, int k, dg_bucket* out) {
+    if (!b || !out || k < 0 || k >= (int)b->buckets.size()) return fail(DG_E_INVALID, "bad bucket index (is this a DG_BATCH_COLLATE batch?)");
+    const BucketPlan& bk = b->buckets[k];
+    memset(out, 0, sizeof *out);
+    memcpy(out->key, bk.key, 16);
+    out->n = (uint32_t)bk.items.size();
+    out->width = bk.w; out->height = bk.h; out->channels = bk.c;
+    out->nbytes = (uint64_t)bk.items.size() * bk.w * bk.h * bk.c;
+    out->device_data = b->d_persist + b->off_out + bk.off;
+    out->packed_offset = bk.off;
+    out->items = bk.items.data();
     return DG_OK;
 }
 

@@ -54,6 +54,10 @@ struct JpegHeader {
 int parse_jpeg_header(const uint8_t* data, uint64_t len, JpegHeader& h);  // dg_status
 bool build_huff_table(const JpegHeader::RawHuff& raw, HuffTable& out);
 
+// ---- errors ---------------------------------------------------------------------------------------------------------
+// Stores msg as the calling thread's dg_last_error text and returns code.
+int dg_set_error(int code, const char* msg);
+
 // ---- sharding -------------------------------------------------------------------------------------------------------
 uint64_t siphash13_str(const char* key, uint64_t len);
 

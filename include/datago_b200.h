@@ -42,7 +42,8 @@ typedef enum dg_status {
     DG_E_UNKNOWN_KEY = 8,  /* forced aspect-ratio key is not a bucket (datago panics: image_processing.rs:335) */
     DG_E_NO_TRANSFORM = 9, /* a bucket query on a ctx created without crop_and_resize */
     DG_E_SYNC_LIMIT = 10,  /* entropy decoder did not converge within its iteration cap */
-    DG_E_TOO_LARGE = 11    /* input exceeds a stated size limit */
+    DG_E_TOO_LARGE = 11,   /* input exceeds a stated size limit */
+    DG_E_TIMEOUT = 12      /* dg_wait: the sample has not finished within the given time (the ticket stays valid) */
 } dg_status;
 
 /* image_config of the client JSON: ImageTransformConfig, src/image_processing.rs:43-70 (the fields on this path). */
@@ -93,14 +94,27 @@ typedef struct dg_result {
     uint64_t packed_offset;       /* where dg_batch_download_packed puts this payload, from its host base */
 } dg_result;
 
+/* One bucket of a DG_BATCH_COLLATE batch: n same-shape payloads stored back to back, i.e. one dense uint8
+ * [n][height][width][channels] array -- what a training loop stacks from the `ImagePayload`s of one aspect-ratio
+ * bucket after src/structs.rs:154-188 (to_numpy_array) has copied each of them. */
+typedef struct dg_bucket {
+    char key[16];                /* bucket key; "" for batches without a transform (grouped by decoded shape) */
+    uint32_t n, width, height, channels;
+    uint64_t nbytes;             /* n * height * width * channels */
+    const uint8_t* device_data;  /* device memory owned by the batch */
+    uint64_t packed_offset;      /* where dg_batch_download_packed puts the array, from its host base */
+    const int32_t* items;        /* n batch indices: items[k] is the item stored at position k (batch order kept) */
+} dg_bucket;
+
 typedef struct dg_ctx dg_ctx;
 typedef struct dg_batch dg_batch;
 
 enum {
     DG_BATCH_DECODE_ONLY = 1u,  /* ignore the ctx transform: payload = decoded image (image_to_payload with img_tfm None) */
     DG_BATCH_TIMING = 2u,       /* record CUDA events around each stage of dg_batch_run */
-    DG_BATCH_KEEP_COEFFICIENTS = 4u /* leave the decoded coefficients in place for dg_batch_debug (they are normally
-                                       zeroed again as they are consumed) */
+    DG_BATCH_KEEP_COEFFICIENTS = 4u, /* leave the decoded coefficients in place for dg_batch_debug (they are normally
+                                        zeroed again as they are consumed) */
+    DG_BATCH_COLLATE = 8u       /* lay the payloads out bucket by bucket, see dg_batch_bucket */
 };
 
 /* Stages reported by dg_batch_stage_ms. */
@@ -166,6 +180,11 @@ DG_API int dg_batch_download_packed(dg_batch* b, uint8_t* host_base, uint64_t ca
 DG_API uint64_t dg_batch_packed_bytes(const dg_batch* b);
 DG_API int dg_batch_sync(dg_batch* b);
 DG_API int dg_batch_result(const dg_batch* b, int i, dg_result* out);
+/* Buckets of a DG_BATCH_COLLATE batch, in order of first appearance.  Items that failed belong to no bucket; images and
+ * masks of one key differ in channels and form separate buckets.  Per-item results stay valid (they point into the
+ * bucket arrays).  0 buckets for a batch created without the flag. */
+DG_API int dg_batch_bucket_count(const dg_batch* b);
+DG_API int dg_batch_bucket(const dg_batch* b, int k, dg_bucket* out);
 /* Milliseconds per stage of the last dg_batch_run of a DG_BATCH_TIMING batch (after dg_batch_sync). */
 DG_API int dg_batch_stage_ms(const dg_batch* b, float ms[DG_STAGE_COUNT]);
 /* Bytes copied host->device by upload, and kernels launched by one run. */
@@ -181,6 +200,51 @@ DG_API void dg_batch_destroy(dg_batch* b);
 /* One call doing create + upload + run + download + sync + destroy; results[i] (optional) receive the outcomes
  * (device_data is NULL there: the batch is gone). */
 DG_API int dg_process(dg_ctx* ctx, const dg_item* items, int n, uint32_t flags, uint8_t* const* host_out, dg_result* results);
+
+/* ---- submit / wait: single samples from many threads, batched for the GPU ----------------------------------------
+ * datago calls the decode + image_to_payload pair once per sample from num_cpus tokio worker threads, all at once
+ * (src/worker_files.rs:83-121,150-152; src/worker_wds.rs:183-227; src/worker_http.rs:276-332).  A feeder keeps that
+ * calling pattern: any number of threads call dg_submit / dg_wait concurrently; lane threads inside the feeder gather
+ * the queued samples into batches (up to max_batch, or whatever is there once the oldest sample has waited
+ * max_wait_us) and run them through the batch entry points above, so results are the batch path's results.
+ *   dg_submit   copies the sample's bytes (the caller's buffer is free again on return, like the `&item.buffer` borrow
+ *               of src/worker_wds.rs:45) and returns a ticket; blocks while queue_limit samples are already waiting
+ *               (the bounded-concurrency role of DATAGO_MAX_TASKS).  host_out may be NULL.
+ *   dg_wait     blocks up to timeout_ns (UINT64_MAX: no limit) for the ticket; fills *out.  With a host_out given at
+ *               submit it also copies the payload there, on the calling thread; out->device_data is then NULL.
+ *               Without one, out->device_data points at the payload in device memory until dg_release, and
+ *               dg_fetch copies it to host memory once the caller has sized a buffer from out->nbytes.
+ *   dg_release  ends the ticket (any state); every ticket must be released.  A ticket belongs to one thread at a time.
+ * A sample that fails (bad JPEG, unknown forced key) completes with that status in out->status, as datago logs and drops
+ * such a sample (src/worker_files.rs:63-70); the dg_wait call itself still returns DG_OK. */
+typedef struct dg_feeder dg_feeder;
+typedef uint64_t dg_ticket;
+
+typedef struct dg_feeder_config {  /* zero fields take the default */
+    uint32_t lanes;        /* batches in flight, each with its own context and thread (default 2, at most 8) */
+    uint32_t max_batch;    /* samples per batch (default 512) */
+    uint32_t max_wait_us;  /* longest time a queued sample waits for its batch to fill (default 2000) */
+    uint32_t queue_limit;  /* dg_submit blocks while this many samples are queued (default 4 * max_batch) */
+    uint32_t batch_flags;  /* 0 or DG_BATCH_DECODE_ONLY */
+    uint32_t reserved;
+} dg_feeder_config;
+
+typedef struct dg_feeder_stats {
+    uint64_t submitted, completed, failed; /* failed: completed with a non-zero status */
+    uint64_t batches, batched_items;
+    uint32_t largest_batch, queued, open_tickets, reserved;
+} dg_feeder_stats;
+
+DG_API int dg_feeder_create(int device, const dg_image_config* image_config, const dg_feeder_config* config, dg_feeder** out);
+/* A context with the feeder's transform, for dg_plan_geometry / dg_closest_aspect_ratio / dg_bucket_table queries. */
+DG_API const dg_ctx* dg_feeder_ctx(const dg_feeder* f);
+DG_API int dg_submit(dg_feeder* f, const dg_item* item, uint8_t* host_out, uint64_t host_capacity, dg_ticket* ticket);
+DG_API int dg_wait(dg_feeder* f, dg_ticket ticket, uint64_t timeout_ns, dg_result* out);
+DG_API int dg_fetch(dg_feeder* f, dg_ticket ticket, uint8_t* host_out, uint64_t capacity);
+DG_API int dg_release(dg_feeder* f, dg_ticket ticket);
+DG_API int dg_feeder_get_stats(dg_feeder* f, dg_feeder_stats* out);
+/* Stops the lanes, fails what is still queued, frees everything (device payloads of unreleased tickets included). */
+DG_API void dg_feeder_destroy(dg_feeder* f);
 
 /* crop_and_resize of ONE image that is already in device memory, without any device allocation.
  * No counterpart in datago: it exists for hosts that must not let a library allocate device memory while they run

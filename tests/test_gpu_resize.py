@@ -150,3 +150,18 @@ def test_packed_download_matches_per_item_download():
             if st == 0:
                 assert r.packed_offset % 256 == 0
                 assert np.array_equal(buf[r.packed_offset:r.packed_offset + r.nbytes], want.reshape(-1))
+
+
+def test_raw_input_without_transform_is_returned_unchanged():
+    # image_to_payload with img_tfm None (src/image_processing.rs:354-361 skipped): the payload is the image itself
+    rng = np.random.default_rng(29)
+    raws = [rng.integers(0, 256, (33, 47, 3), dtype=np.uint8), rng.integers(0, 256, (200, 1000), dtype=np.uint8),
+            rng.integers(0, 256, (1, 1, 3), dtype=np.uint8)]
+    mixed = [raws[0], jpeg(rng, 120, 90), raws[1], raws[2]]
+    for c in (ctx(None), ctx(C1)):
+        res = c.process(mixed, None, dg.BATCH_DECODE_ONLY)
+        for i, a in ((0, raws[0]), (2, raws[1]), (3, raws[2])):
+            st, out, r = res[i]
+            assert st == 0 and (r.width, r.height) == (a.shape[1], a.shape[0])
+            assert_same(out, a, f"raw item {i}")
+        assert_same(res[1][1], oracle.jpeg_decode(mixed[1]), "the JPEG beside them")

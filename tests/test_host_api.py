@@ -49,6 +49,11 @@ def test_no_cpu_path_without_a_device():
     ctx = dg.Context(dg.DG_DEVICE_NONE, CFG224)
     with pytest.raises(dg.DatagoB200Error):
         ctx.batch([b"\xff\xd8\xff\xd9"])
+    with pytest.raises(dg.DatagoB200Error) as e:
+        dg.Feeder(0, CFG224)                      # the submit / wait front end has no CPU path either
+    assert "no CPU path" in str(e.value)
+    with pytest.raises(dg.DatagoB200Error):
+        dg.Feeder(dg.DG_DEVICE_NONE, CFG224, lanes=1)
 
 
 def test_reference_known_answers_through_the_c_abi():
