@@ -64,6 +64,13 @@ class Item(C.Structure):
                 ("raw_c", C.c_uint32), ("reserved", C.c_uint32), ("forced_key", C.c_char_p)]
 
 
+class _ItemBytes(C.Structure):
+    """Same layout as Item with `data` typed as char*: assigning a bytes object to it is the cheapest way ctypes
+    offers to take the address of its buffer (and it keeps the object alive)."""
+    _fields_ = [("data", C.c_char_p), ("len", C.c_uint64), ("raw_w", C.c_uint32), ("raw_h", C.c_uint32),
+                ("raw_c", C.c_uint32), ("reserved", C.c_uint32), ("forced_key", C.c_char_p)]
+
+
 class Result(C.Structure):
     _fields_ = [("status", C.c_int32), ("original_width", C.c_uint32), ("original_height", C.c_uint32),
                 ("width", C.c_uint32), ("height", C.c_uint32), ("channels", C.c_uint32), ("bit_depth", C.c_uint32),
@@ -304,13 +311,21 @@ class Batch:
         self.ctx = ctx
         self._n = len(inputs)
         self._items = (Item * max(1, self._n))()
-        self._keep = []
+        as_bytes = (_ItemBytes * max(1, self._n)).from_buffer(self._items)
+        self._keep = [as_bytes]
         for i, x in enumerate(inputs):
+            if type(x) is bytes:
+                it = as_bytes[i]
+                it.data = x
+                it.len = len(x)
+                if forced_keys and forced_keys[i]:
+                    it.forced_key = forced_keys[i].encode()
+                continue
             it = self._items[i]
             if isinstance(x, (bytes, bytearray, memoryview)):
-                buf = (C.c_char * len(x)).from_buffer_copy(bytes(x)) if not isinstance(x, bytes) else x
+                buf = (C.c_char * len(x)).from_buffer_copy(bytes(x))
                 self._keep.append(buf)
-                it.data = C.cast(C.c_char_p(buf) if isinstance(buf, bytes) else buf, C.c_void_p)
+                it.data = C.cast(buf, C.c_void_p)
                 it.len = len(x)
             else:
                 a = np.ascontiguousarray(x, np.uint8)

@@ -375,7 +375,23 @@ struct Planner {
 
     ~Planner() { for (auto* t : tables) delete t; }
 
+    // Most batches repeat a handful of tables (every libjpeg-encoded file carries the same four Huffman tables), so the
+    // tables seen last are compared byte-wise before anything is hashed.
+    std::vector<std::pair<const JpegHeader::RawHuff*, uint32_t>> recent_huff;
+    std::vector<std::pair<const uint16_t*, uint32_t>> recent_qt;
+    template <typename P> static void remember(std::vector<std::pair<P, uint32_t>>& v, P p, uint32_t id) {
+        if (v.size() >= 8) v.pop_back();
+        v.insert(v.begin(), std::make_pair(p, id));
+    }
+
     int huff_id(const JpegHeader::RawHuff& raw, uint32_t* id) {
+        for (const auto& r : recent_huff)
+            if (r.first->count == raw.count && memcmp(r.first->bits, raw.bits, 17) == 0 && memcmp(r.first->vals, raw.vals, (size_t)std::max(raw.count, 0)) == 0) { *id = r.second; return DG_OK; }
+        const int rc = huff_id_slow(raw, id);
+        if (!rc) remember(recent_huff, &raw, *id);
+        return rc;
+    }
+    int huff_id_slow(const JpegHeader::RawHuff& raw, uint32_t* id) {
         std::string key((const char*)raw.bits, 17);
         key.append((const char*)raw.vals, 256);
         auto it = huff_ids.find(key);
@@ -388,6 +404,13 @@ struct Planner {
         return DG_OK;
     }
     uint32_t qt_id(const uint16_t* q) {
+        for (const auto& r : recent_qt)
+            if (memcmp(r.first, q, 128) == 0) return r.second;
+        const uint32_t id = qt_id_slow(q);
+        remember(recent_qt, q, id);
+        return id;
+    }
+    uint32_t qt_id_slow(const uint16_t* q) {
         std::string key((const char*)q, 128);
         auto it = qt_ids.find(key);
         if (it != qt_ids.end()) return it->second;
@@ -566,6 +589,19 @@ static size_t resize_mid_bound(const dg_plan& p, uint32_t C) {
     return align_up(a, 256) + 2 * align_up(b, 256);
 }
 
+// Runs fn(0..n-1) on up to eight host threads (contiguous ranges); small counts stay on the calling thread.
+template <typename F> static void parallel_items(int n, F&& fn) {
+    const unsigned hw = std::thread::hardware_concurrency();
+    const int threads = std::min<int>({8, hw ? (int)hw : 1, n / 128});
+    if (threads <= 1) { for (int i = 0; i < n; ++i) fn(i); return; }
+    std::vector<std::thread> pool;
+    const int per = (n + threads - 1) / threads;
+    for (int t = 1; t < threads; ++t)
+        pool.emplace_back([&fn, t, per, n]() { for (int i = t * per; i < std::min(n, (t + 1) * per); ++i) fn(i); });
+    for (int i = 0; i < std::min(n, per); ++i) fn(i);
+    for (auto& th : pool) th.join();
+}
+
 static int abandon(dg_batch* b, int rc) {
     dg_ctx* ctx = b->ctx;
     ctx->dev.release(b->blk_persist);
@@ -592,36 +628,43 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     Planner pl{ctx, b};
 
     // ---- pass 1: headers, geometry, arena layout -----------------------------------------------------------------------
-    size_t blob = 0, rawin = 0, outb = 0;
-    for (int i = 0; i < n; ++i) {
+    // Header parsing and geometry are independent per item and run on several host threads for large batches; the arena
+    // offsets are then assigned in item order.
+    auto inspect = [&](int i) {
         ItemPlan& it = b->items[i];
         const dg_item& src = items[i];
         it.transform = transform;
-        if (!src.data) { it.status = DG_E_INVALID; continue; }
+        if (!src.data) { it.status = DG_E_INVALID; return; }
         if (src.raw_w) {
-            if (src.raw_h == 0 || (src.raw_c != 1 && src.raw_c != 3) || src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; continue; }
+            if (src.raw_h == 0 || (src.raw_c != 1 && src.raw_c != 3) || src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; return; }
             it.w = src.raw_w; it.h = src.raw_h; it.c = src.raw_c;
         } else {
             JpegHeader& h = b->headers[i];
             it.status = parse_jpeg_header(src.data, src.len, h);
-            if (it.status) continue;
-            if (h.scan_len > 0xFFFFFF00ull) { it.status = DG_E_TOO_LARGE; continue; }
+            if (it.status) return;
+            if (h.scan_len > 0xFFFFFF00ull) { it.status = DG_E_TOO_LARGE; return; }
             it.is_jpeg = true; it.hdr = &h;
             it.w = h.width; it.h = h.height; it.c = h.ncomp == 1 ? 1 : 3;
         }
         if (transform) {
             it.status = plan_geometry(ctx->tfm, it.w, it.h, it.c, src.forced_key, &it.plan);
-            if (it.status) continue;
+            if (it.status) return;
             it.out_w = it.plan.target_w; it.out_h = it.plan.target_h;
         } else {
             it.out_w = it.w; it.out_h = it.h;
             it.plan.src_w = it.w; it.plan.src_h = it.h; it.plan.channels = it.c;
         }
         it.out_bytes = (size_t)it.out_w * it.out_h * it.c;
+    };
+    parallel_items(n, inspect);
+    size_t blob = 0, rawin = 0, outb = 0;
+    for (int i = 0; i < n; ++i) {
+        ItemPlan& it = b->items[i];
+        if (it.status) continue;
         it.out_off = outb;
         outb += align_up(it.out_bytes, 256);
         if (it.is_jpeg) blob += align_up(b->headers[i].scan_len, 16) + 16;
-        else { it.raw_in_off = rawin; rawin += align_up((size_t)it.w * it.h * it.c, 256); b->raw_src[i] = src.data; }
+        else { it.raw_in_off = rawin; rawin += align_up((size_t)it.w * it.h * it.c, 256); b->raw_src[i] = items[i].data; }
     }
     if (flags & DG_BATCH_COLLATE) {
         // Re-lay the output arena bucket by bucket (buckets in order of first appearance, items in batch order):
@@ -884,18 +927,22 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     b->h_status = (uint32_t*)ctx->pin.blocks[b->blk_pin_status].ptr;
     memset(b->h_pin, 0, b->off_blob);
     {
+        std::vector<std::pair<int, size_t>> jobs;  // (item, offset in the blob): same order as the descriptors' raw_off
         size_t off = 0;
         for (WavePlan& wv : b->waves)
             for (int i = wv.first_item; i < wv.last_item; ++i) {
                 const ItemPlan& it = b->items[i];
                 if (it.status || !it.is_jpeg || it.wave_local < 0) continue;
-                const JpegHeader& h = *it.hdr;
-                uint8_t* dst = b->h_pin + b->off_blob + off;
-                memcpy(dst, items[i].data + h.scan_off, h.scan_len);
-                const size_t padded = align_up(h.scan_len, 16) + 16;
-                memset(dst + h.scan_len, 0, padded - h.scan_len);
-                off += padded;
+                jobs.emplace_back(i, off);
+                off += align_up(it.hdr->scan_len, 16) + 16;
             }
+        parallel_items((int)jobs.size(), [&](int k) {
+            const int i = jobs[k].first;
+            const JpegHeader& h = *b->items[i].hdr;
+            uint8_t* dst = b->h_pin + b->off_blob + jobs[k].second;
+            memcpy(dst, items[i].data + h.scan_off, h.scan_len);
+            memset(dst + h.scan_len, 0, align_up(h.scan_len, 16) + 16 - h.scan_len);
+        });
     }
     memcpy(b->h_pin + b->off_blob + align_up(blob, 256), b->meta.bytes.data(), b->meta.bytes.size());
     *out = b;
