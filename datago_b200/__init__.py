@@ -18,7 +18,9 @@ BATCH_DECODE_ONLY = 1
 BATCH_TIMING = 2
 BATCH_KEEP_COEFFICIENTS = 4
 BATCH_COLLATE = 8
-STAGES = ("unstuff", "coef_clear", "huff_restart", "huff_spec", "idct", "color", "resize_h", "resize_v", "resize_shift")
+ITEM_TO_RGB8 = 1
+STAGES = ("unstuff", "coef_clear", "huff_restart", "huff_spec", "idct", "color", "resize_h", "resize_v", "resize_shift",
+          "to_rgb8")
 STATUS_NAMES = {0: "ok", 1: "invalid", 2: "cuda", 3: "truncated", 4: "bad_marker", 5: "unsupported", 6: "bad_table",
                 7: "bad_code", 8: "unknown_key", 9: "no_transform", 10: "sync_limit", 11: "too_large", 12: "timeout"}
 E_TIMEOUT = 12
@@ -61,14 +63,14 @@ class JpegInfo(C.Structure):
 
 class Item(C.Structure):
     _fields_ = [("data", C.c_void_p), ("len", C.c_uint64), ("raw_w", C.c_uint32), ("raw_h", C.c_uint32),
-                ("raw_c", C.c_uint32), ("reserved", C.c_uint32), ("forced_key", C.c_char_p)]
+                ("raw_c", C.c_uint32), ("flags", C.c_uint32), ("forced_key", C.c_char_p)]
 
 
 class _ItemBytes(C.Structure):
     """Same layout as Item with `data` typed as char*: assigning a bytes object to it is the cheapest way ctypes
     offers to take the address of its buffer (and it keeps the object alive)."""
     _fields_ = [("data", C.c_char_p), ("len", C.c_uint64), ("raw_w", C.c_uint32), ("raw_h", C.c_uint32),
-                ("raw_c", C.c_uint32), ("reserved", C.c_uint32), ("forced_key", C.c_char_p)]
+                ("raw_c", C.c_uint32), ("flags", C.c_uint32), ("forced_key", C.c_char_p)]
 
 
 class Result(C.Structure):
@@ -276,12 +278,12 @@ class Context:
         _check(lib().dg_plan_geometry(self._h, w, h, channels, forced_key.encode() if forced_key else None, C.byref(p)))
         return p
 
-    def batch(self, inputs, forced_keys=None, flags=0):
-        return Batch(self, inputs, forced_keys, flags)
+    def batch(self, inputs, forced_keys=None, flags=0, to_rgb8=None):
+        return Batch(self, inputs, forced_keys, flags, to_rgb8)
 
-    def process(self, inputs, forced_keys=None, flags=0):
+    def process(self, inputs, forced_keys=None, flags=0, to_rgb8=None):
         """create + upload + run + download + sync in one go: list of (status, numpy array or None, Result)."""
-        with self.batch(inputs, forced_keys, flags) as b:
+        with self.batch(inputs, forced_keys, flags, to_rgb8) as b:
             b.upload()
             b.run()
             outs = b.download()
@@ -305,23 +307,27 @@ class Context:
 
 
 class Batch:
-    """A batch of samples.  inputs: bytes (JPEG files) or numpy uint8 arrays HxW / HxWx3 (raw pixels)."""
+    """A batch of samples.  inputs: bytes (JPEG files) or numpy uint8 arrays HxW / HxWxC (raw pixels).
+    to_rgb8: True, or one bool per input: datago's `image_to_rgb8` (gray -> RGB, RGBA composited over gray)."""
 
-    def __init__(self, ctx, inputs, forced_keys=None, flags=0):
+    def __init__(self, ctx, inputs, forced_keys=None, flags=0, to_rgb8=None):
         self.ctx = ctx
         self._n = len(inputs)
         self._items = (Item * max(1, self._n))()
         as_bytes = (_ItemBytes * max(1, self._n)).from_buffer(self._items)
         self._keep = [as_bytes]
         for i, x in enumerate(inputs):
+            item_flags = ITEM_TO_RGB8 if (to_rgb8 is True or (to_rgb8 and to_rgb8[i])) else 0
             if type(x) is bytes:
                 it = as_bytes[i]
                 it.data = x
                 it.len = len(x)
+                it.flags = item_flags
                 if forced_keys and forced_keys[i]:
                     it.forced_key = forced_keys[i].encode()
                 continue
             it = self._items[i]
+            it.flags = item_flags
             if isinstance(x, (bytes, bytearray, memoryview)):
                 buf = (C.c_char * len(x)).from_buffer_copy(bytes(x))
                 self._keep.append(buf)
@@ -476,7 +482,7 @@ class Feeder:
         except Exception:
             pass
 
-    def submit(self, x, forced_key=None, host_out=None):
+    def submit(self, x, forced_key=None, host_out=None, to_rgb8=False):
         """x: bytes (a JPEG file) or a numpy uint8 array HxW / HxWx3.  host_out: optional writable uint8 array the
         payload is copied into by wait().  Returns the ticket."""
         it = Item()
@@ -492,6 +498,8 @@ class Feeder:
             it.raw_c = 1 if keep.ndim == 2 else keep.shape[2]
         if forced_key:
             it.forced_key = forced_key.encode()
+        if to_rgb8:
+            it.flags = ITEM_TO_RGB8
         t = C.c_uint64()
         _check(lib().dg_submit(self._h, C.byref(it), host_out.ctypes.data if host_out is not None else None,
                                host_out.nbytes if host_out is not None else 0, C.byref(t)))
@@ -517,9 +525,9 @@ class Feeder:
     def release(self, ticket):
         _check(lib().dg_release(self._h, ticket))
 
-    def process_one(self, x, forced_key=None):
+    def process_one(self, x, forced_key=None, to_rgb8=False):
         """submit + wait + fetch + release: (status, array or None, Result) -- the blocking call a worker thread makes."""
-        t = self.submit(x, forced_key)
+        t = self.submit(x, forced_key, to_rgb8=to_rgb8)
         try:
             r = self.wait(t)
             return r.status, (self.fetch(t, r) if r.status == 0 else None), r

@@ -298,6 +298,9 @@ struct ItemPlan {
     dg_plan plan{};
     uint32_t out_w = 0, out_h = 0;
     size_t out_off = 0, out_bytes = 0;  // in the output arena
+    bool to_rgb = false;                // convert_to_rgb8 follows the pipeline: it writes c channels at pipe_off,
+    uint32_t c_out = 0;                 // the conversion writes the c_out = 3 channel payload at out_off
+    size_t pipe_off = 0;                // where decode / resize / copy put their result (== out_off unless to_rgb)
     size_t raw_in_off = 0;              // raw pixel inputs: offset in the input arena
     JpegHeader* hdr = nullptr;
     int wave = -1, wave_local = -1;     // JPEG index inside its wave
@@ -314,12 +317,14 @@ struct WavePlan {
     std::vector<uint32_t> pass_first[4];
     std::vector<CopyJob> copies;
     std::vector<uint32_t> copy_first;
+    std::vector<ToRgbJob> torgb;
+    std::vector<uint32_t> torgb_first;
     // scratch layout (bytes from the wave scratch base)
     size_t us_bytes = 0, coef_blocks = 0, plane_bytes = 0, decoded_bytes = 0, mid_bytes = 0, nseg = 0;
     size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
     // meta offsets
-    size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0;
-    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy;
+    size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0, m_torgbs = 0;
+    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy, m_torgb;
 };
 
 struct StageEvent { int stage; cudaEvent_t a, b; };
@@ -352,6 +357,7 @@ struct dg_batch {
     uint32_t* h_status = nullptr;   // pinned, n words
     size_t off_meta = 0, off_status = 0, off_blob = 0, off_rawin = 0, off_out = 0, persist_bytes = 0;
     size_t blob_bytes = 0, rawin_bytes = 0, out_bytes = 0, pin_bytes = 0;
+    size_t arena_bytes = 0;  // out_bytes plus the pre-conversion images of DG_ITEM_TO_RGB8 items (never downloaded)
     size_t m_huff = 0, m_qt = 0, m_tables = 0;
     std::vector<const uint8_t*> raw_src;  // caller memory of raw items (valid until upload)
     uint64_t h2d = 0, d2h = 0;
@@ -635,8 +641,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         const dg_item& src = items[i];
         it.transform = transform;
         if (!src.data) { it.status = DG_E_INVALID; return; }
+        const bool want_rgb = (src.flags & DG_ITEM_TO_RGB8) != 0;
         if (src.raw_w) {
-            if (src.raw_h == 0 || (src.raw_c != 1 && src.raw_c != 3) || src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; return; }
+            const bool alpha = src.raw_c == 2 || src.raw_c == 4;
+            if (src.raw_h == 0 || src.raw_c < 1 || src.raw_c > 4 || (alpha && !want_rgb) ||
+                src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; return; }
             it.w = src.raw_w; it.h = src.raw_h; it.c = src.raw_c;
         } else {
             JpegHeader& h = b->headers[i];
@@ -654,7 +663,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             it.out_w = it.w; it.out_h = it.h;
             it.plan.src_w = it.w; it.plan.src_h = it.h; it.plan.channels = it.c;
         }
-        it.out_bytes = (size_t)it.out_w * it.out_h * it.c;
+        // images with an alpha channel would need fast_image_resize's alpha pre-multiplication to be resized
+        if ((it.c == 2 || it.c == 4) && transform && !it.plan.identity) { it.status = DG_E_UNSUPPORTED; return; }
+        it.to_rgb = want_rgb && it.c != 3;
+        it.c_out = it.to_rgb ? 3 : it.c;
+        it.out_bytes = (size_t)it.out_w * it.out_h * it.c_out;
     };
     parallel_items(n, inspect);
     size_t blob = 0, rawin = 0, outb = 0;
@@ -674,12 +687,12 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             if (it.status) continue;
             BucketPlan* bk = nullptr;
             for (BucketPlan& cand : b->buckets)
-                if (cand.w == it.out_w && cand.h == it.out_h && cand.c == it.c && memcmp(cand.key, it.plan.key, 16) == 0) { bk = &cand; break; }
+                if (cand.w == it.out_w && cand.h == it.out_h && cand.c == it.c_out && memcmp(cand.key, it.plan.key, 16) == 0) { bk = &cand; break; }
             if (!bk) {
                 b->buckets.emplace_back();
                 bk = &b->buckets.back();
                 memcpy(bk->key, it.plan.key, 16);
-                bk->w = it.out_w; bk->h = it.out_h; bk->c = it.c;
+                bk->w = it.out_w; bk->h = it.out_h; bk->c = it.c_out;
             }
             bk->items.push_back(i);
         }
@@ -692,6 +705,14 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         }
     }
     b->blob_bytes = blob; b->rawin_bytes = rawin; b->out_bytes = outb;
+    // pre-conversion images live behind the payloads, addressed from the same base
+    size_t arena = align_up(outb, 256);
+    for (ItemPlan& it : b->items) {
+        if (it.status) continue;
+        it.pipe_off = it.out_off;
+        if (it.to_rgb) { it.pipe_off = arena; arena += align_up((size_t)it.out_w * it.out_h * it.c, 256); }
+    }
+    b->arena_bytes = arena;
 
     // ---- pass 2: waves ----------------------------------------------------------------------------------------------------
     // Few, large, equally sized waves: large because the entropy kernels fill the GPU only with hundreds of images per
@@ -780,7 +801,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             d.seg_off = (uint32_t)segs; segs += d.nseg;
             d.item = (uint32_t)i;
             if (transform) { d.out_off = decoded; it.decoded_off = decoded; decoded += align_up((size_t)it.w * it.h * it.c, 256); }
-            else d.out_off = it.out_off;
+            else d.out_off = it.pipe_off;
             it.coef_off_blocks = blocks;
             blocks += it.nblocks;
             it.wave_local = (int)wv.descs.size();
@@ -835,7 +856,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     b->off_blob = align_up((size_t)n * 4 + 32, 256);
     b->off_rawin = b->off_blob + align_up(blob, 256);
     b->off_out = b->off_rawin + align_up(rawin, 256);
-    const size_t fixed_bytes = b->off_out + align_up(outb, 256);
+    const size_t fixed_bytes = b->off_out + align_up(b->arena_bytes, 256);
 
     // Resize descriptors hold device addresses inside the persistent block, whose size depends on the metadata that
     // contains them.  So the passes are planned twice: once against a stand-in base to size the metadata (filter
@@ -853,17 +874,28 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             uint8_t* const kBaseS = (wi & 1) ? b->d_scratch2 : b->d_scratch;
             for (int s = 0; s < 4; ++s) { wv.passes[s].clear(); wv.pass_first[s].clear(); }
             wv.copies.clear(); wv.copy_first.clear();
+            wv.torgb.clear(); wv.torgb_first.clear();
             size_t mid_used = 0;
             for (int i = wv.first_item; i < wv.last_item; ++i) {
                 ItemPlan& it = b->items[i];
                 if (it.status || it.wave < 0) continue;
                 const uint8_t* src = it.is_jpeg ? kBaseS + wv.off_decoded + it.decoded_off : baseP + b->off_rawin + it.raw_in_off;
-                uint8_t* dst = baseP + b->off_out + it.out_off;
+                uint8_t* dst = baseP + b->off_out + it.pipe_off;
+                const uint8_t* converted_from = dst;
                 if (transform) plan_resize(pl, wv, it.plan, it.c, src, dst, kBaseS + wv.off_mid, &mid_used);
                 else if (!it.is_jpeg) {  // raw pixels, no transform: the payload is the input (JPEGs decode straight into dst)
-                    CopyJob j;
-                    j.src = src; j.dst = dst; j.src_pitch = it.w * it.c; j.row_bytes = it.w * it.c; j.rows = it.h; j.tile_first = 0;
-                    wv.copies.push_back(j);
+                    if (it.to_rgb) converted_from = src;  // the conversion reads the input itself
+                    else {
+                        CopyJob j;
+                        j.src = src; j.dst = dst; j.src_pitch = it.w * it.c; j.row_bytes = it.w * it.c; j.rows = it.h; j.tile_first = 0;
+                        wv.copies.push_back(j);
+                    }
+                }
+                if (it.to_rgb) {
+                    ToRgbJob j;
+                    j.src = converted_from; j.dst = baseP + b->off_out + it.out_off; j.npx = it.out_w * it.out_h; j.channels = it.c;
+                    j.tile_first = 0; j.pad = 0;
+                    wv.torgb.push_back(j);
                 }
             }
             if (mid_used > wv.mid_bytes) return abandon(b, fail(DG_E_INVALID, "internal: resize scratch bound exceeded"));
@@ -882,6 +914,13 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                 j.tile_first = t;
                 t += (uint32_t)(((uint64_t)j.row_bytes * j.rows + kCopyTileBytes - 1) / kCopyTileBytes);
                 wv.copy_first.push_back(t);
+            }
+            t = 0;
+            wv.torgb_first.push_back(0);
+            for (ToRgbJob& j : wv.torgb) {
+                j.tile_first = t;
+                t += (j.npx + kToRgbTilePx - 1) / kToRgbTilePx;
+                wv.torgb_first.push_back(t);
             }
         }
         // meta image
@@ -905,6 +944,9 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.m_copies = m.put(wv.copies, 16);
             if (wv.copy_first.empty()) wv.copy_first.push_back(0);
             wv.m_copy = put_owner_map(m, wv.copy_first);
+            wv.m_torgbs = m.put(wv.torgb, 16);
+            if (wv.torgb_first.empty()) wv.torgb_first.push_back(0);
+            wv.m_torgb = put_owner_map(m, wv.torgb_first);
         }
         if (round == 0) {
             b->off_meta = fixed_bytes;
@@ -913,7 +955,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             if (rc) return abandon(b, rc);
             b->d_persist = (uint8_t*)ctx->dev.blocks[b->blk_persist].ptr;
             bool pointers = transform;  // resize passes and copy jobs carry device pointers: lay them out again for real
-            for (const WavePlan& wv : b->waves) pointers = pointers || !wv.copies.empty();
+            for (const WavePlan& wv : b->waves) pointers = pointers || !wv.copies.empty() || !wv.torgb.empty();
             if (!pointers) break;
         }
     }
@@ -1131,6 +1173,12 @@ static int batch_run_locked(dg_batch* b) {
             ++b->launches;
             CU(mark(DG_STAGE_RESIZE_SHIFT, false));
         }
+        if (!wv.torgb.empty()) {
+            CU(mark(DG_STAGE_TO_RGB8, true));
+            launch_to_rgb8((const ToRgbJob*)(meta + wv.m_torgbs), resolve(b, wv.m_torgb), s);
+            ++b->launches;
+            CU(mark(DG_STAGE_TO_RGB8, false));
+        }
     }
     if (two_lanes) {
         CU(cudaEventRecord(ctx->ev_join, ctx->stream2));
@@ -1208,7 +1256,7 @@ extern "C" int dg_batch_result(const dg_batch* b, int i, dg_result* out) {
     out->status = it.status;
     out->original_width = it.w; out->original_height = it.h;
     if (it.status == DG_OK) {
-        out->width = it.out_w; out->height = it.out_h; out->channels = it.c; out->bit_depth = 8;
+        out->width = it.out_w; out->height = it.out_h; out->channels = it.c_out; out->bit_depth = 8;
         out->nbytes = it.out_bytes;
         out->device_data = b->d_persist + b->off_out + it.out_off;
         out->packed_offset = it.out_off;
@@ -1266,7 +1314,7 @@ extern "C" int dg_batch_debug(const dg_batch* b, int i, const int16_t** coef, ui
     if (coef) *coef = (const int16_t*)(b->d_scratch + wv.off_coef) + it.coef_off_blocks * 64;
     if (nblocks) *nblocks = it.nblocks;
     const bool transform = b->ctx->has_tfm && !(b->flags & DG_BATCH_DECODE_ONLY);
-    if (decoded) *decoded = transform ? b->d_scratch + wv.off_decoded + it.decoded_off : b->d_persist + b->off_out + it.out_off;
+    if (decoded) *decoded = transform ? b->d_scratch + wv.off_decoded + it.decoded_off : b->d_persist + b->off_out + it.pipe_off;
     return DG_OK;
 }
 

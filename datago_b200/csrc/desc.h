@@ -82,4 +82,10 @@ struct CopyJob {  // identity payloads / pitch removal
     uint32_t src_pitch, row_bytes, rows, tile_first;
 };
 
+struct ToRgbJob {  // convert_to_rgb8 of one payload: channels 1, 2 or 4 -> 3
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t npx, channels, tile_first, pad;
+};
+
 }  // namespace dg

@@ -46,7 +46,7 @@ struct Ticket {
     int state = 0;  // 0 queued, 1 taken by a lane, 2 done
     bool orphan = false, fetched = false;
     std::vector<uint8_t> bytes;
-    uint32_t raw_w = 0, raw_h = 0, raw_c = 0;
+    uint32_t raw_w = 0, raw_h = 0, raw_c = 0, flags = 0;
     std::string key;
     uint8_t* host_out = nullptr;
     uint64_t host_cap = 0;
@@ -166,7 +166,7 @@ void lane_main(dg_feeder* f, Lane* lane) {
             Ticket* t = group[i];
             items[i].data = t->bytes.data();
             items[i].len = t->bytes.size();
-            items[i].raw_w = t->raw_w; items[i].raw_h = t->raw_h; items[i].raw_c = t->raw_c;
+            items[i].raw_w = t->raw_w; items[i].raw_h = t->raw_h; items[i].raw_c = t->raw_c; items[i].flags = t->flags;
             items[i].forced_key = t->key.empty() ? nullptr : t->key.c_str();
         }
         dg_batch* batch = nullptr;
@@ -246,7 +246,7 @@ extern "C" int dg_submit(dg_feeder* f, const dg_item* item, uint8_t* host_out, u
     if (item->raw_w && item->len < (uint64_t)item->raw_w * item->raw_h * item->raw_c) return set_error(DG_E_INVALID, "raw item shorter than its size says");
     std::unique_ptr<Ticket> t(new Ticket());
     t->bytes.assign(item->data, item->data + item->len);  // the caller's buffer is free again when this call returns
-    t->raw_w = item->raw_w; t->raw_h = item->raw_h; t->raw_c = item->raw_c;
+    t->raw_w = item->raw_w; t->raw_h = item->raw_h; t->raw_c = item->raw_c; t->flags = item->flags;
     if (item->forced_key) t->key = item->forced_key;
     t->host_out = host_out; t->host_cap = host_capacity;
     std::unique_lock<std::mutex> lock(f->mu);

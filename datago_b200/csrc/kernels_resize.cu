@@ -280,4 +280,47 @@ void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s) {
     if (map.total) k_copy<<<map.total, 256, 0, s>>>(jobs, map);
 }
 
+// ---- convert_to_rgb8 (datago src/image_processing.rs:163-186) -------------------------------------------------------
+// One thread per pixel, 2048 pixels per CTA.  Gray: the value in all three channels.  RGBA: source-over compositing on
+// an opaque (128,128,128) background in f32 on values scaled to 0..1, scaled back by 255 and truncated -- each
+// operation rounded once (the _rn intrinsics keep the compiler from fusing a multiply into an add), in the order the
+// `image` crate's Pixel::blend uses, so that the result equals a CPU evaluation of the same expression bit for bit.
+__global__ void __launch_bounds__(256) k_to_rgb8(const ToRgbJob* jobs, OwnerMap map) {
+    const uint32_t ji = owner_of_tile(map, blockIdx.x);
+    const ToRgbJob& j = jobs[ji];
+    const uint32_t base = (blockIdx.x - j.tile_first) * kToRgbTilePx;
+    for (uint32_t k = threadIdx.x; k < kToRgbTilePx; k += 256) {
+        const uint32_t i = base + k;
+        if (i >= j.npx) break;
+        uint8_t* d = j.dst + (size_t)i * 3;
+        if (j.channels <= 2) {
+            const uint8_t v = __ldg(j.src + (size_t)i * j.channels);
+            d[0] = v; d[1] = v; d[2] = v;
+            continue;
+        }
+        const uint32_t px = __ldg(reinterpret_cast<const uint32_t*>(j.src) + i);  // RGBA rows are 4-byte aligned
+        const uint32_t a = px >> 24;
+        uint32_t c[3] = {px & 255u, (px >> 8) & 255u, (px >> 16) & 255u};
+        if (a == 0) { c[0] = c[1] = c[2] = 128; }
+        else if (a != 255) {
+            const float max_t = 255.0f;
+            const float bg_a = __fdiv_rn(255.0f, max_t), fg_a = __fdiv_rn((float)a, max_t);
+            const float alpha_final = __fsub_rn(__fadd_rn(bg_a, fg_a), __fmul_rn(bg_a, fg_a));
+            const float bg_pre = __fmul_rn(__fdiv_rn(128.0f, max_t), bg_a);
+            const float keep = __fsub_rn(1.0f, fg_a);
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) {
+                const float fg_pre = __fmul_rn(__fdiv_rn((float)c[ch], max_t), fg_a);
+                const float out_pre = __fadd_rn(fg_pre, __fmul_rn(bg_pre, keep));
+                c[ch] = (uint32_t)__fmul_rn(max_t, __fdiv_rn(out_pre, alpha_final));  // float -> u32 truncates
+            }
+        }
+        d[0] = (uint8_t)c[0]; d[1] = (uint8_t)c[1]; d[2] = (uint8_t)c[2];
+    }
+}
+
+void launch_to_rgb8(const ToRgbJob* jobs, OwnerMap map, cudaStream_t s) {
+    if (map.total) k_to_rgb8<<<map.total, 256, 0, s>>>(jobs, map);
+}
+
 }  // namespace dg

@@ -77,11 +77,22 @@ typedef struct dg_jpeg_info {
 typedef struct dg_item {
     const uint8_t* data;   /* JPEG file bytes, or raw interleaved 8-bit pixels when raw_w > 0 (host memory) */
     uint64_t len;
-    uint32_t raw_w, raw_h, raw_c; /* raw input: size and channels (1 or 3); 0 for JPEG input */
-    uint32_t reserved;
+    uint32_t raw_w, raw_h, raw_c; /* raw input: size and channels (1 = L8, 3 = RGB8; 2 = LA8 and 4 = RGBA8 only with
+                                     DG_ITEM_TO_RGB8 and no resize); 0 for JPEG input */
+    uint32_t flags;        /* DG_ITEM_* */
     const char* forced_key; /* NULL or "": bucket chosen from the image's own aspect ratio; else the key to force
                                (the "same bucket for every payload of a sample" rule, src/worker_wds.rs:68-76) */
 } dg_item;
+
+/* dg_item.flags.
+ * DG_ITEM_TO_RGB8: ImageEncoding.img_to_rgb8 (`image_to_rgb8` of the client JSON, src/image_processing.rs:27,63): after
+ * crop_and_resize a payload that is not RGB8 is converted by convert_to_rgb8 (:163-186, applied at :366-372):
+ * one-channel images repeat their value in three channels, RGBA is composited over an opaque (128,128,128)
+ * background (source-over in f32, truncated to 8 bits), and the payload reports channels = 3.  datago sets it for
+ * the main image and never for masks / additional images (src/worker_http.rs:188-192).  RGBA and LA inputs are
+ * accepted only when nothing has to be resized: datago resizes them with alpha pre-multiplication inside
+ * fast_image_resize, which this library does not restate (DG_E_UNSUPPORTED). */
+enum { DG_ITEM_TO_RGB8 = 1u };
 
 /* Per-item outcome: the fields of ImagePayload (src/structs.rs:52-71) plus where the pixels are. */
 typedef struct dg_result {
@@ -119,7 +130,7 @@ enum {
 
 /* Stages reported by dg_batch_stage_ms. */
 enum { DG_STAGE_UNSTUFF = 0, DG_STAGE_COEF_CLEAR, DG_STAGE_HUFF_RESTART, DG_STAGE_HUFF_SPEC, DG_STAGE_IDCT, DG_STAGE_COLOR,
-       DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V, DG_STAGE_RESIZE_SHIFT, DG_STAGE_COUNT };
+       DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V, DG_STAGE_RESIZE_SHIFT, DG_STAGE_TO_RGB8, DG_STAGE_COUNT };
 
 DG_API const char* dg_last_error(void);
 DG_API const char* dg_version(void);

@@ -68,6 +68,7 @@ def lib():
         _lib.orc_run_batch.argtypes = [C.POINTER(Item), C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_double,
                                        C.c_double, C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
         _lib.orc_aspect_ratio_to_str.argtypes = [C.c_uint32, C.c_uint32, C.c_char_p]
+        _lib.orc_to_rgb8.argtypes = [C.c_void_p, C.c_uint64, C.c_int, C.c_void_p]
     return _lib
 
 
@@ -147,6 +148,16 @@ def crop_and_resize(cfg, src, forced_key=None, mode=MODE_FIR):
                                    dst.ctypes.data, C.byref(p), mode)
     assert rc == 0
     return dst, p
+
+
+def to_rgb8(src):
+    """convert_to_rgb8 of an HxW or HxWxC uint8 image (C = 1..4): HxWx3."""
+    src = np.ascontiguousarray(src, np.uint8)
+    h, w = src.shape[:2]
+    c = 1 if src.ndim == 2 else src.shape[2]
+    dst = np.empty((h, w, 3), np.uint8)
+    assert lib().orc_to_rgb8(src.ctypes.data, h * w, c, dst.ctypes.data) == 0
+    return dst
 
 
 def jpeg_info(data: bytes):

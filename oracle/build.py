@@ -11,7 +11,7 @@ OUT = os.path.join(HERE, "liboracle.so")
 def build(force: bool = False) -> str:
     if not force and os.path.exists(OUT) and os.path.getmtime(OUT) >= os.path.getmtime(SRC):
         return OUT
-    cmd = ["g++", "-O3", "-march=x86-64-v3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+    cmd = ["g++", "-O3", "-march=x86-64-v3", "-std=c++17", "-ffp-contract=off", "-fPIC", "-shared", "-fvisibility=hidden",
            "-pthread", "-o", OUT, SRC]
     subprocess.run(cmd, check=True)
     return OUT

@@ -350,6 +350,40 @@ ORC_API int orc_crop_and_resize(uint32_t size, uint32_t ratio, double mn, double
     return 0;
 }
 
+// convert_to_rgb8 (image_processing.rs:163-186), applied by image_to_payload after crop_and_resize when
+// `img_to_rgb8` is set and the image is not RGB8 already (:366-372).
+//   1 channel (Luma8): the `image` crate's to_rgb8 repeats the value in all three channels (pinned by :891-904);
+//   2 channels (LumaA8): the same on the luma byte, alpha dropped;
+//   3 channels: unchanged (:907-920);
+//   4 channels (Rgba8): every pixel is composited over an opaque (128,128,128) background with the crate's
+//     `Pixel::blend`: source-over in f32 on values scaled to 0..1, the result scaled back by 255 and converted to
+//     u8 by truncation; alpha 255 copies the pixel, alpha 0 keeps the background.  The reference's own test
+//     (:847-888) pins alpha 0 / 255 exactly and (200,100,50,128) -> (164,114,89) within 2; the f32 operation order
+//     below is a restatement of the published algorithm, PARITY UNPINNED beyond that test.
+// Compiled with -ffp-contract=off: every operation rounds once, as the Rust code does.
+ORC_API int orc_to_rgb8(const uint8_t* src, uint64_t npx, int C, uint8_t* dst) {
+    if (C < 1 || C > 4) return 1;
+    const float max_t = 255.0f;
+    for (uint64_t i = 0; i < npx; ++i) {
+        const uint8_t* s = src + i * (uint64_t)C;
+        uint8_t* d = dst + i * 3;
+        if (C <= 2) { d[0] = d[1] = d[2] = s[0]; continue; }
+        if (C == 3) { d[0] = s[0]; d[1] = s[1]; d[2] = s[2]; continue; }
+        if (s[3] == 255) { d[0] = s[0]; d[1] = s[1]; d[2] = s[2]; continue; }
+        if (s[3] == 0) { d[0] = d[1] = d[2] = 128; continue; }
+        const float bg_a = 255.0f / max_t, fg_a = (float)s[3] / max_t;
+        const float alpha_final = bg_a + fg_a - bg_a * fg_a;
+        for (int c = 0; c < 3; ++c) {
+            const float bg = 128.0f / max_t, fg = (float)s[c] / max_t;
+            const float bg_pre = bg * bg_a, fg_pre = fg * fg_a;
+            const float out_pre = fg_pre + bg_pre * (1.0f - fg_a);
+            const float out = out_pre / alpha_final;
+            d[c] = (uint8_t)(max_t * out);
+        }
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------------------
 // 3. Baseline JPEG decode
 // ---------------------------------------------------------------------------

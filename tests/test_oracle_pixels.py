@@ -110,3 +110,21 @@ def test_crop_and_resize_half_pixel_crop():
     mid = oracle.resample(a, (0, 0, 300, 200), (272, 181))
     want = oracle.resample(mid, (0.0, 2.5, 272.0, 176.0), (272, 176))
     assert np.array_equal(out, want)
+
+
+def test_to_rgb8_reference_known_answers():
+    # datago src/image_processing.rs:847-920: opaque kept, transparent -> (128,128,128), (200,100,50,128) within 2 of
+    # (164,114,89); gray repeated; RGB unchanged
+    rgba = np.array([[[255, 100, 50, 255], [200, 100, 50, 128], [255, 0, 0, 0]]], np.uint8)
+    out = oracle.to_rgb8(rgba)
+    assert out[0, 0].tolist() == [255, 100, 50] and out[0, 2].tolist() == [128, 128, 128]
+    assert np.all(np.abs(out[0, 1].astype(int) - [164, 114, 89]) <= 2)
+    assert oracle.to_rgb8(np.array([[100]], np.uint8))[0, 0].tolist() == [100, 100, 100]
+    assert oracle.to_rgb8(np.array([[[255, 100, 50]]], np.uint8))[0, 0].tolist() == [255, 100, 50]
+    # against exact rational source-over: never more than one step away (f32 rounding + truncation)
+    rng = np.random.default_rng(5)
+    a = rng.integers(0, 256, (64, 64, 4), dtype=np.uint8)
+    al = a[:, :, 3:4].astype(np.float64) / 255.0
+    exact = a[:, :, :3] * al + 128.0 * (1.0 - al)
+    d = oracle.to_rgb8(a).astype(np.float64) - exact
+    assert d.max() <= 0.01 and d.min() > -1.01
