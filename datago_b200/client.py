@@ -324,7 +324,10 @@ class DatagoClient:
         made = 0
         if not inputs and not units:
             return 0
-        batch = self.ctx.batch(inputs, keys, 0 if has_tfm else BATCH_DECODE_ONLY)
+        # `image_to_rgb8` of image_config applies to every image payload the file and webdataset workers produce
+        # (src/worker_files.rs:19-30, src/worker_wds.rs:45-53 pass the client's ImageEncoding unchanged)
+        to_rgb8 = True if (self.image_config or {}).get("image_to_rgb8") else None
+        batch = self.ctx.batch(inputs, keys, 0 if has_tfm else BATCH_DECODE_ONLY, to_rgb8=to_rgb8)
         batch.upload()
         batch.run()
         outs = None if self.device_payloads else batch.download()

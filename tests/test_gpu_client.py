@@ -140,3 +140,18 @@ def test_device_payloads_are_zero_copy_tensors(tmp_path):
     want, _ = oracle.jpeg_to_payload(d, CFG)
     assert np.array_equal(t.cpu().numpy(), want)
     assert np.array_equal(torch.from_dlpack(s.image).cpu().numpy(), want)
+
+
+def test_image_to_rgb8_config_key_turns_gray_files_into_rgb(tmp_path):
+    # src/worker_files.rs:385-413: a gray file with img_to_rgb8 comes back with three equal channels
+    rng = np.random.default_rng(57)
+    g = jpeg(rng, 150, 100, gray=True)
+    (tmp_path / "g.jpg").write_bytes(g)
+    for flag, channels in ((True, 3), (False, 1)):
+        cfg = dict(source_type="file", source_config=dict(root_path=str(tmp_path)),
+                   image_config=dict(CFG, image_to_rgb8=flag), limit=4, samples_buffer_size=2)
+        (s,) = _drain(DatagoClient(json.dumps(cfg)))
+        want, p = oracle.crop_and_resize(CFG, oracle.jpeg_decode(g))
+        assert (s.image.channels, s.image.width, s.image.height) == (channels, p.target_w, p.target_h)
+        got = s.image.to_numpy_array()
+        assert np.array_equal(got, oracle.to_rgb8(want) if flag else want.reshape(got.shape))
