@@ -100,7 +100,7 @@ class ClockSampler:
 
 
 def workload_stats(items, workload):
-    """Pixels and algorithmic bytes of one pass (per-unit figures: see DESIGN.md)."""
+    """Pixels and algorithmic bytes of one pass: coefficients 2 B per MCU-padded sample, planes 1 B per sample, RGB 3 B per pixel."""
     import datago_b200 as dg
     st = dict(images=len(items), pixels=0, compressed=0, coef_bytes=0, plane_bytes=0, rgb_bytes=0, ecs_bits=0)
     for it in items:
@@ -167,6 +167,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c0", "c1", "c2"])
     ap.add_argument("--images", type=int, default=0)
     ap.add_argument("--e2e-chunk", type=int, default=1024)
+    ap.add_argument("--feeder-threads", type=int, default=4, help="worker threads of the submit / wait measurement (0: skip)")
     ap.add_argument("--contexts", type=int, default=1, help="library contexts the resident workload is split over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -370,6 +371,60 @@ def main():
                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                   "note": "payloads stay on the device, collated per bucket; not the headline e2e"}
 
+    # Same host-to-host job through the per-sample front end: worker threads submit single samples and wait for
+    # them, as datago's tokio workers would; the library cuts the batches (two lanes of up to 512 samples).
+    import threading
+    n_workers = args.feeder_threads
+    feeder_value = None
+    if n_workers > 0:
+        flags = dg.BATCH_DECODE_ONLY if not (cfg and cfg.get("crop_and_resize")) else 0
+        with dg.Feeder(local_rank, cfg, lanes=2, max_batch=min(chunk, 512), max_wait_us=2000, queue_limit=4 * chunk, flags=flags) as feeder:
+            # samples each worker keeps in flight; few Python threads with deep queues, because threads that take turns
+            # on the interpreter lock are slower than the library (a Rust or C++ host has no such limit)
+            depth = 128
+
+            def worker(k):
+                # each worker keeps `depth` samples in flight and reads every payload where the library's download
+                # left it (dg_peek: page-locked host memory), touching its first and last byte
+                mine = list(range(k, len(items), n_workers))
+                pending = []
+
+                def finish(t):
+                    r = feeder.wait(t)
+                    assert r.status == 0
+                    px = feeder.peek(t, r)
+                    assert px.size == r.nbytes and int(px.flat[0]) + int(px.flat[-1]) >= 0
+                    feeder.release(t)
+
+                for i in mine:
+                    if len(pending) == depth:
+                        finish(pending.pop(0))
+                    pending.append(feeder.submit(items[i]))
+                for t in pending:
+                    finish(t)
+
+            def feeder_pass():
+                ths = [threading.Thread(target=worker, args=(k,)) for k in range(n_workers)]
+                for th in ths:
+                    th.start()
+                for th in ths:
+                    th.join()
+
+            feeder_pass()  # warm-up
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                feeder_pass()
+            fs = time.perf_counter() - t0
+            barrier()
+            st = feeder.stats()
+        t = torch.tensor([fs], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        feeder_value = {"value": world * len(items) * e2e_steps / float(t.item()), "unit": "images/s", "threads": n_workers, "in_flight": n_workers * depth,
+                        "mean_batch": round(st["batched_items"] / max(1, st["batches"]), 1),
+                        "note": "per-sample dg_submit / dg_wait / dg_peek from Python worker threads, payloads in the library's page-locked host buffers; not the headline e2e"}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -410,22 +465,45 @@ def main():
                     "frac": round(achieved / peak, 4) if achieved else None,
                     "traffic": int(ratio * bytes_of[top]) if ratio and bytes_of.get(top) else None, "peak_source": peak_src}
     post_ms = stage_ms.get("idct", 0.0) + stage_ms.get("color", 0.0)
+    roofline_top = top
     post_bytes = stats["coef_bytes"] + stats["rgb_bytes"]
     post = {"ms": round(post_ms, 3), "bytes": post_bytes, "gbs": round(post_bytes / post_ms / 1e6, 1) if post_ms else None,
             "frac": round(post_bytes / post_ms / 1e6 / peak, 4) if post_ms else None}
+    # crop_and_resize: C * P_used + C * tw * th per image, P_used = the source pixels that map into the crop
+    resize = None
+    resize_ms = stage_ms.get("resize_h", 0.0) + stage_ms.get("resize_v", 0.0) + stage_ms.get("resize_shift", 0.0)
+    if cfg and cfg.get("crop_and_resize") and resize_ms > 0:
+        import math
+        rbytes = 0
+        for it in items:
+            if isinstance(it, (bytes, bytearray)):
+                i = dg.jpeg_probe(it)
+                w_, h_, c_ = i.width, i.height, i.channels
+            else:
+                h_, w_ = it.shape[:2]
+                c_ = 1 if it.ndim == 2 else it.shape[2]
+            p = ctx.plan_geometry(w_, h_, c_)
+            scale = max(p.target_w / w_, p.target_h / h_)
+            used = min(w_, math.ceil(p.target_w / scale)) * min(h_, math.ceil(p.target_h / scale))
+            rbytes += c_ * used + c_ * p.target_w * p.target_h
+        resize = {"ms": round(resize_ms, 3), "bytes": rbytes, "gbs": round(rbytes / resize_ms / 1e6, 1),
+                  "frac": round(rbytes / resize_ms / 1e6 / peak, 4)}
     huff_ms = stage_ms.get("huff_restart", 0.0) + stage_ms.get("huff_spec", 0.0)
     sm_mhz = clocks.get("sm_mhz") or 1965.0
     huff = {"ms": round(huff_ms, 3),
             "bits_per_cycle_per_sm": round(stats["compressed"] * 8 / (huff_ms / 1000.0 * sm_mhz * 1e6 * 148), 4) if huff_ms else None}
 
+    if roofline and roofline_top and roofline_top.startswith("resize") and resize:
+        # the resize passes share one algorithmic figure (source pixels used + payload), reported over their sum
+        roofline.update({"kernel": "resize_h+resize_v+resize_shift", "achieved": resize["gbs"], "frac": resize["frac"]})
     line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u8", "data": "synthetic", "config": config,
             "mpix_per_s": value * stats["pixels"] / len(items) / 1e6,
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": e2e_h2d, "d2h_bytes_per_step": e2e_d2h,
                     "steps": e2e_steps, "batch": chunk, "streams": 2},
-            "e2e_device_payloads": e2e_device,
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "stages": stages, "post_entropy": post,
+            "e2e_device_payloads": e2e_device, "e2e_feeder": feeder_value,
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "stages": stages, "post_entropy": post, "resize": resize,
             "huffman": huff, "stage_pass": {"ms_serial_sum": round(serial_ms, 3), "note": "stages timed in a one-stream pass over the whole workload; value is timed with the workload split over `contexts` contexts, each overlapping its waves on two streams"}}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(items, kind, cfg)

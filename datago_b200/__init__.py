@@ -163,6 +163,7 @@ def lib():
         "dg_submit": (C.c_int, [vp, C.POINTER(Item), vp, C.c_uint64, u64p]),
         "dg_wait": (C.c_int, [vp, C.c_uint64, C.c_uint64, C.POINTER(Result)]),
         "dg_fetch": (C.c_int, [vp, C.c_uint64, vp, C.c_uint64]),
+        "dg_peek": (C.c_int, [vp, C.c_uint64, C.POINTER(vp)]),
         "dg_release": (C.c_int, [vp, C.c_uint64]),
         "dg_feeder_get_stats": (C.c_int, [vp, C.POINTER(FeederStats)]),
         "dg_feeder_destroy": (None, [vp]),
@@ -181,7 +182,7 @@ EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ct
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
            "dg_batch_download_packed dg_batch_packed_bytes dg_batch_bucket_count dg_batch_bucket "
            "dg_batch_result dg_batch_stage_ms dg_batch_counters dg_batch_huffman_stats dg_batch_debug dg_batch_destroy dg_process "
-           "dg_copy_to_host dg_resize_device_static dg_feeder_create dg_feeder_ctx dg_submit dg_wait dg_fetch dg_release "
+           "dg_copy_to_host dg_resize_device_static dg_feeder_create dg_feeder_ctx dg_submit dg_wait dg_fetch dg_peek dg_release "
            "dg_feeder_get_stats dg_feeder_destroy").split()
 
 
@@ -521,6 +522,14 @@ class Feeder:
         out = np.empty(shape, np.uint8)
         _check(lib().dg_fetch(self._h, ticket, out.ctypes.data, out.nbytes))
         return out
+
+    def peek(self, ticket, result):
+        """The payload of a finished ticket as a numpy view of the feeder's own page-locked host buffer (no copy);
+        valid until release()."""
+        ptr = C.c_void_p()
+        _check(lib().dg_peek(self._h, ticket, C.byref(ptr)))
+        shape = (result.height, result.width, 3) if result.channels == 3 else (result.height, result.width)
+        return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(int(result.nbytes),)).reshape(shape)
 
     def release(self, ticket):
         _check(lib().dg_release(self._h, ticket))

@@ -318,6 +318,20 @@ extern "C" int dg_fetch(dg_feeder* f, dg_ticket id, uint8_t* host_out, uint64_t 
     return copy_out(t, fl, host_out, capacity);
 }
 
+extern "C" int dg_peek(dg_feeder* f, dg_ticket id, const uint8_t** host_data) {
+    if (!f || !host_data) return set_error(DG_E_INVALID, "NULL argument");
+    *host_data = nullptr;
+    std::lock_guard<std::mutex> lock(f->mu);
+    auto it = f->tickets.find(id);
+    if (it == f->tickets.end() || it->second->orphan) return set_error(DG_E_INVALID, "unknown ticket");
+    const Ticket* t = it->second.get();
+    if (t->state != 2) return set_error(DG_E_INVALID, "ticket not finished: call dg_wait first");
+    if (t->res.status) return set_error(t->res.status, "the sample failed: there is no payload");
+    if (!t->flight) return set_error(DG_E_INVALID, "payload already handed over (host buffer given at submit)");
+    *host_data = t->flight->pinned + t->res.packed_offset;
+    return DG_OK;
+}
+
 extern "C" int dg_release(dg_feeder* f, dg_ticket id) {
     if (!f) return set_error(DG_E_INVALID, "NULL feeder");
     std::lock_guard<std::mutex> lock(f->mu);

@@ -252,9 +252,13 @@ DG_API const dg_ctx* dg_feeder_ctx(const dg_feeder* f);
 DG_API int dg_submit(dg_feeder* f, const dg_item* item, uint8_t* host_out, uint64_t host_capacity, dg_ticket* ticket);
 DG_API int dg_wait(dg_feeder* f, dg_ticket ticket, uint64_t timeout_ns, dg_result* out);
 DG_API int dg_fetch(dg_feeder* f, dg_ticket ticket, uint8_t* host_out, uint64_t capacity);
+/* The payload where the feeder's own device -> host copy left it (page-locked host memory of the library), valid until
+ * dg_release: lets a caller consume the pixels without a second host copy. */
+DG_API int dg_peek(dg_feeder* f, dg_ticket ticket, const uint8_t** host_data);
 DG_API int dg_release(dg_feeder* f, dg_ticket ticket);
 DG_API int dg_feeder_get_stats(dg_feeder* f, dg_feeder_stats* out);
-/* Stops the lanes, fails what is still queued, frees everything (device payloads of unreleased tickets included). */
+/* Stops the lanes, fails what is still queued, frees everything (device payloads of unreleased tickets included).
+ * No other call on the feeder may be in progress or follow. */
 DG_API void dg_feeder_destroy(dg_feeder* f);
 
 /* crop_and_resize of ONE image that is already in device memory, without any device allocation.

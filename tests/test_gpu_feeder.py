@@ -77,6 +77,8 @@ def test_host_buffer_at_submit_device_payload_and_forced_key():
         got = ctx.copy_to_host(r.device_data, r.nbytes).reshape(r.height, r.width, 3)
         assert_same(got, _want(CFG224, samples[1], "1.900"), "device payload")
         assert_same(f.fetch(t, r), got, "fetch")
+        view = f.peek(t, r)                       # the library's own page-locked copy, no second host copy
+        assert_same(np.array(view), got, "peek")
         f.release(t)
         ctx.close()
         # (c) too small a buffer is an error of the call, the ticket survives and can be fetched
