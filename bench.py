@@ -167,7 +167,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c0", "c1", "c2"])
     ap.add_argument("--images", type=int, default=0)
     ap.add_argument("--e2e-chunk", type=int, default=1024)
-    ap.add_argument("--feeder-threads", type=int, default=4, help="worker threads of the submit / wait measurement (0: skip)")
+    ap.add_argument("--feeder-threads", type=int, default=16, help="worker threads of the submit / wait measurement (0: skip)")
     ap.add_argument("--contexts", type=int, default=1, help="library contexts the resident workload is split over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -379,8 +379,8 @@ def main():
     if n_workers > 0:
         flags = dg.BATCH_DECODE_ONLY if not (cfg and cfg.get("crop_and_resize")) else 0
         with dg.Feeder(local_rank, cfg, lanes=2, max_batch=min(chunk, 512), max_wait_us=2000, queue_limit=4 * chunk, flags=flags) as feeder:
-            # samples each worker keeps in flight; few Python threads with deep queues, because threads that take turns
-            # on the interpreter lock are slower than the library (a Rust or C++ host has no such limit)
+            # samples each worker keeps in flight: the batches fill to what arrives within max_wait_us, so the workers
+            # have to keep a few hundred samples outstanding between them
             depth = 128
 
             def worker(k):

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <array>
 #include <cmath>
 #include <cstdarg>
@@ -359,7 +360,7 @@ struct dg_batch {
     size_t blob_bytes = 0, rawin_bytes = 0, out_bytes = 0, pin_bytes = 0;
     size_t arena_bytes = 0;  // out_bytes plus the pre-conversion images of DG_ITEM_TO_RGB8 items (never downloaded)
     size_t m_huff = 0, m_qt = 0, m_tables = 0;
-    std::vector<const uint8_t*> raw_src;  // caller memory of raw items (valid until upload)
+    std::vector<const uint8_t*> raw_src;  // caller memory of raw items (used inside dg_batch_create only)
     uint64_t h2d = 0, d2h = 0;
     uint32_t launches = 0;
     bool uploaded = false, ran = false;
@@ -960,8 +961,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         }
     }
 
-    // ---- pinned staging: [status zeros | blob] + meta ----------------------------------------------------------------
-    b->pin_bytes = b->off_blob + align_up(blob, 256) + align_up(b->meta.bytes.size(), 256);
+    // ---- pinned staging: [status zeros | blob | raw pixel inputs] + meta ------------------------------------------
+    // Raw inputs are staged too: a copy from pageable caller memory is serialised by the driver at a fraction of the
+    // link rate, while host threads fill page-locked memory in parallel and the upload becomes one large transfer.
+    const size_t staged_head = b->off_rawin + align_up(rawin, 256);
+    b->pin_bytes = staged_head + align_up(b->meta.bytes.size(), 256);
     rc = ctx->pin.acquire(b->pin_bytes, &b->blk_pin);
     if (!rc) rc = ctx->pin.acquire(std::max<size_t>((size_t)n * 4, 256), &b->blk_pin_status);
     if (rc) return abandon(b, rc);
@@ -986,7 +990,27 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             memset(dst + h.scan_len, 0, align_up(h.scan_len, 16) + 16 - h.scan_len);
         });
     }
-    memcpy(b->h_pin + b->off_blob + align_up(blob, 256), b->meta.bytes.data(), b->meta.bytes.size());
+    if (rawin) {
+        struct Piece { uint8_t* dst; const uint8_t* src; size_t len; };
+        std::vector<Piece> pieces;  // 4 MB pieces, so that a few large images still spread over the threads
+        for (int i = 0; i < n; ++i) {
+            const ItemPlan& it = b->items[i];
+            if (it.status || it.is_jpeg || !b->raw_src[i]) continue;
+            const size_t bytes = (size_t)it.w * it.h * it.c;
+            for (size_t o = 0; o < bytes; o += (size_t)4 << 20)
+                pieces.push_back({b->h_pin + b->off_rawin + it.raw_in_off + o, b->raw_src[i] + o, std::min(bytes - o, (size_t)4 << 20)});
+        }
+        const unsigned hw = std::thread::hardware_concurrency();
+        const size_t threads = std::min<size_t>({8, hw ? hw : 1, pieces.size()});
+        std::atomic<size_t> next{0};
+        auto work = [&]() { for (size_t k; (k = next.fetch_add(1)) < pieces.size();) memcpy(pieces[k].dst, pieces[k].src, pieces[k].len); };
+        std::vector<std::thread> pool;
+        for (size_t t = 1; t < threads; ++t) pool.emplace_back(work);
+        work();
+        for (auto& th : pool) th.join();
+    }
+    b->raw_src.clear();  // caller memory is not needed after this call
+    memcpy(b->h_pin + staged_head, b->meta.bytes.data(), b->meta.bytes.size());
     *out = b;
     return DG_OK;
 }
@@ -997,21 +1021,13 @@ extern "C" int dg_batch_upload(dg_batch* b) {
     std::lock_guard<std::mutex> lock(ctx->mu);
     CU(cudaSetDevice(ctx->device));
     b->h2d = 0;
-    // status zeros + compressed blob
-    const size_t head = b->off_blob + align_up(b->blob_bytes, 256);
+    // status zeros + compressed blob + raw pixel inputs (contiguous in the staging buffer and on the device)
+    const size_t head = b->off_rawin + align_up(b->rawin_bytes, 256);
     CU(cudaMemcpyAsync(b->d_persist, b->h_pin, head, cudaMemcpyHostToDevice, ctx->stream));
     b->h2d += head;
     // metadata
     CU(cudaMemcpyAsync(b->d_persist + b->off_meta, b->h_pin + head, b->meta.bytes.size(), cudaMemcpyHostToDevice, ctx->stream));
     b->h2d += b->meta.bytes.size();
-    // raw pixel inputs straight from caller memory
-    for (int i = 0; i < b->n; ++i) {
-        const ItemPlan& it = b->items[i];
-        if (it.status || it.is_jpeg || !b->raw_src[i]) continue;
-        const size_t bytes = (size_t)it.w * it.h * it.c;
-        CU(cudaMemcpyAsync(b->d_persist + b->off_rawin + it.raw_in_off, b->raw_src[i], bytes, cudaMemcpyHostToDevice, ctx->stream));
-        b->h2d += bytes;
-    }
     b->uploaded = true;
     return DG_OK;
 }
