@@ -211,6 +211,10 @@ def main():
     import datago_b200 as dg
 
     torch.cuda.set_device(local_rank)
+    # stdout carries the one JSON line: keep NCCL's own banner (NCCL_DEBUG=VERSION) and debug text off it
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
