@@ -610,20 +610,22 @@ constexpr int kCTileCols = kColorTileW / 2 + 8;  // 4 bytes of left margin (halo
 
 __device__ __forceinline__ uint32_t dp4a_u(uint32_t a, uint32_t b, uint32_t c) { return __dp4a(a, b, c); }
 
-// 8 pixels: luma words y0, y1; chroma values cb[i], cr[i]; out: 24 bytes
+// 8 pixels: luma words y0, y1; chroma values cb[i] - 128, cr[i] - 128; out: 24 bytes.
+// R = Y + ((91881 * (cr - 128) + 32768) >> 16) = (91881 * (cr - 128) + ((Y << 16) + 32768)) >> 16, and likewise for G and
+// B: the luma byte is moved into bits 16..23 of a word that already carries the rounding term (one byte permute per
+// pixel), so each channel is one multiply-add per chroma term and one shift.
 __device__ __forceinline__ void ycc_to_rgb8(uint32_t y0, uint32_t y1, const int32_t (&cb)[8], const int32_t (&cr)[8], uint32_t (&out)[6]) {
-    constexpr int32_t kR = 32768 - 91881 * 128, kG = 32768 + 22554 * 128 + 46802 * 128, kB = 32768 - 116130 * 128;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {  // four pixels at a time keeps fewer values live
         const uint32_t yw = h ? y1 : y0;
         int32_t v[12];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t sel = 1u << (8 * i);
+            const int32_t y16 = (int32_t)__byte_perm(yw, 0x00008000u, 0x7054u | ((uint32_t)i << 8));  // 0x00YY8000
             const int32_t b = cb[4 * h + i], r = cr[4 * h + i];
-            v[3 * i] = (int32_t)dp4a_u(yw, sel, (uint32_t)((r * 91881 + kR) >> 16));
-            v[3 * i + 1] = (int32_t)dp4a_u(yw, sel, (uint32_t)((b * -22554 + (r * -46802 + kG)) >> 16));
-            v[3 * i + 2] = (int32_t)dp4a_u(yw, sel, (uint32_t)((b * 116130 + kB) >> 16));
+            v[3 * i] = (r * 91881 + y16) >> 16;
+            v[3 * i + 1] = (b * -22554 + (r * -46802 + y16)) >> 16;
+            v[3 * i + 2] = (b * 116130 + y16) >> 16;
         }
 #pragma unroll
         for (int j = 0; j < 3; ++j) out[3 * h + j] = pack_sat_u8(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
@@ -766,10 +768,12 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
                 const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
                 constexpr uint32_t kEven = 0x03090103u, kOdd = 0x01030309u;  // weights per byte: even pixel / odd pixel
                 int32_t* dst = comp ? crv : cbv;
-                dst[0] = (int32_t)(dp4a_u(Lp, kEven, 8) >> 4); dst[1] = (int32_t)(dp4a_u(I0, kOdd, 7) >> 4);
-                dst[2] = (int32_t)(dp4a_u(I0, kEven, 8) >> 4); dst[3] = (int32_t)(dp4a_u(J, kOdd, 7) >> 4);
-                dst[4] = (int32_t)(dp4a_u(J, kEven, 8) >> 4);  dst[5] = (int32_t)(dp4a_u(I1, kOdd, 7) >> 4);
-                dst[6] = (int32_t)(dp4a_u(I1, kEven, 8) >> 4); dst[7] = (int32_t)(dp4a_u(Rp, kOdd, 7) >> 4);
+                // the chroma offset of 128 rides in the rounding term: (s + 8 - 2048) >> 4 = ((s + 8) >> 4) - 128
+                constexpr uint32_t kE = (uint32_t)(8 - 2048), kO = (uint32_t)(7 - 2048);
+                dst[0] = (int32_t)dp4a_u(Lp, kEven, kE) >> 4; dst[1] = (int32_t)dp4a_u(I0, kOdd, kO) >> 4;
+                dst[2] = (int32_t)dp4a_u(I0, kEven, kE) >> 4; dst[3] = (int32_t)dp4a_u(J, kOdd, kO) >> 4;
+                dst[4] = (int32_t)dp4a_u(J, kEven, kE) >> 4;  dst[5] = (int32_t)dp4a_u(I1, kOdd, kO) >> 4;
+                dst[6] = (int32_t)dp4a_u(I1, kEven, kE) >> 4; dst[7] = (int32_t)dp4a_u(Rp, kOdd, kO) >> 4;
             }
             uint32_t px[6];
             ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
@@ -788,8 +792,8 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
             int32_t cbv[8], crv[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                cbv[i] = (int32_t)(((i < 4 ? b.x : b.y) >> (8 * (i & 3))) & 255u);
-                crv[i] = (int32_t)(((i < 4 ? r.x : r.y) >> (8 * (i & 3))) & 255u);
+                cbv[i] = (int32_t)(((i < 4 ? b.x : b.y) >> (8 * (i & 3))) & 255u) - 128;
+                crv[i] = (int32_t)(((i < 4 ? r.x : r.y) >> (8 * (i & 3))) & 255u) - 128;
             }
             const uint2 yv = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
             uint32_t px[6];
