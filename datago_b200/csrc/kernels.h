@@ -50,7 +50,9 @@ void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaSt
 // The colour kernel gives one CTA 256 pixels of four MCU rows.
 constexpr uint32_t kColorTileW = 256, kColorMcuRows = 4;
 inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) {
-    return ((width + kColorTileW - 1) / kColorTileW) * ((mcuy + kColorMcuRows - 1) / kColorMcuRows);
+    // one more row of tiles than the MCU rows need: the 4:2:0 path shifts its tiles up by one pixel row, so that every
+    // pair of output rows that shares its two chroma rows falls into one tile
+    return ((width + kColorTileW - 1) / kColorTileW) * (mcuy / kColorMcuRows + 1);
 }
 
 // ---- resize ---------------------------------------------------------------------------------------------------------

@@ -743,41 +743,53 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
         if (x >= W) return;
         const int cl = lane * 4 + 4;  // s_c column of this thread's first chroma sample (a word boundary)
         const int npx = min(8, W - x);
-        uint8_t* orow = out + ((size_t)(y_base + rowi) * W + x) * 3;
-        const size_t ostep = (size_t)8 * W * 3;
-        const uint8_t* yrow = yp + (size_t)(y_base + rowi) * ypitch + x;
-        const size_t ystep = (size_t)8 * ypitch;
-        uint2 ynext = make_uint2(0, 0);
-        if (y_base + rowi < H) ynext = __ldg(reinterpret_cast<const uint2*>(yrow));
-#pragma unroll 2
-        for (int k = 0; k < 2 * (int)kColorMcuRows; ++k) {
-            const int yl = rowi + 8 * k;
-            if (y_base + yl >= H) break;
-            const uint2 yv = ynext;
-            if (y_base + yl + 8 < H) ynext = __ldg(reinterpret_cast<const uint2*>(yrow + (size_t)(k + 1) * ystep));  // next row's luma in flight
-            const int cy = (yl >> 1) + 1, far = (yl & 1) ? cy + 1 : cy - 1;
-            int32_t cbv[8], crv[8];
+        // Output rows 2j+1 and 2j+2 read the same two chroma rows (j and j+1) with the near / far weights exchanged, so
+        // the tile is shifted up by one row -- it covers rows 64 ty - 1 .. 64 ty + 62 -- and a thread converts such a
+        // pair at a time: the byte gathering is done once, the second row only swaps the weights.
+        const int y_first = (int)ty * 8 * 2 * (int)kColorMcuRows - 1;
+        constexpr uint32_t kEvenA = 0x03090103u, kOddA = 0x01030309u;  // bytes: (near a, far a, near b, far b)
+        constexpr uint32_t kEvenB = 0x09030301u, kOddB = 0x03010903u;  // the same bytes with near and far exchanged
+        constexpr uint32_t kE = (uint32_t)(8 - 2048), kO = (uint32_t)(7 - 2048);  // rounding term minus 128 * 16
+        auto luma = [&](int y) -> uint2 {
+            return (y >= 0 && y < H) ? __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x)) : make_uint2(0, 0);
+        };
+        uint2 nextA = luma(y_first + 2 * rowi), nextB = luma(y_first + 2 * rowi + 1);
+#pragma unroll 1
+        for (int m = 0; m < (int)kColorMcuRows; ++m) {
+            const int p = rowi + 8 * m;  // pair index inside the tile = s_c row of the upper chroma row
+            const int yA = y_first + 2 * p, yB = yA + 1;
+            if (yA >= H) break;
+            const uint2 ya = nextA, yb = nextB;
+            if (m + 1 < (int)kColorMcuRows) { nextA = luma(yA + 16); nextB = luma(yB + 16); }  // next pair's luma in flight
+            int32_t cbA[8], crA[8], cbB[8], crB[8];
 #pragma unroll
             for (int comp = 0; comp < 2; ++comp) {
-                const uint32_t* nr = reinterpret_cast<const uint32_t*>(&s_c[comp][cy][cl]);
-                const uint32_t* fr = reinterpret_cast<const uint32_t*>(&s_c[comp][far][cl]);
+                const uint32_t* nr = reinterpret_cast<const uint32_t*>(&s_c[comp][p][cl]);
+                const uint32_t* fr = reinterpret_cast<const uint32_t*>(&s_c[comp][p + 1][cl]);
                 const uint32_t Ln = nr[-1], Mn = nr[0], Nn = nr[1], Lf = fr[-1], Mf = fr[0], Nf = fr[1];
-                // interleaved pairs of columns: bytes (near a, far a, near b, far b)
                 const uint32_t I0 = __byte_perm(Mn, Mf, 0x5140), J = __byte_perm(Mn, Mf, 0x6251), I1 = __byte_perm(Mn, Mf, 0x7362);
                 const uint32_t Lp = __byte_perm(__byte_perm(Ln, Lf, 0x0073), I0, 0x5410);  // (c-1, c)
                 const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
-                constexpr uint32_t kEven = 0x03090103u, kOdd = 0x01030309u;  // weights per byte: even pixel / odd pixel
-                int32_t* dst = comp ? crv : cbv;
-                // the chroma offset of 128 rides in the rounding term: (s + 8 - 2048) >> 4 = ((s + 8) >> 4) - 128
-                constexpr uint32_t kE = (uint32_t)(8 - 2048), kO = (uint32_t)(7 - 2048);
-                dst[0] = (int32_t)dp4a_u(Lp, kEven, kE) >> 4; dst[1] = (int32_t)dp4a_u(I0, kOdd, kO) >> 4;
-                dst[2] = (int32_t)dp4a_u(I0, kEven, kE) >> 4; dst[3] = (int32_t)dp4a_u(J, kOdd, kO) >> 4;
-                dst[4] = (int32_t)dp4a_u(J, kEven, kE) >> 4;  dst[5] = (int32_t)dp4a_u(I1, kOdd, kO) >> 4;
-                dst[6] = (int32_t)dp4a_u(I1, kEven, kE) >> 4; dst[7] = (int32_t)dp4a_u(Rp, kOdd, kO) >> 4;
+                int32_t* da = comp ? crA : cbA;
+                int32_t* db = comp ? crB : cbB;
+                da[0] = (int32_t)dp4a_u(Lp, kEvenA, kE) >> 4; da[1] = (int32_t)dp4a_u(I0, kOddA, kO) >> 4;
+                da[2] = (int32_t)dp4a_u(I0, kEvenA, kE) >> 4; da[3] = (int32_t)dp4a_u(J, kOddA, kO) >> 4;
+                da[4] = (int32_t)dp4a_u(J, kEvenA, kE) >> 4;  da[5] = (int32_t)dp4a_u(I1, kOddA, kO) >> 4;
+                da[6] = (int32_t)dp4a_u(I1, kEvenA, kE) >> 4; da[7] = (int32_t)dp4a_u(Rp, kOddA, kO) >> 4;
+                db[0] = (int32_t)dp4a_u(Lp, kEvenB, kE) >> 4; db[1] = (int32_t)dp4a_u(I0, kOddB, kO) >> 4;
+                db[2] = (int32_t)dp4a_u(I0, kEvenB, kE) >> 4; db[3] = (int32_t)dp4a_u(J, kOddB, kO) >> 4;
+                db[4] = (int32_t)dp4a_u(J, kEvenB, kE) >> 4;  db[5] = (int32_t)dp4a_u(I1, kOddB, kO) >> 4;
+                db[6] = (int32_t)dp4a_u(I1, kEvenB, kE) >> 4; db[7] = (int32_t)dp4a_u(Rp, kOddB, kO) >> 4;
             }
             uint32_t px[6];
-            ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
-            store_rgb8(orow + k * ostep, px, npx);
+            if (yA >= 0) {
+                ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
+                store_rgb8(out + ((size_t)yA * W + x) * 3, px, npx);
+            }
+            if (yB < H) {
+                ycc_to_rgb8(yb.x, yb.y, cbB, crB, px);
+                store_rgb8(out + ((size_t)yB * W + x) * 3, px, npx);
+            }
         }
         return;
     }
