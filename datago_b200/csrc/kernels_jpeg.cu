@@ -128,7 +128,7 @@ void launch_unstuff(const JpegWave& w, cudaStream_t s) {
 //    for every j (Huffman streams re-synchronise after a few symbols, so this takes 2-3 rounds; the loop is
 //    bounded by the thread count because thread j is final after round j).  A prefix sum over the slots and DC
 //    differences of the subsequences then gives every thread its output position and DC predictors, and a last
-//    pass writes the coefficients.  One CTA walks one image in chunks of kSpecThreads subsequences, carrying
+//    pass writes the coefficients.  One CTA walks one image in chunks of as many subsequences as it has threads, carrying
 //    the exact state across chunks, so no CTA ever waits on another.
 // ---------------------------------------------------------------------------------------------------------------
 struct HuffCtx {
@@ -242,6 +242,9 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
 }
 
 // ---- images without restart markers: speculative subsequences, one CTA per image ---------------------------------
+// Two CTA sizes: 256 threads when a launch has enough images to fill the GPU with them, 512 when it has not (few, large
+// images: the launch then lasts as long as its longest image, whose chunks are walked one after the other, and a CTA
+// twice as wide halves the number of chunks).
 #ifndef DG_SPEC_THREADS
 #define DG_SPEC_THREADS 256
 #endif
@@ -251,30 +254,34 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
 #ifndef DG_SPEC_MIN_CTAS
 #define DG_SPEC_MIN_CTAS 6
 #endif
-constexpr int kSpecThreads = DG_SPEC_THREADS;
+constexpr int kSpecThreads = DG_SPEC_THREADS;      // the narrow variant
+constexpr int kSpecThreadsWide = 512, kSpecMinCtasWide = 3;
+constexpr uint32_t kSpecWideBelow = 1024;         // images per launch below which the wide variant is used
 constexpr uint32_t kSubseqBits = DG_SUBSEQ_BITS;
 
 struct Scan4 { uint32_t n; int32_t a, b, c; };
 
 // Per-subsequence state of the chunk being synchronised (shared memory).
+template <int T>
 struct SpecState {
-    uint32_t entry_p[kSpecThreads], entry_sm[kSpecThreads];  // decoder state at the start of the subsequence
-    uint32_t exit_p[kSpecThreads], exit_sm[kSpecThreads];    // ... after its last symbol
-    uint32_t n[kSpecThreads];                                // slots consumed
-    int32_t dc[3][kSpecThreads];                             // sums of DC differences per component
-    uint32_t list[kSpecThreads];                             // subsequences to re-decode this round
+    uint32_t entry_p[T], entry_sm[T];  // decoder state at the start of the subsequence
+    uint32_t exit_p[T], exit_sm[T];    // ... after its last symbol
+    uint32_t n[T];                     // slots consumed
+    int32_t dc[3][T];                  // sums of DC differences per component
+    uint32_t list[T];                  // subsequences to re-decode this round
 };
 
-__global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(JpegWave w) {
+template <int T, int MIN_CTAS>
+__global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
     const uint32_t img = w.spec_list[blockIdx.x];
     const JpegDesc& d = w.descs[img];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     __shared__ HuffTable s_tab[6];
     __shared__ uint8_t s_nat[64];
-    __shared__ SpecState st;
-    __shared__ Scan4 s_warp[kSpecThreads / 32];
-    __shared__ uint32_t s_wcount[kSpecThreads / 32];
+    __shared__ SpecState<T> st;
+    __shared__ Scan4 s_warp[T / 32];
+    __shared__ uint32_t s_wcount[T / 32];
     __shared__ uint32_t s_carry_p, s_carry_slot;
     __shared__ int32_t s_carry_dc[3];
 
@@ -284,7 +291,7 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
         for (int t = 0; t < 6; ++t) {
             const uint32_t* src = reinterpret_cast<const uint32_t*>(w.huff + ids[t]);
             uint32_t* dst = reinterpret_cast<uint32_t*>(&s_tab[t]);
-            for (int i = tid; i < kWords; i += kSpecThreads) dst[i] = __ldg(src + i);
+            for (int i = tid; i < kWords; i += T) dst[i] = __ldg(src + i);
         }
         if (tid < 64) s_nat[tid] = kNatural[tid];
         if (tid == 0) { s_carry_p = 0; s_carry_slot = 0; s_carry_dc[0] = s_carry_dc[1] = s_carry_dc[2] = 0; }
@@ -316,8 +323,8 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
         st.dc[0][j] = a; st.dc[1][j] = b; st.dc[2][j] = c;
     };
 
-    for (uint32_t chunk = 0; chunk < nsub; chunk += kSpecThreads) {
-        const int cnt = (int)min((uint32_t)kSpecThreads, nsub - chunk);
+    for (uint32_t chunk = 0; chunk < nsub; chunk += T) {
+        const int cnt = (int)min((uint32_t)T, nsub - chunk);
         const bool active = tid < cnt;
         // entry state: exact for the first subsequence of the chunk, a guess (AC code of the first block) elsewhere
         st.entry_p[tid] = tid == 0 ? s_carry_p : (chunk + tid) * kSubseqBits;
@@ -328,7 +335,7 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
         // Re-decode every subsequence whose entry state differs from its left neighbour's exit state until none
         // does.  After round r the first r subsequences are final, so the loop ends within cnt rounds.  The
         // subsequences to redo are compacted so that a late round with a handful of them occupies one warp.
-        for (int round = 0; round <= kSpecThreads + 1; ++round) {
+        for (int round = 0; round <= T + 1; ++round) {
             bool need = false;
             if (active && tid > 0) {
                 const uint32_t pp = st.exit_p[tid - 1], ps = st.exit_sm[tid - 1];
@@ -340,7 +347,7 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
             __syncthreads();
             uint32_t before = 0, total = 0;
 #pragma unroll
-            for (int i = 0; i < kSpecThreads / 32; ++i) { const uint32_t v = s_wcount[i]; if (i < warp) before += v; total += v; }
+            for (int i = 0; i < T / 32; ++i) { const uint32_t v = s_wcount[i]; if (i < warp) before += v; total += v; }
             if (total == 0) break;
             if (need) st.list[before + __popc(ballot & ((1u << lane) - 1))] = (uint32_t)tid;
             __syncthreads();
@@ -348,7 +355,7 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
             ++rounds;
             decodes += total;
             __syncthreads();
-            if (round == kSpecThreads + 1) err |= kStSyncLimit;
+            if (round == T + 1) err |= kStSyncLimit;
         }
         // exclusive prefix over (slots, DC sums) of the chunk
         Scan4 inc{active ? st.n[tid] : 0u, active ? st.dc[0][tid] : 0, active ? st.dc[1][tid] : 0, active ? st.dc[2][tid] : 0};
@@ -364,7 +371,7 @@ __global__ void __launch_bounds__(kSpecThreads, DG_SPEC_MIN_CTAS) k_huff_spec(Jp
         __syncthreads();
         Scan4 pre{0, 0, 0, 0}, tot{0, 0, 0, 0};
 #pragma unroll
-        for (int i = 0; i < kSpecThreads / 32; ++i) {
+        for (int i = 0; i < T / 32; ++i) {
             const Scan4 t = s_warp[i];
             if (i < warp) { pre.n += t.n; pre.a += t.a; pre.b += t.b; pre.c += t.c; }
             tot.n += t.n; tot.a += t.a; tot.b += t.b; tot.c += t.c;
@@ -399,7 +406,9 @@ void launch_huff_restart(const JpegWave& w, cudaStream_t s) {
 }
 
 void launch_huff_spec(const JpegWave& w, cudaStream_t s) {
-    if (w.n_spec) k_huff_spec<<<w.n_spec, kSpecThreads, 0, s>>>(w);
+    if (!w.n_spec) return;
+    if (w.n_spec < kSpecWideBelow) k_huff_spec<kSpecThreadsWide, kSpecMinCtasWide><<<w.n_spec, kSpecThreadsWide, 0, s>>>(w);
+    else k_huff_spec<kSpecThreads, DG_SPEC_MIN_CTAS><<<w.n_spec, kSpecThreads, 0, s>>>(w);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
