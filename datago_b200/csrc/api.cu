@@ -119,7 +119,10 @@ struct dg_ctx {
     std::mutex mu;
     BlockCache dev{false}, pin{true};
     size_t wave_bytes = (size_t)13 << 30;  // coefficient bytes per wave (upper bound; waves are balanced below it)
-    size_t l2_group_bytes = (size_t)64 << 20;  // plane bytes per IDCT + colour launch pair
+    // Plane bytes per IDCT + colour launch pair.  Launching the two kernels in groups of images whose planes fit the L2
+    // used to pay; with the present colour kernel the tails of many small launches cost more than the plane reads from
+    // DRAM, so the default is one pair per wave (DATAGO_B200_L2_GROUP_MB restores the grouping).
+    size_t l2_group_bytes = (size_t)1 << 40;
 };
 
 static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool have_stream, dg_ctx** out) {
