@@ -118,7 +118,6 @@ struct dg_ctx {
     Transform tfm;
     std::mutex mu;
     BlockCache dev{false}, pin{true};
-    bool huff_chunked = false;  // DATAGO_B200_HUFF=chunked: the three-launch speculative decoder
     size_t wave_bytes = (size_t)13 << 30;  // coefficient bytes per wave (upper bound; waves are balanced below it)
     // Plane bytes per IDCT + colour launch pair.  Launching the two kernels in groups of images whose planes fit the L2
     // used to pay; with the present colour kernel the tails of many small launches cost more than the plane reads from
@@ -165,7 +164,6 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
         return fail(DG_E_CUDA, "creating the second stream failed");
     }
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
-    if (const char* v = getenv("DATAGO_B200_HUFF")) c->huff_chunked = strcmp(v, "chunked") == 0;
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
     return DG_OK;
@@ -318,7 +316,6 @@ struct WavePlan {
     int first_item = 0, last_item = 0;  // [first, last)
     std::vector<JpegDesc> descs;
     std::vector<uint32_t> spec_list, restart_list, restart_first, block_first, color_first;
-    std::vector<uint32_t> chunk_first, sub_first;  // chunked decoder: prefix sums over spec_list (after its sort)
     std::vector<std::array<uint32_t, 4>> groups;  // (first block, block count, first colour tile, tile count) per L2 group
     std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
     std::vector<uint32_t> pass_first[4];
@@ -328,10 +325,10 @@ struct WavePlan {
     std::vector<uint32_t> torgb_first;
     // scratch layout (bytes from the wave scratch base)
     size_t us_bytes = 0, coef_blocks = 0, plane_bytes = 0, decoded_bytes = 0, mid_bytes = 0, nseg = 0;
-    size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_sub = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
+    size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
     // meta offsets
     size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0, m_torgbs = 0;
-    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy, m_torgb, m_chunks, m_subs;
+    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy, m_torgb;
 };
 
 struct StageEvent { int stage; cudaEvent_t a, b; };
@@ -832,13 +829,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         // longest streams first: one CTA decodes one image, and the launch ends with its slowest CTA
         std::stable_sort(wv.spec_list.begin(), wv.spec_list.end(),
                          [&](uint32_t a, uint32_t c) { return wv.descs[a].raw_len > wv.descs[c].raw_len; });
-        wv.chunk_first.push_back(0);
-        wv.sub_first.push_back(0);
-        for (uint32_t di : wv.spec_list) {
-            const uint32_t subs = subseq_bound(wv.descs[di].raw_len);
-            wv.sub_first.push_back(wv.sub_first.back() + subs);
-            wv.chunk_first.push_back(wv.chunk_first.back() + (subs + kChunkSubseqs - 1) / kChunkSubseqs);
-        }
         wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
         size_t o = 0;
         wv.off_coef = o; o += align_up(blocks * 128, 256);  // first: the zero prefix of a scratch block is tracked from offset 0
@@ -846,7 +836,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         wv.off_uslen = o; o += align_up(wv.descs.size() * 4, 256);
         wv.off_segfound = o; o += align_up(wv.descs.size() * 4, 256);
         wv.off_segstart = o; o += align_up(segs * 4, 256);
-        wv.off_sub = o; o += align_up((size_t)wv.sub_first.back() * sizeof(SubRec), 256);
         wv.off_planes = o; o += align_up(planes, 256);
         wv.off_decoded = o; o += align_up(decoded, 256);
         wv.off_mid = o; o += align_up(mids, 256);
@@ -949,8 +938,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.m_spec = m.put(wv.spec_list);
             wv.m_restart_list = m.put(wv.restart_list);
             wv.m_restart = put_owner_map(m, wv.restart_first);
-            wv.m_chunks = put_owner_map(m, wv.chunk_first);
-            wv.m_subs = put_owner_map(m, wv.sub_first);
             wv.m_blocks = put_owner_map(m, wv.block_first);
             wv.m_color = put_owner_map(m, wv.color_first);
             for (int s = 0; s < 4; ++s) {
@@ -1136,9 +1123,6 @@ static int batch_run_locked(dg_batch* b) {
             w.n_spec = (uint32_t)wv.spec_list.size();
             w.restart_list = (const uint32_t*)(meta + wv.m_restart_list);
             w.restart_segs = resolve(b, wv.m_restart);
-            w.sub = (SubRec*)(sc + wv.off_sub);
-            w.spec_chunks = resolve(b, wv.m_chunks);
-            w.spec_subs = resolve(b, wv.m_subs);
             w.blocks = resolve(b, wv.m_blocks);
             w.color_tiles = resolve(b, wv.m_color);
             CU(mark(DG_STAGE_UNSTUFF, true));
@@ -1173,8 +1157,8 @@ static int batch_run_locked(dg_batch* b) {
             }
             if (w.n_spec) {
                 CU(mark(DG_STAGE_HUFF_SPEC, true));
-                if (ctx->huff_chunked) { launch_huff_chunked(w, s); b->launches += 3; }
-                else { launch_huff_spec(w, s); ++b->launches; }
+                launch_huff_spec(w, s);
+                ++b->launches;
                 CU(mark(DG_STAGE_HUFF_SPEC, false));
             }
             if (side_by_side) CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));

@@ -82,14 +82,6 @@ struct CopyJob {  // identity payloads / pitch removal
     uint32_t src_pitch, row_bytes, rows, tile_first;
 };
 
-// State of one subsequence of a speculatively decoded stream (chunked decoder).  After the synchronisation kernels:
-// entry and exit decoder states, slots consumed, sums of DC differences.  After the per-image scan: exit_p holds the
-// absolute slot the subsequence starts at and dc[] the DC predictors at its entry.
-struct SubRec {
-    uint32_t entry_p, entry_sm, exit_p, exit_sm, n;
-    int32_t dc[3];
-};
-
 struct ToRgbJob {  // convert_to_rgb8 of one payload: channels 1, 2 or 4 -> 3
     const uint8_t* src;
     uint8_t* dst;

@@ -31,11 +31,6 @@ struct JpegWave {
     const uint32_t* qt32;    // quantisation pool, 32 words per table: word i holds q[2i] in byte 0 and q[2i+1] in byte 3
     // speculative (no restart marker) images and restart-interval images of this wave
     const uint32_t* spec_list; uint32_t n_spec;
-    // the chunked speculative decoder (launch_huff_chunked): one record per subsequence, and flat indices over the
-    // chunks and the subsequences of all speculative images (owner = index into spec_list; counts are upper bounds
-    // from the stuffed stream length)
-    SubRec* sub;
-    OwnerMap spec_chunks, spec_subs;
     OwnerMap restart_segs;   // owner = index into restart_list
     const uint32_t* restart_list;
     OwnerMap blocks;         // owner = image
@@ -45,12 +40,6 @@ struct JpegWave {
 void launch_unstuff(const JpegWave& w, cudaStream_t s);
 void launch_huff_restart(const JpegWave& w, cudaStream_t s);
 void launch_huff_spec(const JpegWave& w, cudaStream_t s);
-// The same decoding split into three launches: every chunk of kChunkSubseqs subsequences is synchronised by its own CTA
-// from a guessed entry state, one CTA per image repairs the chunk boundaries and computes output positions and DC
-// predictors, and a flat grid over all subsequences writes the coefficients.  No launch lasts as long as an image.
-constexpr uint32_t kSubseqBits = 2048, kChunkSubseqs = 256;
-inline uint32_t subseq_bound(uint64_t stuffed_scan_bytes) { return (uint32_t)((stuffed_scan_bytes * 8 + kSubseqBits - 1) / kSubseqBits) + 1; }
-void launch_huff_chunked(const JpegWave& w, cudaStream_t s);
 // blocks [first, first + count) of the wave / colour tiles [first, first + count): callers launch them in groups of a
 // few images so that the planes written by the IDCT are still in L2 when the colour kernel reads them
 // rezero: the kernel writes zeros back over every coefficient row it found non-zero, which leaves the coefficient

@@ -248,12 +248,16 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
 #ifndef DG_SPEC_THREADS
 #define DG_SPEC_THREADS 256
 #endif
+#ifndef DG_SUBSEQ_BITS
+#define DG_SUBSEQ_BITS 2048
+#endif
 #ifndef DG_SPEC_MIN_CTAS
 #define DG_SPEC_MIN_CTAS 6
 #endif
 constexpr int kSpecThreads = DG_SPEC_THREADS;      // the narrow variant
 constexpr int kSpecThreadsWide = 512, kSpecMinCtasWide = 3;
 constexpr uint32_t kSpecWideBelow = 1024;         // images per launch below which the wide variant is used
+constexpr uint32_t kSubseqBits = DG_SUBSEQ_BITS;
 
 struct Scan4 { uint32_t n; int32_t a, b, c; };
 
@@ -394,231 +398,6 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
     }
     if (tid == 0 && s_carry_slot < total_slots) err |= kStTruncated;
     if (err) atomicOr(w.status + d.item, err);
-}
-
-// ---- the same decoding in three launches (see kernels.h) ----------------------------------------------------------
-struct HuffSmem {
-    HuffTable tab[6];
-    uint8_t nat[64];
-};
-
-__device__ __forceinline__ HuffCtx stage_tables(HuffSmem& sm, const JpegWave& w, const JpegDesc& d, int tid, int nthreads) {
-    const uint32_t ids[6] = {d.dc_tab[0], d.dc_tab[1], d.dc_tab[2], d.ac_tab[0], d.ac_tab[1], d.ac_tab[2]};
-    constexpr int kWords = sizeof(HuffTable) / 4;
-    for (int t = 0; t < 6; ++t) {
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(w.huff + ids[t]);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(&sm.tab[t]);
-        for (int i = tid; i < kWords; i += nthreads) dst[i] = __ldg(src + i);
-    }
-    if (tid < 64) sm.nat[tid] = kNatural[tid];
-    HuffCtx hc;
-    hc.base = reinterpret_cast<const char*>(&sm.tab[0]);
-    hc.dc_off0 = 0; hc.dc_off1 = sizeof(HuffTable); hc.dc_off2 = 2 * sizeof(HuffTable);
-    hc.ac_off0 = 3 * sizeof(HuffTable); hc.ac_off1 = 4 * sizeof(HuffTable); hc.ac_off2 = 5 * sizeof(HuffTable);
-    hc.luma_blocks = d.hs * d.vs;
-    hc.mcu_slots = d.bpm * 64u;
-    return hc;
-}
-
-// S: one CTA per chunk of kChunkSubseqs subsequences.  Every subsequence is decoded from a guessed entry state (exact only
-// for the first subsequence of the image) and then re-decoded from its left neighbour's exit state until the chunk is
-// consistent; the first subsequence of a chunk keeps its guess, kernel F repairs it.  Results go to the records.
-__global__ void __launch_bounds__(kChunkSubseqs, 6) k_huff_chunk_sync(JpegWave w) {
-    constexpr int T = (int)kChunkSubseqs;
-    const uint32_t k = owner_of(w.spec_chunks, blockIdx.x);
-    const uint32_t img = w.spec_list[k];
-    const JpegDesc& d = w.descs[img];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ HuffSmem sm;
-    __shared__ SpecState<T> st;
-    __shared__ uint32_t s_wcount[T / 32];
-    const HuffCtx hc = stage_tables(sm, w, d, tid, T);
-    __syncthreads();
-    const uint32_t us_len = w.us_len[img];
-    const uint32_t total_bits = us_len * 8u;
-    const uint32_t nsub = (total_bits + kSubseqBits - 1) / kSubseqBits;
-    const uint32_t first_sub = (blockIdx.x - w.spec_chunks.first[k]) * T;  // of this chunk, within the image
-    if (first_sub >= nsub) return;  // the chunk count is an upper bound taken from the stuffed stream
-    const int cnt = (int)min((uint32_t)T, nsub - first_sub);
-    const bool active = tid < cnt;
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
-    const uint32_t nwords = (us_len + 3) / 4 + 2;
-    auto decode_into_state = [&](int j) {
-        uint32_t p = st.entry_p[j], smod = st.entry_sm[j], n = 0, dummy = 0;
-        int32_t a = 0, b = 0, c = 0;
-        const uint32_t end_bit = min((first_sub + j + 1) * kSubseqBits, total_bits);
-        decode_span<false>(words, nwords, p, end_bit, total_bits, smod, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, sm.nat, dummy);
-        st.exit_p[j] = p; st.exit_sm[j] = smod; st.n[j] = n;
-        st.dc[0][j] = a; st.dc[1][j] = b; st.dc[2][j] = c;
-    };
-    const uint32_t gsub = first_sub + tid;
-    st.entry_p[tid] = gsub * kSubseqBits;
-    st.entry_sm[tid] = gsub == 0 ? 0u : 1u;  // the image starts with a DC code; elsewhere guess "an AC code of the first block"
-    if (active) decode_into_state(tid);
-    __syncthreads();
-    uint32_t rounds = 1, decodes = (uint32_t)cnt;
-    for (int round = 0; round <= T + 1; ++round) {
-        bool need = false;
-        if (active && tid > 0) {
-            const uint32_t pp = st.exit_p[tid - 1], ps = st.exit_sm[tid - 1];
-            need = pp != st.entry_p[tid] || ps != st.entry_sm[tid];
-            if (need) { st.entry_p[tid] = pp; st.entry_sm[tid] = ps; }
-        }
-        const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, need);
-        if (lane == 0) s_wcount[warp] = __popc(ballot);
-        __syncthreads();
-        uint32_t before = 0, total = 0;
-#pragma unroll
-        for (int i = 0; i < T / 32; ++i) { const uint32_t v = s_wcount[i]; if (i < warp) before += v; total += v; }
-        if (total == 0) break;
-        if (need) st.list[before + __popc(ballot & ((1u << lane) - 1))] = (uint32_t)tid;
-        __syncthreads();
-        if ((uint32_t)tid < total) decode_into_state((int)st.list[tid]);
-        ++rounds;
-        decodes += total;
-        __syncthreads();
-        if (round == T + 1 && tid == 0) atomicOr(w.status + d.item, kStSyncLimit);
-    }
-    if (active) {
-        SubRec r;
-        r.entry_p = st.entry_p[tid]; r.entry_sm = st.entry_sm[tid]; r.exit_p = st.exit_p[tid]; r.exit_sm = st.exit_sm[tid];
-        r.n = st.n[tid]; r.dc[0] = st.dc[0][tid]; r.dc[1] = st.dc[1][tid]; r.dc[2] = st.dc[2][tid];
-        w.sub[w.spec_subs.first[k] + gsub] = r;
-    }
-    if (tid == 0) {
-        atomicAdd(w.spec_stats, 1ull);
-        atomicAdd(w.spec_stats + 1, (unsigned long long)rounds);
-        atomicAdd(w.spec_stats + 2, (unsigned long long)decodes + (uint32_t)cnt);  // + the write pass of these subsequences
-    }
-}
-
-// F: one CTA per image.  Repairs the subsequences whose entry state differs from their left neighbour's exit (at first
-// only the first subsequence of every chunk; a repair can move an exit and so ask for the next one) until none does,
-// then turns slot counts and DC sums into each subsequence's absolute first slot and entry DC predictors.
-constexpr int kFixThreads = 256;
-constexpr uint32_t kFixMaxSubs = 1u << 16;  // flag bitmap capacity: streams up to 16 MiB
-
-__global__ void __launch_bounds__(kFixThreads) k_huff_chunk_fix(JpegWave w) {
-    constexpr int T = kFixThreads;
-    const uint32_t k = blockIdx.x;
-    const uint32_t img = w.spec_list[k];
-    const JpegDesc& d = w.descs[img];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ HuffSmem sm;
-    __shared__ uint32_t s_flag[kFixMaxSubs / 32];
-    __shared__ Scan4 s_warp[T / 32];
-    __shared__ Scan4 s_carry;
-    const HuffCtx hc = stage_tables(sm, w, d, tid, T);
-    const uint32_t us_len = w.us_len[img];
-    const uint32_t total_bits = us_len * 8u;
-    const uint32_t total_slots = d.nblocks * 64u;
-    const uint32_t nsub = (total_bits + kSubseqBits - 1) / kSubseqBits;
-    SubRec* rec = w.sub + w.spec_subs.first[k];
-    const uint32_t* words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
-    const uint32_t nwords = (us_len + 3) / 4 + 2;
-    uint32_t err = 0;
-    if (nsub > kFixMaxSubs) { if (tid == 0) atomicOr(w.status + d.item, kStSyncLimit); return; }
-    for (uint32_t i = tid; i < (nsub + 31) / 32; i += T) s_flag[i] = 0;
-    __syncthreads();
-    uint32_t redone = 0;
-    for (uint32_t round = 0; round <= nsub + 1; ++round) {
-        // phase 1: adopt the left neighbour's exit where it differs (exits are not written in this phase)
-        bool any = false;
-        for (uint32_t j = 1 + tid; j < nsub; j += T) {
-            const uint32_t pp = rec[j - 1].exit_p, ps = rec[j - 1].exit_sm;
-            if (pp != rec[j].entry_p || ps != rec[j].entry_sm) {
-                rec[j].entry_p = pp; rec[j].entry_sm = ps;
-                atomicOr(&s_flag[j >> 5], 1u << (j & 31));
-                any = true;
-            }
-        }
-        if (!__syncthreads_or(any)) break;
-        // phase 2: re-decode the flagged subsequences
-        for (uint32_t j = 1 + tid; j < nsub; j += T) {
-            if (!((s_flag[j >> 5] >> (j & 31)) & 1u)) continue;
-            uint32_t p = rec[j].entry_p, smod = rec[j].entry_sm, n = 0, dummy = 0;
-            int32_t a = 0, b = 0, c = 0;
-            const uint32_t end_bit = min((j + 1) * kSubseqBits, total_bits);
-            decode_span<false>(words, nwords, p, end_bit, total_bits, smod, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, sm.nat, dummy);
-            rec[j].exit_p = p; rec[j].exit_sm = smod; rec[j].n = n;
-            rec[j].dc[0] = a; rec[j].dc[1] = b; rec[j].dc[2] = c;
-            ++redone;
-        }
-        __syncthreads();
-        for (uint32_t i = tid; i < (nsub + 31) / 32; i += T) s_flag[i] = 0;
-        __syncthreads();
-        if (round == nsub + 1) err |= kStSyncLimit;
-    }
-    // exclusive prefix over (slots, DC sums), tile by tile
-    if (tid == 0) s_carry = Scan4{0, 0, 0, 0};
-    __syncthreads();
-    for (uint32_t base = 0; base < nsub; base += T) {
-        const uint32_t j = base + tid;
-        const bool on = j < nsub;
-        Scan4 inc{on ? rec[j].n : 0u, on ? rec[j].dc[0] : 0, on ? rec[j].dc[1] : 0, on ? rec[j].dc[2] : 0};
-        const Scan4 mine = inc;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t tn = __shfl_up_sync(0xFFFFFFFFu, inc.n, o);
-            const int32_t ta = __shfl_up_sync(0xFFFFFFFFu, inc.a, o), tb = __shfl_up_sync(0xFFFFFFFFu, inc.b, o),
-                          tc = __shfl_up_sync(0xFFFFFFFFu, inc.c, o);
-            if (lane >= o) { inc.n += tn; inc.a += ta; inc.b += tb; inc.c += tc; }
-        }
-        if (lane == 31) s_warp[warp] = inc;
-        __syncthreads();
-        Scan4 pre = s_carry, tot{0, 0, 0, 0};
-#pragma unroll
-        for (int i = 0; i < T / 32; ++i) {
-            const Scan4 t = s_warp[i];
-            if (i < warp) { pre.n += t.n; pre.a += t.a; pre.b += t.b; pre.c += t.c; }
-            tot.n += t.n; tot.a += t.a; tot.b += t.b; tot.c += t.c;
-        }
-        if (on) {
-            rec[j].exit_p = pre.n + inc.n - mine.n;  // absolute first slot
-            rec[j].dc[0] = pre.a + inc.a - mine.a; rec[j].dc[1] = pre.b + inc.b - mine.b; rec[j].dc[2] = pre.c + inc.c - mine.c;
-        }
-        __syncthreads();
-        if (tid == 0) { s_carry.n += tot.n; s_carry.a += tot.a; s_carry.b += tot.b; s_carry.c += tot.c; }
-        __syncthreads();
-    }
-    if (tid == 0 && s_carry.n < total_slots) err |= kStTruncated;
-    if (err) atomicOr(w.status + d.item, err);
-    if (redone) atomicAdd(w.spec_stats + 2, (unsigned long long)redone);
-}
-
-// W: one CTA per chunk again (so that all its threads share an image and its tables sit in shared memory): every
-// subsequence is decoded once more from its final entry state and written.
-__global__ void __launch_bounds__(kChunkSubseqs, 6) k_huff_chunk_write(JpegWave w) {
-    constexpr int T = (int)kChunkSubseqs;
-    const uint32_t k = owner_of(w.spec_chunks, blockIdx.x);
-    const uint32_t img = w.spec_list[k];
-    const JpegDesc& d = w.descs[img];
-    const int tid = threadIdx.x;
-    __shared__ HuffSmem sm;
-    const uint32_t us_len = w.us_len[img];
-    const uint32_t total_bits = us_len * 8u;
-    const uint32_t j = (blockIdx.x - w.spec_chunks.first[k]) * T + tid;  // subsequence within the image
-    if ((j - tid) * kSubseqBits >= total_bits) return;  // whole chunk beyond the unstuffed stream (uniform)
-    const HuffCtx hc = stage_tables(sm, w, d, tid, T);
-    __syncthreads();
-    if (j * kSubseqBits >= total_bits) return;
-    const SubRec r = w.sub[w.spec_subs.first[k] + j];
-    const uint32_t total_slots = d.nblocks * 64u;
-    const uint32_t slot0 = r.exit_p;
-    if (slot0 >= total_slots) return;
-    uint32_t p = r.entry_p, smod = r.entry_sm, nn = 0, err = 0;
-    int32_t p0 = r.dc[0], p1 = r.dc[1], p2 = r.dc[2];
-    const uint32_t end_bit = min((j + 1) * kSubseqBits, total_bits);
-    decode_span<true>(reinterpret_cast<const uint32_t*>(w.us + d.us_off), (us_len + 3) / 4 + 2, p, end_bit, total_bits, smod, nn,
-                      total_slots - slot0, p0, p1, p2, hc, w.coef + d.block_off * 64, slot0, sm.nat, err);
-    if (err) atomicOr(w.status + d.item, err);
-}
-
-void launch_huff_chunked(const JpegWave& w, cudaStream_t s) {
-    if (!w.n_spec) return;
-    k_huff_chunk_sync<<<w.spec_chunks.total, kChunkSubseqs, 0, s>>>(w);
-    k_huff_chunk_fix<<<w.n_spec, kFixThreads, 0, s>>>(w);
-    k_huff_chunk_write<<<w.spec_chunks.total, kChunkSubseqs, 0, s>>>(w);
 }
 
 void launch_huff_restart(const JpegWave& w, cudaStream_t s) {
