@@ -15,6 +15,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -118,6 +119,10 @@ struct dg_ctx {
     Transform tfm;
     std::mutex mu;
     BlockCache dev{false}, pin{true};
+    // Lanczos tables built so far, by (input size, box, output size): data sets repeat image sizes, and every epoch
+    // repeats all of them, while a table costs two sin() per weight.  Dropped wholesale when it outgrows its cap.
+    std::map<std::array<uint64_t, 4>, std::shared_ptr<const FilterTable>> table_cache;
+    size_t table_cache_bytes = 0, table_cache_cap = (size_t)512 << 20;
     size_t wave_bytes = (size_t)13 << 30;  // coefficient bytes per wave (upper bound; waves are balanced below it)
     // Plane bytes per IDCT + colour launch pair.  Launching the two kernels in groups of images whose planes fit the L2
     // used to pay; with the present colour kernel the tails of many small launches cost more than the plane reads from
@@ -379,11 +384,10 @@ struct Planner {
     std::unordered_map<std::string, uint32_t> huff_ids, qt_ids;
     std::vector<HuffTable> huff_pool;
     std::vector<uint32_t> qt_pool;  // 32 words per table, the layout JpegWave::qt32 documents
-    std::map<std::array<uint64_t, 4>, std::pair<size_t, FilterTable*>> table_ids;  // key -> (word offset, table)
-    std::vector<FilterTable*> tables;
+    std::map<std::array<uint64_t, 4>, std::pair<size_t, const FilterTable*>> table_ids;  // key -> (word offset, table)
+    std::vector<std::shared_ptr<const FilterTable>> tables;  // keeps the batch's tables alive whatever the ctx cache does
     std::vector<uint32_t> table_words;
 
-    ~Planner() { for (auto* t : tables) delete t; }
 
     // Most batches repeat a handful of tables (every libjpeg-encoded file carries the same four Huffman tables), so the
     // tables seen last are compared byte-wise before anything is hashed.
@@ -437,19 +441,33 @@ struct Planner {
         key[3] = 0;
         return key;
     }
-    void adopt(const std::array<uint64_t, 4>& key, FilterTable* t) {
+    std::shared_ptr<const FilterTable> cached(const std::array<uint64_t, 4>& key) const {
+        auto it = ctx->table_cache.find(key);
+        return it == ctx->table_cache.end() ? nullptr : it->second;
+    }
+    void remember_in_ctx(const std::array<uint64_t, 4>& key, const std::shared_ptr<const FilterTable>& t) {
+        const size_t bytes = t->words() * 4 + 4 * (t->start.size() + t->size.size()) + 2 * t->k.size();
+        if (ctx->table_cache_bytes + bytes > ctx->table_cache_cap) { ctx->table_cache.clear(); ctx->table_cache_bytes = 0; }
+        if (ctx->table_cache.emplace(key, t).second) ctx->table_cache_bytes += bytes;
+    }
+    void adopt(const std::array<uint64_t, 4>& key, std::shared_ptr<const FilterTable> t) {
         tables.push_back(t);
         size_t off = align_up(table_words.size(), 4);
         table_words.resize(off + t->words());
         t->pack(table_words.data() + off);
-        table_ids.emplace(key, std::make_pair(off, t));
+        table_ids.emplace(key, std::make_pair(off, t.get()));
     }
     // returns the table and its word offset in the pool
     const FilterTable* table(int in_size, double in0, double in1, int out_size, size_t* word_off) {
         const auto key = table_key(in_size, in0, in1, out_size);
         auto it = table_ids.find(key);
         if (it == table_ids.end()) {
-            adopt(key, new FilterTable(make_filter_table(in_size, in0, in1, out_size)));
+            std::shared_ptr<const FilterTable> t = cached(key);
+            if (!t) {
+                t = std::make_shared<const FilterTable>(make_filter_table(in_size, in0, in1, out_size));
+                remember_in_ctx(key, t);
+            }
+            adopt(key, t);
             it = table_ids.find(key);
         }
         *word_off = it->second.first;
@@ -457,13 +475,14 @@ struct Planner {
     }
     // Builds the filter tables a set of plans will ask for on all host cores (the weights cost a sin() each).
     void prebuild_tables(const std::vector<const dg_plan*>& plans) {
-        struct Req { std::array<uint64_t, 4> key; int in_size; double in0, in1; int out_size; FilterTable* t; };
+        struct Req { std::array<uint64_t, 4> key; int in_size; double in0, in1; int out_size; std::shared_ptr<const FilterTable> t; };
         std::vector<Req> reqs;
         std::map<std::array<uint64_t, 4>, int> seen;
         auto want = [&](int in_size, double in0, double in1, int out_size) {
             const auto key = table_key(in_size, in0, in1, out_size);
             if (table_ids.count(key) || seen.count(key)) return;
             seen[key] = 1;
+            if (auto t = cached(key)) { adopt(key, t); return; }
             reqs.push_back(Req{key, in_size, in0, in1, out_size, nullptr});
         };
         for (const dg_plan* pp : plans) {
@@ -483,10 +502,10 @@ struct Planner {
         for (size_t w = 0; w < nthreads; ++w)
             pool.emplace_back([&, w]() {
                 for (size_t i = w; i < reqs.size(); i += nthreads)
-                    reqs[i].t = new FilterTable(make_filter_table(reqs[i].in_size, reqs[i].in0, reqs[i].in1, reqs[i].out_size));
+                    reqs[i].t = std::make_shared<const FilterTable>(make_filter_table(reqs[i].in_size, reqs[i].in0, reqs[i].in1, reqs[i].out_size));
             });
         for (auto& th : pool) th.join();
-        for (Req& r : reqs) adopt(r.key, r.t);
+        for (Req& r : reqs) { remember_in_ctx(r.key, r.t); adopt(r.key, r.t); }
     }
 };
 
