@@ -367,7 +367,7 @@ struct dg_batch {
     size_t off_meta = 0, off_status = 0, off_blob = 0, off_rawin = 0, off_out = 0, persist_bytes = 0;
     size_t blob_bytes = 0, rawin_bytes = 0, out_bytes = 0, pin_bytes = 0;
     size_t arena_bytes = 0;  // out_bytes plus the pre-conversion images of DG_ITEM_TO_RGB8 items (never downloaded)
-    size_t m_huff = 0, m_qt = 0, m_tables = 0;
+    size_t m_huff = 0, m_qt = 0, m_tables = 0, meta_total = 0;  // meta_total: meta.bytes plus the filter tables behind it
     std::vector<const uint8_t*> raw_src;  // caller memory of raw items (used inside dg_batch_create only)
     uint64_t h2d = 0, d2h = 0;
     uint32_t launches = 0;
@@ -386,7 +386,12 @@ struct Planner {
     std::vector<uint32_t> qt_pool;  // 32 words per table, the layout JpegWave::qt32 documents
     std::map<std::array<uint64_t, 4>, std::pair<size_t, const FilterTable*>> table_ids;  // key -> (word offset, table)
     std::vector<std::shared_ptr<const FilterTable>> tables;  // keeps the batch's tables alive whatever the ctx cache does
-    std::vector<uint32_t> table_words;
+    // Tables of the batch in pool order: (word offset, table).  The pool itself is never materialised on the host heap:
+    // dg_batch_create packs every table straight into the page-locked staging buffer (tens of MB per batch, and a fresh
+    // heap block of that size costs more in page faults than the copy).
+    size_t table_words_total = 0;
+    std::vector<std::pair<size_t, const FilterTable*>> table_list;
+    void pack_tables(uint32_t* dst) const { for (const auto& e : table_list) e.second->pack(dst + e.first); }
 
 
     // Most batches repeat a handful of tables (every libjpeg-encoded file carries the same four Huffman tables), so the
@@ -452,9 +457,9 @@ struct Planner {
     }
     void adopt(const std::array<uint64_t, 4>& key, std::shared_ptr<const FilterTable> t) {
         tables.push_back(t);
-        size_t off = align_up(table_words.size(), 4);
-        table_words.resize(off + t->words());
-        t->pack(table_words.data() + off);
+        const size_t off = align_up(table_words_total, 4);
+        table_words_total = off + t->words();
+        table_list.emplace_back(off, t.get());
         table_ids.emplace(key, std::make_pair(off, t.get()));
     }
     // returns the table and its word offset in the pool
@@ -951,7 +956,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         m.bytes.clear();
         b->m_huff = m.put(pl.huff_pool, 16);
         b->m_qt = m.put(pl.qt_pool, 16);
-        b->m_tables = m.put(pl.table_words, 16);
         for (WavePlan& wv : b->waves) {
             wv.m_descs = m.put(wv.descs, 16);
             wv.m_spec = m.put(wv.spec_list);
@@ -971,9 +975,12 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             if (wv.torgb_first.empty()) wv.torgb_first.push_back(0);
             wv.m_torgb = put_owner_map(m, wv.torgb_first);
         }
+        // the filter tables follow the rest of the metadata; they are written into the staging buffer directly
+        b->m_tables = align_up(m.bytes.size(), 256);
+        b->meta_total = b->m_tables + pl.table_words_total * 4;
         if (round == 0) {
             b->off_meta = fixed_bytes;
-            b->persist_bytes = fixed_bytes + align_up(m.bytes.size(), 256);
+            b->persist_bytes = fixed_bytes + align_up(b->meta_total, 256);
             rc = ctx->dev.acquire(b->persist_bytes, &b->blk_persist);
             if (rc) return abandon(b, rc);
             b->d_persist = (uint8_t*)ctx->dev.blocks[b->blk_persist].ptr;
@@ -987,7 +994,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     // Raw inputs are staged too: a copy from pageable caller memory is serialised by the driver at a fraction of the
     // link rate, while host threads fill page-locked memory in parallel and the upload becomes one large transfer.
     const size_t staged_head = b->off_rawin + align_up(rawin, 256);
-    b->pin_bytes = staged_head + align_up(b->meta.bytes.size(), 256);
+    b->pin_bytes = staged_head + align_up(b->meta_total, 256);
     rc = ctx->pin.acquire(b->pin_bytes, &b->blk_pin);
     if (!rc) rc = ctx->pin.acquire(std::max<size_t>((size_t)n * 4, 256), &b->blk_pin_status);
     if (rc) return abandon(b, rc);
@@ -1033,6 +1040,18 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     }
     b->raw_src.clear();  // caller memory is not needed after this call
     memcpy(b->h_pin + staged_head, b->meta.bytes.data(), b->meta.bytes.size());
+    {
+        uint32_t* pool = reinterpret_cast<uint32_t*>(b->h_pin + staged_head + b->m_tables);
+        const auto& list = pl.table_list;
+        const unsigned hw = std::thread::hardware_concurrency();
+        const size_t threads = std::min<size_t>({8, hw ? hw : 1, list.size() / 16 + 1});
+        std::atomic<size_t> next{0};
+        auto work = [&]() { for (size_t k; (k = next.fetch_add(1)) < list.size();) list[k].second->pack(pool + list[k].first); };
+        std::vector<std::thread> pool_threads;
+        for (size_t t = 1; t < threads; ++t) pool_threads.emplace_back(work);
+        work();
+        for (auto& th : pool_threads) th.join();
+    }
     *out = b;
     return DG_OK;
 }
@@ -1048,8 +1067,8 @@ extern "C" int dg_batch_upload(dg_batch* b) {
     CU(cudaMemcpyAsync(b->d_persist, b->h_pin, head, cudaMemcpyHostToDevice, ctx->stream));
     b->h2d += head;
     // metadata
-    CU(cudaMemcpyAsync(b->d_persist + b->off_meta, b->h_pin + head, b->meta.bytes.size(), cudaMemcpyHostToDevice, ctx->stream));
-    b->h2d += b->meta.bytes.size();
+    CU(cudaMemcpyAsync(b->d_persist + b->off_meta, b->h_pin + head, b->meta_total, cudaMemcpyHostToDevice, ctx->stream));
+    b->h2d += b->meta_total;
     b->uploaded = true;
     return DG_OK;
 }
@@ -1462,7 +1481,9 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
     plan_resize(pl, wv, plan, channels, device_src, device_dst, mid_base, &mid_used);
     if (mid_used > mid_bound) return fail(DG_E_TOO_LARGE, "internal: intermediates exceed their bound");
     Meta m;
-    const size_t m_tables = m.put(pl.table_words, 16);
+    std::vector<uint32_t> packed(pl.table_words_total);
+    pl.pack_tables(packed.data());
+    const size_t m_tables = m.put(packed, 16);
     size_t m_passes[4];
     OwnerMapOff m_pass[4], m_copy;
     for (int s = 0; s < 4; ++s) {
