@@ -169,6 +169,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
         return fail(DG_E_CUDA, "creating the second stream failed");
     }
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
+    if (const char* mb = getenv("DATAGO_B200_TABLE_CACHE_MB")) { long v = atol(mb); if (v >= 0) c->table_cache_cap = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
     return DG_OK;

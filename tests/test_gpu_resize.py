@@ -165,3 +165,21 @@ def test_raw_input_without_transform_is_returned_unchanged():
             assert st == 0 and (r.width, r.height) == (a.shape[1], a.shape[0])
             assert_same(out, a, f"raw item {i}")
         assert_same(res[1][1], oracle.jpeg_decode(mixed[1]), "the JPEG beside them")
+
+
+def test_filter_table_cache_can_be_dropped_at_any_time(monkeypatch):
+    # a context keeps the Lanczos tables it has built; with a tiny cap the cache is emptied again and again, and a
+    # batch must keep the tables it uses alive by itself
+    monkeypatch.setenv("DATAGO_B200_TABLE_CACHE_MB", "0")
+    small = dg.Context(0, C1)
+    monkeypatch.delenv("DATAGO_B200_TABLE_CACHE_MB")
+    rng = np.random.default_rng(31)
+    raws = [rng.integers(0, 256, (int(rng.integers(300, 900)), int(rng.integers(300, 900)), 3), dtype=np.uint8) for _ in range(12)]
+    for _ in range(2):   # second round: same sizes again (cache hits in a normal context, rebuilds here)
+        for a, (st, out, r) in zip(raws, small.process(raws)):
+            want, p = oracle.crop_and_resize(C1, a)
+            assert st == 0 and r.plan.as_tuple() == p.as_tuple()
+            assert_same(out, want, f"{a.shape}")
+        for a, (st, out, r) in zip(raws, ctx(C1).process(raws)):
+            assert_same(out, oracle.crop_and_resize(C1, a)[0], f"cached {a.shape}")
+    small.close()
