@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdatago_b200.so")
 SOURCES = ["api.cu", "kernels_jpeg.cu", "kernels_resize.cu", "host_logic.cpp", "jpeg_header.cpp", "feeder.cpp"]
-HEADERS = ["desc.h", "host.h", "kernels.h", os.path.join("..", "..", "include", "datago_b200.h")]
+HEADERS = ["desc.h", "host.h", "host_pool.h", "kernels.h", os.path.join("..", "..", "include", "datago_b200.h")]
 
 
 def _stale():

@@ -23,6 +23,7 @@
 #include <vector>
 
 #include "host.h"
+#include "host_pool.h"
 #include "kernels.h"
 
 using namespace dg;
@@ -86,7 +87,10 @@ struct BlockCache {
                 blocks[victim] = Block();
             }
             cudaError_t e = pinned ? cudaHostAlloc(&nb.ptr, nb.size, cudaHostAllocDefault) : cudaMalloc(&nb.ptr, nb.size);
-            if (e != cudaSuccess) return fail(DG_E_CUDA, "%s of %zu bytes: %s", pinned ? "cudaHostAlloc" : "cudaMalloc", nb.size, cudaGetErrorString(e));
+            if (e != cudaSuccess) {
+                cudaGetLastError();  // a failed allocation must not surface again as the next healthy batch's error
+                return fail(DG_E_CUDA, "%s of %zu bytes: %s", pinned ? "cudaHostAlloc" : "cudaMalloc", nb.size, cudaGetErrorString(e));
+            }
             if (victim >= 0) { blocks[victim] = nb; best = victim; }
             else { blocks.push_back(nb); best = (int)blocks.size() - 1; }
         }
@@ -128,6 +132,8 @@ struct dg_ctx {
     // used to pay; with the present colour kernel the tails of many small launches cost more than the plane reads from
     // DRAM, so the default is one pair per wave (DATAGO_B200_L2_GROUP_MB restores the grouping).
     size_t l2_group_bytes = (size_t)1 << 40;
+    // Largest decoded image accepted (width * height * channels bytes); the `image` crate's default allocation limit is 512 MiB.
+    uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
 
 static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool have_stream, dg_ctx** out) {
@@ -170,6 +176,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
     }
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_TABLE_CACHE_MB")) { long v = atol(mb); if (v >= 0) c->table_cache_cap = (size_t)v << 20; }
+    if (const char* mb = getenv("DATAGO_B200_MAX_IMAGE_MB")) { long v = atol(mb); if (v >= 1) c->max_image_bytes = (uint64_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
     return DG_OK;
@@ -502,15 +509,9 @@ struct Planner {
                 want((int)p.new_h, p.crop_top, p.crop_top + p.crop_h, (int)p.target_h);
         }
         if (reqs.empty()) return;
-        const unsigned hw = std::thread::hardware_concurrency();
-        const size_t nthreads = std::min<size_t>(reqs.size() / 4 + 1, hw ? std::min(hw, 32u) : 4);
-        std::vector<std::thread> pool;
-        for (size_t w = 0; w < nthreads; ++w)
-            pool.emplace_back([&, w]() {
-                for (size_t i = w; i < reqs.size(); i += nthreads)
-                    reqs[i].t = std::make_shared<const FilterTable>(make_filter_table(reqs[i].in_size, reqs[i].in0, reqs[i].in1, reqs[i].out_size));
-            });
-        for (auto& th : pool) th.join();
+        HostPool::get().run(reqs.size(), [&](size_t i) {
+            reqs[i].t = std::make_shared<const FilterTable>(make_filter_table(reqs[i].in_size, reqs[i].in0, reqs[i].in1, reqs[i].out_size));
+        }, 2);
         for (Req& r : reqs) { remember_in_ctx(r.key, r.t); adopt(r.key, r.t); }
     }
 };
@@ -530,8 +531,10 @@ struct PassDraft {
 
 // Plans the resize of one image: appends passes / copy jobs to the wave.  src: device pointer of the source image
 // (tight pitch), dst: device pointer of the payload (tight pitch), mid: scratch for intermediates.
+// caller_owned_src: the source is memory of the caller with nothing guaranteed around it (the batch path's sources sit
+// in padded arenas of the library): the pass that reads it is then planned so that no load leaves the image's bytes.
 static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C, const uint8_t* src, uint8_t* dst,
-                        uint8_t* mid_base, size_t* mid_used) {
+                        uint8_t* mid_base, size_t* mid_used, bool caller_owned_src = false) {
     const uint32_t w = p.src_w, h = p.src_h, tw = p.target_w, th = p.target_h;
     auto add_copy = [&](const uint8_t* s, uint32_t pitch, uint32_t row_bytes, uint32_t rows) {
         CopyJob j;
@@ -573,12 +576,16 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         cp.src = s; cp.dst = d; cp.src_pitch = spitch; cp.dst_pitch = dpitch; cp.out_w = out_w; cp.out_h = out_h;
         cp.channels = C; cp.src_origin = origin; cp.t0 = t0; cp.tab_n = (uint32_t)T->n; cp.window = (uint32_t)T->window;
         cp.precision = (uint32_t)T->precision; cp.tab_off = tab_off;
+        const bool guarded = caller_owned_src && s >= src && s < src + (size_t)w * h * C;
         if (horizontal) {
             cp.fast = 1;
+            if (guarded) { cp.guard_lo = src; cp.guard_hi = src + (size_t)w * h * C; }
         } else {
             const uintptr_t bits = (uintptr_t)s | (uintptr_t)d | spitch | dpitch;
             cp.fast = (bits & 15) == 0 && (uint32_t)T->window <= kVFastMaxWindow && (size_t)align_up((size_t)out_w * C, 16) <= spitch &&
                       (size_t)align_up((size_t)out_w * C, 16) <= dpitch;
+            // the vector path reads whole 16-byte chunks: in caller memory they must end inside the row they start in
+            if (guarded && (size_t)(s - src) % spitch + align_up((size_t)out_w * C, 16) > spitch) cp.fast = 0;
         }
         cp.tiles_x = conv_tiles_x(cp, !horizontal);
         wv.passes[stage].push_back(cp);
@@ -624,17 +631,9 @@ static size_t resize_mid_bound(const dg_plan& p, uint32_t C) {
     return align_up(a, 256) + 2 * align_up(b, 256);
 }
 
-// Runs fn(0..n-1) on up to eight host threads (contiguous ranges); small counts stay on the calling thread.
+// Runs fn(0..n-1) on the process-wide host pool; small counts stay on the calling thread.
 template <typename F> static void parallel_items(int n, F&& fn) {
-    const unsigned hw = std::thread::hardware_concurrency();
-    const int threads = std::min<int>({8, hw ? (int)hw : 1, n / 128});
-    if (threads <= 1) { for (int i = 0; i < n; ++i) fn(i); return; }
-    std::vector<std::thread> pool;
-    const int per = (n + threads - 1) / threads;
-    for (int t = 1; t < threads; ++t)
-        pool.emplace_back([&fn, t, per, n]() { for (int i = t * per; i < std::min(n, (t + 1) * per); ++i) fn(i); });
-    for (int i = 0; i < std::min(n, per); ++i) fn(i);
-    for (auto& th : pool) th.join();
+    HostPool::get().run((size_t)std::max(n, 0), [&fn](size_t i) { fn((int)i); }, 64);
 }
 
 static int abandon(dg_batch* b, int rc) {
@@ -681,9 +680,21 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             it.status = parse_jpeg_header(src.data, src.len, h);
             if (it.status) return;
             if (h.scan_len > 0xFFFFFF00ull) { it.status = DG_E_TOO_LARGE; return; }
+            // Everything the host can tell about the tables is settled here, before the output arena is laid out, so
+            // that an item that fails on them takes no slot of a collated bucket.  (The dequantiser multiplies by one
+            // byte: 16-bit quantisation tables are not on this path.)
+            for (uint32_t c = 0; c < h.ncomp && c < 3; ++c) {
+                for (int k = 0; k < 64; ++k)
+                    if (h.qt[h.comp_tq[c]][k] > 255) { it.status = DG_E_UNSUPPORTED; return; }
+                if (!huff_lengths_valid(h.dc[h.comp_td[c]]) || !huff_lengths_valid(h.ac[h.comp_ta[c]])) { it.status = DG_E_BAD_TABLE; return; }
+            }
             it.is_jpeg = true; it.hdr = &h;
             it.w = h.width; it.h = h.height; it.c = h.ncomp == 1 ? 1 : 3;
         }
+        // A header can declare far more pixels than its bytes could ever hold (a forged SOF of 65535 x 65535 plans tens
+        // of GB).  datago decodes through the `image` crate, whose default limits refuse such a file and drop that one
+        // sample (src/worker_files.rs:14-16, 63-70); here the item alone gets DG_E_TOO_LARGE.
+        if ((uint64_t)it.w * it.h * it.c > ctx->max_image_bytes) { it.status = DG_E_TOO_LARGE; return; }
         if (transform) {
             it.status = plan_geometry(ctx->tfm, it.w, it.h, it.c, src.forced_key, &it.plan);
             if (it.status) return;
@@ -1030,28 +1041,14 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             for (size_t o = 0; o < bytes; o += (size_t)4 << 20)
                 pieces.push_back({b->h_pin + b->off_rawin + it.raw_in_off + o, b->raw_src[i] + o, std::min(bytes - o, (size_t)4 << 20)});
         }
-        const unsigned hw = std::thread::hardware_concurrency();
-        const size_t threads = std::min<size_t>({8, hw ? hw : 1, pieces.size()});
-        std::atomic<size_t> next{0};
-        auto work = [&]() { for (size_t k; (k = next.fetch_add(1)) < pieces.size();) memcpy(pieces[k].dst, pieces[k].src, pieces[k].len); };
-        std::vector<std::thread> pool;
-        for (size_t t = 1; t < threads; ++t) pool.emplace_back(work);
-        work();
-        for (auto& th : pool) th.join();
+        HostPool::get().run(pieces.size(), [&](size_t k) { memcpy(pieces[k].dst, pieces[k].src, pieces[k].len); }, 1);
     }
     b->raw_src.clear();  // caller memory is not needed after this call
     memcpy(b->h_pin + staged_head, b->meta.bytes.data(), b->meta.bytes.size());
     {
         uint32_t* pool = reinterpret_cast<uint32_t*>(b->h_pin + staged_head + b->m_tables);
         const auto& list = pl.table_list;
-        const unsigned hw = std::thread::hardware_concurrency();
-        const size_t threads = std::min<size_t>({8, hw ? hw : 1, list.size() / 16 + 1});
-        std::atomic<size_t> next{0};
-        auto work = [&]() { for (size_t k; (k = next.fetch_add(1)) < list.size();) list[k].second->pack(pool + list[k].first); };
-        std::vector<std::thread> pool_threads;
-        for (size_t t = 1; t < threads; ++t) pool_threads.emplace_back(work);
-        work();
-        for (auto& th : pool_threads) th.join();
+        HostPool::get().run(list.size(), [&](size_t k) { list[k].second->pack(pool + list[k].first); }, 8);
     }
     *out = b;
     return DG_OK;
@@ -1479,7 +1476,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
     Planner pl{ctx, nullptr};
     WavePlan wv;
     size_t mid_used = 0;
-    plan_resize(pl, wv, plan, channels, device_src, device_dst, mid_base, &mid_used);
+    plan_resize(pl, wv, plan, channels, device_src, device_dst, mid_base, &mid_used, true);
     if (mid_used > mid_bound) return fail(DG_E_TOO_LARGE, "internal: intermediates exceed their bound");
     Meta m;
     std::vector<uint32_t> packed(pl.table_words_total);

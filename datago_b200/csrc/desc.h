@@ -74,6 +74,10 @@ struct ConvPass {
     uint32_t tiles_x;               // tiles per row of tiles
     uint32_t fast;                  // 1: the staged / vectorised kernel path applies (see kernels_resize.cu)
     uint32_t pad;
+    // Set when `src` is memory the library does not own (no slack behind it): the horizontal pass then loads no byte
+    // outside [guard_lo, guard_hi).  Both null for sources inside the library's own padded arenas.
+    const uint8_t* guard_lo;
+    const uint8_t* guard_hi;
 };
 
 struct CopyJob {  // identity payloads / pitch removal

@@ -53,6 +53,7 @@ struct JpegHeader {
 };
 int parse_jpeg_header(const uint8_t* data, uint64_t len, JpegHeader& h);  // dg_status
 bool build_huff_table(const JpegHeader::RawHuff& raw, HuffTable& out);
+bool huff_lengths_valid(const JpegHeader::RawHuff& raw);  // what build_huff_table would accept, without building
 
 // ---- errors ---------------------------------------------------------------------------------------------------------
 // Stores msg as the calling thread's dg_last_error text and returns code.

@@ -150,6 +150,15 @@ int parse_jpeg_header(const uint8_t* data, uint64_t len, JpegHeader& h) {
 }
 
 // Canonical code assignment (T.81 Annex C) into the device lookup form.
+bool huff_lengths_valid(const JpegHeader::RawHuff& raw) {
+    int code = 0;
+    for (int l = 1; l <= 16; ++l) {
+        if (code + raw.bits[l] > (1 << l)) return false;  // over-subscribed
+        code = (code + raw.bits[l]) << 1;
+    }
+    return true;
+}
+
 bool build_huff_table(const JpegHeader::RawHuff& raw, HuffTable& out) {
     memset(&out, 0, sizeof out);
     memcpy(out.vals, raw.vals, 256);

@@ -63,11 +63,25 @@ __device__ __forceinline__ Table table_of(const ConvPass& p, const uint32_t* tab
 // One thread per output pixel column and kHRowsPerThread rows.  The window of an output pixel is taps * C consecutive
 // bytes of a source row: it is fetched four taps at a time as aligned 32-bit words, realigned with funnel shifts, and
 // the (tap, tap + 1) byte pairs of each channel are gathered with byte permutes and fed to dp2a.  Weights beyond a
-// window are zero in the table, so the bytes read past it (at most 15, inside the buffer's slack) do not matter.
+// window are zero in the table, so the bytes read past it (at most 15) do not matter -- but they are read: sources
+// inside the library's arenas have that much slack around them; for a source owned by the caller (GUARD) every word
+// that is not entirely inside [guard_lo, guard_hi) is assembled from the bytes that are, the rest reading as zero.
 constexpr int kHRowsPerThread = kConvTileH / 4;
 constexpr int kConvHThreads = kConvTileW * 4;
 
-template <int C>
+template <bool GUARD>
+__device__ __forceinline__ uint32_t load_word(const ConvPass& p, const uint32_t* w) {
+    if (!GUARD) return __ldg(w);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(w);
+    if (b >= p.guard_lo && b + 4 <= p.guard_hi) return __ldg(w);
+    uint32_t v = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (b + j >= p.guard_lo && b + j < p.guard_hi) v |= (uint32_t)__ldg(b + j) << (8 * j);
+    return v;
+}
+
+template <int C, bool GUARD>
 __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, uint32_t x, uint32_t y0) {
     const uint32_t t = p.t0 + x;
     const int32_t first = __ldg(tb.start + t) - p.src_origin;
@@ -96,7 +110,7 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
         for (int r = 0; r < kHRowsPerThread; ++r) {
             const uint32_t* w = base[r] + (i * C) / 4;  // i is a multiple of 4: i * C bytes is a whole number of words
             if (C == 3) {
-                const uint32_t a0 = __ldg(w), a1 = __ldg(w + 1), a2 = __ldg(w + 2), a3 = __ldg(w + 3);
+                const uint32_t a0 = load_word<GUARD>(p, w), a1 = load_word<GUARD>(p, w + 1), a2 = load_word<GUARD>(p, w + 2), a3 = load_word<GUARD>(p, w + 3);
                 const uint32_t w0 = __funnelshift_r(a0, a1, shift[r]), w1 = __funnelshift_r(a1, a2, shift[r]),
                                w2 = __funnelshift_r(a2, a3, shift[r]);
                 // byte 3 * tap + channel
@@ -107,7 +121,7 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
                 acc[r][1] = dp2a_lo(k23, __byte_perm(w1, w2, 0x0063), acc[r][1]);
                 acc[r][2] = dp2a_lo(k23, __byte_perm(w2, w2, 0x0030), acc[r][2]);
             } else {
-                const uint32_t a0 = __ldg(w), a1 = __ldg(w + 1);
+                const uint32_t a0 = load_word<GUARD>(p, w), a1 = load_word<GUARD>(p, w + 1);
                 const uint32_t w0 = __funnelshift_r(a0, a1, shift[r]);
                 acc[r][0] = dp2a_hi(k23, w0, dp2a_lo(k01, w0, acc[r][0]));
             }
@@ -130,8 +144,11 @@ __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes
     const uint32_t y0 = ty * kConvTileH + (threadIdx.x / kConvTileW) * kHRowsPerThread;
     if (x >= p.out_w || y0 >= p.out_h) return;
     const Table tb = table_of(p, tables);
-    if (p.channels == 3) conv_h_rows<3>(p, tb, x, y0);
-    else conv_h_rows<1>(p, tb, x, y0);
+    if (p.guard_hi) {
+        if (p.channels == 3) conv_h_rows<3, true>(p, tb, x, y0);
+        else conv_h_rows<1, true>(p, tb, x, y0);
+    } else if (p.channels == 3) conv_h_rows<3, false>(p, tb, x, y0);
+    else conv_h_rows<1, false>(p, tb, x, y0);
 }
 
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s) {

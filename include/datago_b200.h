@@ -42,7 +42,9 @@ typedef enum dg_status {
     DG_E_UNKNOWN_KEY = 8,  /* forced aspect-ratio key is not a bucket (datago panics: image_processing.rs:335) */
     DG_E_NO_TRANSFORM = 9, /* a bucket query on a ctx created without crop_and_resize */
     DG_E_SYNC_LIMIT = 10,  /* entropy decoder did not converge within its iteration cap */
-    DG_E_TOO_LARGE = 11,   /* input exceeds a stated size limit */
+    DG_E_TOO_LARGE = 11,   /* input exceeds a stated size limit: an image whose header declares more than 512 MiB of
+                              decoded pixels (the `image` crate's default allocation limit; DATAGO_B200_MAX_IMAGE_MB
+                              at context creation changes it), or an entropy-coded segment of 4 GiB */
     DG_E_TIMEOUT = 12      /* dg_wait: the sample has not finished within the given time (the ticket stays valid) */
 } dg_status;
 
@@ -191,7 +193,10 @@ DG_API int dg_batch_download_packed(dg_batch* b, uint8_t* host_base, uint64_t ca
 DG_API uint64_t dg_batch_packed_bytes(const dg_batch* b);
 DG_API int dg_batch_sync(dg_batch* b);
 DG_API int dg_batch_result(const dg_batch* b, int i, dg_result* out);
-/* Buckets of a DG_BATCH_COLLATE batch, in order of first appearance.  Items that failed belong to no bucket; images and
+/* Buckets of a DG_BATCH_COLLATE batch, in order of first appearance.  Items that dg_batch_create rejected (bad header
+ * or tables, unknown key, too large) belong to no bucket.  An item whose entropy-coded data turns out to be damaged is
+ * only found on the device: it keeps its slot, the slot's pixels are undefined and its dg_result.status is non-zero
+ * after dg_batch_sync -- consumers of a bucket array must look at the status of items[k].  Images and
  * masks of one key differ in channels and form separate buckets.  Per-item results stay valid (they point into the
  * bucket arrays).  0 buckets for a batch created without the flag. */
 DG_API int dg_batch_bucket_count(const dg_batch* b);
@@ -265,8 +270,11 @@ DG_API void dg_feeder_destroy(dg_feeder* f);
  * No counterpart in datago: it exists for hosts that must not let a library allocate device memory while they run
  * (a training process whose framework allocator owns all of HBM, a loop that cannot afford the device-wide
  * synchronisation an allocation can imply, a service with a no-allocation-after-start-up rule).
- * device_src: w * h * channels interleaved 8-bit pixels; device_dst: room for the bucket's target_w * target_h *
- * channels bytes (learn the size first with dg_plan_geometry).  Descriptors, filter tables and the images between
+ * device_src: w * h * channels interleaved 8-bit pixels, any alignment; the library loads no byte outside those
+ * w * h * channels, so the image may end where its allocation ends.  device_dst: room for the bucket's target_w *
+ * target_h * channels bytes (learn the size first with dg_plan_geometry).  The work runs on the ctx stream (see
+ * dg_ctx_stream), a non-blocking stream that is not ordered with any stream of the caller: device_src must be
+ * complete, and device_dst free to be written, before the call; the result is complete when the call returns.  Descriptors, filter tables and the images between
  * passes live in one 32 MiB array inside the library image, held by every GPU that loads the library until exit.
  * Limit: intermediates + tables must fit those 32 MiB; the intermediates are bounded by
  * new_w * channels * (max(src_h, new_h) + 2 * new_h) bytes (new_w, new_h from dg_plan_geometry), e.g. a 4096 x 4096

@@ -102,3 +102,28 @@ def test_bucket_array_wraps_as_torch_tensor_without_copy():
     assert tuple(t.shape) == (5, 224, 224, 3) and t.dtype == torch.uint8 and t.data_ptr() == bk["array"].ptr
     assert np.array_equal(t.cpu().numpy().reshape(-1), host[bk["packed_offset"]:bk["packed_offset"] + bk["nbytes"]])
     b.close()
+
+
+def test_items_with_unusable_tables_take_no_bucket_slot():
+    # a Huffman table whose code lengths over-subscribe the code space is found on the host: the item fails before the
+    # buckets are laid out; an item with damaged entropy data keeps its slot and reports a status
+    rng = np.random.default_rng(72)
+    good = [jpeg(rng, 300, 300, q=85) for _ in range(3)]
+    bad_table = bytearray(good[0])
+    dht = bad_table.index(b"\xff\xc4")
+    assert bad_table[dht + 5] == 0 and bad_table[dht + 7] == 5   # the standard luminance DC table
+    bad_table[dht + 5], bad_table[dht + 7] = 3, 2                # three codes of length 1, the symbol count unchanged
+    cut = good[1][: len(good[1]) * 2 // 3]
+    c = ctx(CFG224)
+    b, host = _run(c, [good[0], bytes(bad_table), good[1], cut, good[2]], None, dg.BATCH_COLLATE)
+    assert b.result(1).status == 6
+    assert b.result(3).status == 3
+    slots = [i for bk in b.buckets() for i in bk["items"]]
+    assert sorted(slots) == [0, 2, 3, 4]
+    for bk in b.buckets():
+        n, h, w, ch = bk["shape"]
+        dense = host[bk["packed_offset"]:bk["packed_offset"] + bk["nbytes"]].reshape(n, h, w, ch)
+        for pos, i in enumerate(bk["items"]):
+            if b.result(i).status == 0:
+                assert_same(dense[pos], oracle.jpeg_to_payload([good[0], None, good[1], None, good[2]][i], CFG224)[0])
+    b.close()

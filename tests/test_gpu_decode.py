@@ -171,3 +171,16 @@ def test_random_corruption_never_faults_and_never_leaks_into_neighbours():
     (st, out, _), = ctx().process([base[0]])
     assert st == 0
     assert_same(out, want[0])
+
+
+def test_forged_frame_size_is_refused_per_item():
+    # a small file whose frame header declares 65535 x 65535 pixels must cost nothing but its own status
+    rng = np.random.default_rng(13)
+    good = jpeg(rng, 320, 200)
+    sof = good.index(b"\xff\xc0")
+    forged = bytearray(good)
+    forged[sof + 5:sof + 9] = b"\xff\xff\xff\xff"  # height, width
+    res = ctx().process([good, bytes(forged), good])
+    assert res[0][0] == 0 and res[2][0] == 0 and res[1][0] == 11
+    assert_same(res[0][1], oracle.jpeg_decode(good))
+    assert_same(res[2][1], oracle.jpeg_decode(good))

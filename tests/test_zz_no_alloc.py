@@ -42,6 +42,28 @@ def test_two_calls_in_a_row_match_the_batch_path():
     _static_vs_batch(ctx, first, "1.000")                            # forced bucket, and the array is dirty by now
 
 
+def test_source_that_ends_where_its_allocation_could_end():
+    # The entry point must not load a byte outside [src, src + w * h * c): the caller's image may end exactly where a
+    # mapping ends.  Here the image is an interior slice of a larger tensor (so nothing can leave the allocation
+    # whatever the kernel does), at start offsets of every residue modulo 4 and with sizes whose filter windows are not
+    # multiples of four taps; the bytes around it are sentinels that would change the result if they leaked into it.
+    import torch
+    ctx = dg.Context(0, CFG)
+    rng = np.random.default_rng(43)
+    for (h, w, c), lead in (((301, 1234, 3), 1), ((777, 509, 1), 3), ((640, 1001, 3), 2), ((333, 700, 1), 5), ((512, 515, 3), 7)):
+        img = rng.integers(0, 256, (h, w, c), dtype=np.uint8) if c == 3 else rng.integers(0, 256, (h, w), dtype=np.uint8)
+        n = h * w * c
+        (status, want, res), = ctx.process([img])
+        assert status == 0
+        for sentinel in (0, 255):
+            big = torch.full((lead + n + 64,), sentinel, dtype=torch.uint8, device="cuda")
+            big[lead:lead + n] = torch.from_numpy(img.reshape(-1)).cuda()
+            dst = torch.zeros(want.shape, dtype=torch.uint8, device="cuda")
+            torch.cuda.synchronize()
+            ctx.resize_device_static(big.data_ptr() + lead, w, h, c, dst.data_ptr())
+            assert np.array_equal(dst.cpu().numpy(), want), (h, w, c, lead, sentinel)
+
+
 def test_identity_and_copy_only_plans():
     ctx = dg.Context(0, CFG)
     rng = np.random.default_rng(42)
