@@ -132,6 +132,9 @@ struct dg_ctx {
     // used to pay; with the present colour kernel the tails of many small launches cost more than the plane reads from
     // DRAM, so the default is one pair per wave (DATAGO_B200_L2_GROUP_MB restores the grouping).
     size_t l2_group_bytes = (size_t)1 << 40;
+    // Three-component 4:2:0 images take the fused path (luma never leaves the SM); DATAGO_B200_FUSED=0 sends them through
+    // the general IDCT and colour kernels instead (for measurements and for testing that path on the common sampling).
+    bool fused_path = true;
     // Largest decoded image accepted (width * height * channels bytes); the `image` crate's default allocation limit is 512 MiB.
     uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
@@ -176,6 +179,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
     }
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_TABLE_CACHE_MB")) { long v = atol(mb); if (v >= 0) c->table_cache_cap = (size_t)v << 20; }
+    if (const char* v = getenv("DATAGO_B200_FUSED")) c->fused_path = atoi(v) != 0;
     if (const char* mb = getenv("DATAGO_B200_MAX_IMAGE_MB")) { long v = atol(mb); if (v >= 1) c->max_image_bytes = (uint64_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
@@ -330,6 +334,11 @@ struct WavePlan {
     std::vector<JpegDesc> descs;
     std::vector<uint32_t> spec_list, restart_list, restart_first, block_first, color_first;
     std::vector<std::array<uint32_t, 4>> groups;  // (first block, block count, first colour tile, tile count) per L2 group
+    // descs [fused_first, descs.size()) take the fused 4:2:0 path: prefix sums of their chroma blocks and tiles, and
+    // their own launch groups (first chroma block, count, first tile, count)
+    uint32_t fused_first = 0;
+    std::vector<uint32_t> fchroma_first, ftile_first;
+    std::vector<std::array<uint32_t, 4>> fgroups;
     std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
     std::vector<uint32_t> pass_first[4];
     std::vector<CopyJob> copies;
@@ -341,7 +350,7 @@ struct WavePlan {
     size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
     // meta offsets
     size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0, m_torgbs = 0;
-    OwnerMapOff m_restart, m_blocks, m_color, m_pass[4], m_copy, m_torgb;
+    OwnerMapOff m_restart, m_blocks, m_color, m_fchroma, m_ftile, m_pass[4], m_copy, m_torgb;
 };
 
 struct StageEvent { int stage; cudaEvent_t a, b; };
@@ -798,12 +807,10 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     size_t scratch_max = 0, blob_off = 0;
     for (WavePlan& wv : b->waves) {
         size_t us = 0, planes = 0, decoded = 0, mids = 0, blocks = 0, segs = 0;
-        uint32_t color_total = 0, restart_total = 0;
-        size_t group_bytes = 0;
-        wv.block_first.push_back(0);
-        wv.color_first.push_back(0);
-        wv.groups.push_back({0, 0, 0, 0});
-        wv.restart_first.push_back(0);
+        // Descriptors are built in item order, then arranged so that the images of the general path come first and those
+        // of the fused 4:2:0 path after them: each class then owns one contiguous range of the coefficient array.
+        std::vector<JpegDesc> built;
+        std::vector<int> built_item;
         for (int i = wv.first_item; i < wv.last_item; ++i) {
             ItemPlan& it = b->items[i];
             if (it.status || it.wave < 0) continue;
@@ -826,14 +833,13 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             d.raw_off = blob_off; d.raw_len = (uint32_t)h.scan_len;
             blob_off += align_up(h.scan_len, 16) + 16;
             d.us_off = us; us += align_up(h.scan_len + 32, 16);
-            d.block_off = blocks; d.nblocks = it.nblocks;
+            d.nblocks = it.nblocks;
             d.width = h.width; d.height = h.height; d.mcux = h.mcux; d.mcuy = h.mcuy;
             d.ncomp = h.ncomp; d.hs = h.hs; d.vs = h.vs; d.bpm = h.ncomp == 1 ? 1 : h.hs * h.vs + 2;
             for (uint32_t c = 0; c < 3; ++c) {
                 const uint32_t hs = c == 0 ? h.hs : 1, vs = c == 0 ? h.vs : 1;
                 d.plane_pitch[c] = h.mcux * hs * 8;
                 d.plane_rows[c] = h.mcuy * vs * 8;
-                if (c < h.ncomp) { d.plane_off[c] = planes; planes += align_up((size_t)d.plane_pitch[c] * d.plane_rows[c], 256); }
             }
             d.restart = h.restart;
             const uint32_t mcus = h.mcux * h.mcuy;
@@ -842,25 +848,66 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             d.item = (uint32_t)i;
             if (transform) { d.out_off = decoded; it.decoded_off = decoded; decoded += align_up((size_t)it.w * it.h * it.c, 256); }
             else d.out_off = it.pipe_off;
+            built.push_back(d);
+            built_item.push_back(i);
+        }
+        std::vector<size_t> order;
+        for (int pass = 0; pass < 2; ++pass)
+            for (size_t k = 0; k < built.size(); ++k)
+                if ((int)(ctx->fused_path && fused_decode(built[k].ncomp, built[k].hs, built[k].vs, built[k].width)) == pass) order.push_back(k);
+        uint32_t color_total = 0, restart_total = 0, fchroma_total = 0, ftile_total = 0;
+        size_t group_bytes = 0, fgroup_bytes = 0;
+        wv.block_first.push_back(0);
+        wv.color_first.push_back(0);
+        wv.groups.push_back({0, 0, 0, 0});
+        wv.fchroma_first.push_back(0);
+        wv.ftile_first.push_back(0);
+        wv.fgroups.push_back({0, 0, 0, 0});
+        wv.restart_first.push_back(0);
+        wv.fused_first = (uint32_t)built.size();
+        for (size_t k : order) {
+            JpegDesc d = built[k];
+            ItemPlan& it = b->items[built_item[k]];
+            const bool fused = ctx->fused_path && fused_decode(d.ncomp, d.hs, d.vs, d.width);
+            d.block_off = blocks;
             it.coef_off_blocks = blocks;
             blocks += it.nblocks;
+            // the fused path keeps no luma plane
+            for (uint32_t c = fused ? 1 : 0; c < d.ncomp; ++c) { d.plane_off[c] = planes; planes += align_up((size_t)d.plane_pitch[c] * d.plane_rows[c], 256); }
             it.wave_local = (int)wv.descs.size();
-            if (h.restart) { wv.restart_list.push_back((uint32_t)wv.descs.size()); restart_total += d.nseg; wv.restart_first.push_back(restart_total); }
+            if (d.restart) { wv.restart_list.push_back((uint32_t)wv.descs.size()); restart_total += d.nseg; wv.restart_first.push_back(restart_total); }
             else wv.spec_list.push_back((uint32_t)wv.descs.size());
+            if (fused && wv.fused_first == (uint32_t)built.size()) wv.fused_first = (uint32_t)wv.descs.size();
             wv.descs.push_back(d);
-            wv.block_first.push_back((uint32_t)blocks);
-            const uint32_t ntiles = color_tiles(h.width, h.mcuy);
-            color_total += ntiles;
-            wv.color_first.push_back(color_total);
             // images whose planes fit the L2 budget together share one IDCT launch and one colour launch
-            const size_t pbytes = (size_t)it.nblocks * 64;
-            if (wv.groups.back()[1] && group_bytes + pbytes > ctx->l2_group_bytes) {
-                wv.groups.push_back({(uint32_t)(blocks - it.nblocks), 0, color_total - ntiles, 0});
-                group_bytes = 0;
+            if (!fused) {
+                wv.block_first.push_back((uint32_t)blocks);
+                const uint32_t ntiles = color_tiles(d.width, d.mcuy);
+                color_total += ntiles;
+                wv.color_first.push_back(color_total);
+                const size_t pbytes = (size_t)it.nblocks * 64;
+                if (wv.groups.back()[1] && group_bytes + pbytes > ctx->l2_group_bytes) {
+                    wv.groups.push_back({(uint32_t)(blocks - it.nblocks), 0, color_total - ntiles, 0});
+                    group_bytes = 0;
+                }
+                group_bytes += pbytes;
+                wv.groups.back()[1] += it.nblocks;
+                wv.groups.back()[3] += ntiles;
+            } else {
+                const uint32_t nchroma = 2 * d.mcux * d.mcuy, ntiles = fused_tiles(d.width, d.mcuy);
+                fchroma_total += nchroma;
+                ftile_total += ntiles;
+                wv.fchroma_first.push_back(fchroma_total);
+                wv.ftile_first.push_back(ftile_total);
+                const size_t pbytes = (size_t)nchroma * 64;
+                if (wv.fgroups.back()[1] && fgroup_bytes + pbytes > ctx->l2_group_bytes) {
+                    wv.fgroups.push_back({fchroma_total - nchroma, 0, ftile_total - ntiles, 0});
+                    fgroup_bytes = 0;
+                }
+                fgroup_bytes += pbytes;
+                wv.fgroups.back()[1] += nchroma;
+                wv.fgroups.back()[3] += ntiles;
             }
-            group_bytes += pbytes;
-            wv.groups.back()[1] += it.nblocks;
-            wv.groups.back()[3] += ntiles;
         }
         // longest streams first: one CTA decodes one image, and the launch ends with its slowest CTA
         std::stable_sort(wv.spec_list.begin(), wv.spec_list.end(),
@@ -975,6 +1022,8 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.m_restart = put_owner_map(m, wv.restart_first);
             wv.m_blocks = put_owner_map(m, wv.block_first);
             wv.m_color = put_owner_map(m, wv.color_first);
+            wv.m_fchroma = put_owner_map(m, wv.fchroma_first);
+            wv.m_ftile = put_owner_map(m, wv.ftile_first);
             for (int s = 0; s < 4; ++s) {
                 wv.m_passes[s] = m.put(wv.passes[s], 16);
                 if (wv.pass_first[s].empty()) wv.pass_first[s].push_back(0);
@@ -1161,6 +1210,9 @@ static int batch_run_locked(dg_batch* b) {
             w.restart_segs = resolve(b, wv.m_restart);
             w.blocks = resolve(b, wv.m_blocks);
             w.color_tiles = resolve(b, wv.m_color);
+            w.fused_first = wv.fused_first;
+            w.fused_chroma = resolve(b, wv.m_fchroma);
+            w.fused_tiles = resolve(b, wv.m_ftile);
             CU(mark(DG_STAGE_UNSTUFF, true));
             launch_unstuff(w, s);
             ++b->launches;
@@ -1199,12 +1251,24 @@ static int batch_run_locked(dg_batch* b) {
             }
             if (side_by_side) CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
             for (const auto& g : wv.groups) {
+                if (!g[1]) continue;
                 CU(mark(DG_STAGE_IDCT, true));
                 launch_idct(w, g[0], g[1], rezero, s);
                 ++b->launches;
                 CU(mark(DG_STAGE_IDCT, false));
                 CU(mark(DG_STAGE_COLOR, true));
                 launch_color(w, g[2], g[3], s);
+                ++b->launches;
+                CU(mark(DG_STAGE_COLOR, false));
+            }
+            for (const auto& g : wv.fgroups) {  // 4:2:0: chroma planes first, then luma IDCT + upsampling + colour in one kernel
+                if (!g[1]) continue;
+                CU(mark(DG_STAGE_IDCT, true));
+                launch_idct_chroma(w, g[0], g[1], rezero, s);
+                ++b->launches;
+                CU(mark(DG_STAGE_IDCT, false));
+                CU(mark(DG_STAGE_COLOR, true));
+                launch_luma_color(w, g[2], g[3], rezero, s);
                 ++b->launches;
                 CU(mark(DG_STAGE_COLOR, false));
             }

@@ -35,24 +35,38 @@ struct JpegWave {
     const uint32_t* restart_list;
     OwnerMap blocks;         // owner = image
     OwnerMap color_tiles;    // owner = image
+    // Images [fused_first, n) of the wave are three-component 4:2:0 images at least five pixels wide: they take the fused
+    // path (chroma-only IDCT into planes, then one kernel for luma IDCT + upsampling + colour conversion) and are not
+    // covered by `blocks` / `color_tiles`.  Owner o of these two maps is image fused_first + o.
+    uint32_t fused_first;
+    OwnerMap fused_chroma;   // flat index over the chroma blocks (Cb, Cr of MCU 0, Cb, Cr of MCU 1, ...)
+    OwnerMap fused_tiles;    // colour tiles, color_tiles() per image
 };
 
 void launch_unstuff(const JpegWave& w, cudaStream_t s);
 void launch_huff_restart(const JpegWave& w, cudaStream_t s);
 void launch_huff_spec(const JpegWave& w, cudaStream_t s);
-// blocks [first, first + count) of the wave / colour tiles [first, first + count): callers launch them in groups of a
-// few images so that the planes written by the IDCT are still in L2 when the colour kernel reads them
+// blocks [first, first + count) of the wave / colour tiles [first, first + count): callers may launch them in groups of
+// images (the planes written by the IDCT are then still in L2 when the colour kernel reads them) or once per wave
 // rezero: the kernel writes zeros back over every coefficient row it found non-zero, which leaves the coefficient
 // buffer all-zero again for the next wave that uses it (the entropy decoders only write non-zero coefficients)
 void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s);
 void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s);
+// the fused path: chroma blocks [first, first + count) of fused_chroma, tiles [first, first + count) of fused_tiles
+void launch_idct_chroma(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s);
+void launch_luma_color(const JpegWave& w, uint32_t first_tile, uint32_t count, bool rezero, cudaStream_t s);
+// whether an image takes the fused path
+inline bool fused_decode(uint32_t ncomp, uint32_t hs, uint32_t vs, uint32_t width) { return ncomp == 3 && hs == 2 && vs == 2 && width >= 5; }
 
 // The colour kernel gives one CTA 256 pixels of four MCU rows.
 constexpr uint32_t kColorTileW = 256, kColorMcuRows = 4;
 inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) {
-    // one more row of tiles than the MCU rows need: the 4:2:0 path shifts its tiles up by one pixel row, so that every
-    // pair of output rows that shares its two chroma rows falls into one tile
+    // one more row of tiles than the MCU rows need: the 4:2:0 path of the colour kernel shifts its tiles up by one pixel
+    // row, so that every pair of output rows that shares its two chroma rows falls into one tile
     return ((width + kColorTileW - 1) / kColorTileW) * (mcuy / kColorMcuRows + 1);
+}
+inline uint32_t fused_tiles(uint32_t width, uint32_t mcuy) {  // the fused kernel's tiles are aligned to MCU rows
+    return ((width + kColorTileW - 1) / kColorTileW) * ((mcuy + kColorMcuRows - 1) / kColorMcuRows);
 }
 
 // ---- resize ---------------------------------------------------------------------------------------------------------

@@ -476,6 +476,74 @@ __device__ __forceinline__ void dequant_pair(uint32_t cw, uint32_t qw, int32_t& 
 constexpr int32_t kRound1 = 1 << 10, kRound2 = (1 << 17) + (128 << 18);
 constexpr int kIdctThreads = 128;
 
+// Dequantise + inverse DCT of the calling lane's block; c = its eight coefficient rows, qq = the quantiser rows in the
+// dp2a layout.  emit(r, lo, hi) receives row r of the result as two words of four saturated samples.  The short cuts
+// are taken per warp (all 32 blocks 4x4-sparse / DC only), so every lane of a warp must call this.
+template <class Emit>
+__device__ __forceinline__ void idct_block(const uint4 (&c)[8], const uint4* __restrict__ qq, Emit&& emit) {
+    const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
+                             c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
+    const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
+    const bool sparse = __all_sync(0xFFFFFFFFu, (hi_rows | hi_cols) == 0);
+    const uint32_t ac = (c[0].x >> 16) | c[0].y | c[1].x | c[1].y | c[2].x | c[2].y | c[3].x | c[3].y;
+    const bool dc_only = sparse && __all_sync(0xFFFFFFFFu, ac == 0);
+    if (dc_only) {
+        // flat blocks (a quarter of the warps on smooth content): both passes reduce to shifts of the DC term
+        int32_t lo, hi;
+        dequant_pair(c[0].x, __ldg(reinterpret_cast<const uint32_t*>(qq)), lo, hi);
+        const int32_t wsv = (lo * 8192 + kRound1) >> 11;
+        const int32_t v = (wsv * 8192 + kRound2) >> 18;
+        const uint32_t px4 = pack_sat_u8(v, v, v, v);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) emit(r, px4, px4);
+    } else if (sparse) {
+        int32_t x[4][4], ws[8][4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint4 qv = __ldg(qq + r);
+            dequant_pair(c[r].x, qv.x, x[r][0], x[r][1]);
+            dequant_pair(c[r].y, qv.y, x[r][2], x[r][3]);
+        }
+#pragma unroll
+        for (int col = 0; col < 4; ++col) {
+            int32_t o[8];
+            idct8_lo4<kRound1, 11>(x[0][col], x[1][col], x[2][col], x[3][col], o);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int32_t o[8];
+            idct8_lo4<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], o);
+            emit(r, pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
+        }
+    } else {
+        int32_t ws[8][8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint4 qv = __ldg(qq + r);
+            dequant_pair(c[r].x, qv.x, ws[r][0], ws[r][1]);
+            dequant_pair(c[r].y, qv.y, ws[r][2], ws[r][3]);
+            dequant_pair(c[r].z, qv.z, ws[r][4], ws[r][5]);
+            dequant_pair(c[r].w, qv.w, ws[r][6], ws[r][7]);
+        }
+#pragma unroll
+        for (int col = 0; col < 8; ++col) {
+            int32_t o[8];
+            idct8<kRound1, 11>(ws[0][col], ws[1][col], ws[2][col], ws[3][col], ws[4][col], ws[5][col], ws[6][col], ws[7][col], o);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int32_t o[8];
+            idct8<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], ws[r][4], ws[r][5], ws[r][6], ws[r][7], o);
+            emit(r, pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
+        }
+    }
+}
+
+
 #ifndef DG_IDCT_MIN_CTAS
 #define DG_IDCT_MIN_CTAS 7
 #endif
@@ -532,71 +600,12 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWav
             if ((m >> (lane & 7)) & 1u) gwarp[i * 32 + lane] = make_uint4(0, 0, 0, 0);
         }
     }
-    const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
-                             c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
-    const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
-    const bool sparse = __all_sync(0xFFFFFFFFu, (hi_rows | hi_cols) == 0);
-    const uint32_t ac = (c[0].x >> 16) | c[0].y | c[1].x | c[1].y | c[2].x | c[2].y | c[3].x | c[3].y;
-    const bool dc_only = sparse && __all_sync(0xFFFFFFFFu, ac == 0);
     const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[comp] * 32);
     uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
     const uint32_t pitch = d.plane_pitch[comp];
-    if (dc_only) {
-        // flat blocks (a quarter of the warps on smooth content): both passes reduce to shifts of the DC term
-        int32_t lo, hi;
-        dequant_pair(c[0].x, __ldg(reinterpret_cast<const uint32_t*>(qq)), lo, hi);
-        const int32_t wsv = (lo * 8192 + kRound1) >> 11;
-        const int32_t v = (wsv * 8192 + kRound2) >> 18;
-        const uint32_t px4 = pack_sat_u8(v, v, v, v);
-        if (valid) {
-#pragma unroll
-            for (int r = 0; r < 8; ++r) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(px4, px4);
-        }
-    } else if (sparse) {
-        int32_t x[4][4], ws[8][4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const uint4 qv = __ldg(qq + r);
-            dequant_pair(c[r].x, qv.x, x[r][0], x[r][1]);
-            dequant_pair(c[r].y, qv.y, x[r][2], x[r][3]);
-        }
-#pragma unroll
-        for (int col = 0; col < 4; ++col) {
-            int32_t o[8];
-            idct8_lo4<kRound1, 11>(x[0][col], x[1][col], x[2][col], x[3][col], o);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            int32_t o[8];
-            idct8_lo4<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], o);
-            if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
-        }
-    } else {
-        int32_t ws[8][8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            const uint4 qv = __ldg(qq + r);
-            dequant_pair(c[r].x, qv.x, ws[r][0], ws[r][1]);
-            dequant_pair(c[r].y, qv.y, ws[r][2], ws[r][3]);
-            dequant_pair(c[r].z, qv.z, ws[r][4], ws[r][5]);
-            dequant_pair(c[r].w, qv.w, ws[r][6], ws[r][7]);
-        }
-#pragma unroll
-        for (int col = 0; col < 8; ++col) {
-            int32_t o[8];
-            idct8<kRound1, 11>(ws[0][col], ws[1][col], ws[2][col], ws[3][col], ws[4][col], ws[5][col], ws[6][col], ws[7][col], o);
-#pragma unroll
-            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            int32_t o[8];
-            idct8<kRound2, 18>(ws[r][0], ws[r][1], ws[r][2], ws[r][3], ws[r][4], ws[r][5], ws[r][6], ws[r][7], o);
-            if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
-        }
-    }
+    idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+        if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(lo, hi);
+    });
 }
 
 void launch_idct(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s) {
@@ -679,6 +688,78 @@ struct ChromaPlane {  // per-pixel path
 
 constexpr int kCTileRows = 8 * (int)kColorMcuRows + 2;  // chroma rows of a 4:2:0 tile plus one halo row above and below
 
+// Chroma tile of a 4:2:0 image: rows cy0-1 .. cy0+32, columns cx0-4 .. cx0+131 as aligned words; s_c column = chroma column
+// - cx0 + 4.  Coordinates are clamped to the real plane extent (dw x dh samples) and the first / last real column is
+// replicated into the halo position, which is what the edge rules of the triangle filter amount to.
+// Warp q loads tile rows q, q + 8, ... of both components; a lane loads word `lane` and, for two lanes, word 32 + lane.
+// Every thread of the CTA (256) must call this; the tile is complete when it returns.
+__device__ __forceinline__ void load_chroma_tile(uint8_t (&s_c)[2][kCTileRows][kCTileCols], const JpegWave& w, const JpegDesc& d,
+                                                 int tx, int ty, int dw, int dh) {
+    const int lane = threadIdx.x & 31, rowi = threadIdx.x >> 5;
+    const int cx0 = tx * (int)(kColorTileW / 2), cy0 = ty * 8 * (int)kColorMcuRows;
+    constexpr int kWords = kCTileCols / 4;  // 34
+    const uint32_t cpitch = d.plane_pitch[1];
+    const int wmax = (int)(cpitch / 4) - 1, w0 = cx0 / 4 - 1;
+    const uint8_t* cb_base = w.planes + d.plane_off[1];
+    const uint8_t* cr_base = w.planes + d.plane_off[2];
+#pragma unroll
+    for (int rr = 0; rr < (kCTileRows + 7) / 8; ++rr) {
+        const int r = rowi + 8 * rr;
+        if (r < kCTileRows) {
+            const int gy = min(max(cy0 + r - 1, 0), dh - 1);
+            const uint32_t* gb = reinterpret_cast<const uint32_t*>(cb_base + (size_t)gy * cpitch);
+            const uint32_t* gr = reinterpret_cast<const uint32_t*>(cr_base + (size_t)gy * cpitch);
+            uint32_t* sb = reinterpret_cast<uint32_t*>(s_c[0][r]);
+            uint32_t* sr = reinterpret_cast<uint32_t*>(s_c[1][r]);
+            const int g0 = min(max(w0 + lane, 0), wmax);
+            sb[lane] = __ldg(gb + g0);
+            sr[lane] = __ldg(gr + g0);
+            if (lane < kWords - 32) {
+                const int g1 = min(max(w0 + 32 + lane, 0), wmax);
+                sb[32 + lane] = __ldg(gb + g1);
+                sr[32 + lane] = __ldg(gr + g1);
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * kCTileRows) {
+        const int comp = threadIdx.x / kCTileRows, r = threadIdx.x - comp * kCTileRows;
+        if (cx0 == 0) s_c[comp][r][3] = s_c[comp][r][4];
+        const int last = dw - 1 - cx0;  // tile-local index of the last real column
+        if (last >= 0 && last < (int)(kColorTileW / 2)) s_c[comp][r][4 + last + 1] = s_c[comp][r][4 + last];
+    }
+    __syncthreads();
+}
+
+// Triangle upsampling of the chroma for 8 pixels of two output rows that read the same two chroma rows: row A has
+// tile row p as its near row and p + 1 as its far row, row B the other way round (output rows 2j+1 and 2j+2 of the
+// image).  cl = s_c column of the thread's first chroma sample (a word boundary).  Results are sample - 128.
+__device__ __forceinline__ void chroma_pair(const uint8_t (&s_c)[2][kCTileRows][kCTileCols], int p, int cl, int32_t (&cbA)[8],
+                                            int32_t (&crA)[8], int32_t (&cbB)[8], int32_t (&crB)[8]) {
+    constexpr uint32_t kEvenA = 0x03090103u, kOddA = 0x01030309u;  // bytes: (near a, far a, near b, far b)
+    constexpr uint32_t kEvenB = 0x09030301u, kOddB = 0x03010903u;  // the same bytes with near and far exchanged
+    constexpr uint32_t kE = (uint32_t)(8 - 2048), kO = (uint32_t)(7 - 2048);  // rounding term minus 128 * 16
+#pragma unroll
+    for (int comp = 0; comp < 2; ++comp) {
+        const uint32_t* nr = reinterpret_cast<const uint32_t*>(&s_c[comp][p][cl]);
+        const uint32_t* fr = reinterpret_cast<const uint32_t*>(&s_c[comp][p + 1][cl]);
+        const uint32_t Ln = nr[-1], Mn = nr[0], Nn = nr[1], Lf = fr[-1], Mf = fr[0], Nf = fr[1];
+        const uint32_t I0 = __byte_perm(Mn, Mf, 0x5140), J = __byte_perm(Mn, Mf, 0x6251), I1 = __byte_perm(Mn, Mf, 0x7362);
+        const uint32_t Lp = __byte_perm(__byte_perm(Ln, Lf, 0x0073), I0, 0x5410);  // (c-1, c)
+        const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
+        int32_t* da = comp ? crA : cbA;
+        int32_t* db = comp ? crB : cbB;
+        da[0] = (int32_t)dp4a_u(Lp, kEvenA, kE) >> 4; da[1] = (int32_t)dp4a_u(I0, kOddA, kO) >> 4;
+        da[2] = (int32_t)dp4a_u(I0, kEvenA, kE) >> 4; da[3] = (int32_t)dp4a_u(J, kOddA, kO) >> 4;
+        da[4] = (int32_t)dp4a_u(J, kEvenA, kE) >> 4;  da[5] = (int32_t)dp4a_u(I1, kOddA, kO) >> 4;
+        da[6] = (int32_t)dp4a_u(I1, kEvenA, kE) >> 4; da[7] = (int32_t)dp4a_u(Rp, kOddA, kO) >> 4;
+        db[0] = (int32_t)dp4a_u(Lp, kEvenB, kE) >> 4; db[1] = (int32_t)dp4a_u(I0, kOddB, kO) >> 4;
+        db[2] = (int32_t)dp4a_u(I0, kEvenB, kE) >> 4; db[3] = (int32_t)dp4a_u(J, kOddB, kO) >> 4;
+        db[4] = (int32_t)dp4a_u(J, kEvenB, kE) >> 4;  db[5] = (int32_t)dp4a_u(I1, kOddB, kO) >> 4;
+        db[6] = (int32_t)dp4a_u(I1, kEvenB, kE) >> 4; db[7] = (int32_t)dp4a_u(Rp, kOddB, kO) >> 4;
+    }
+}
+
 __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t first_tile) {
     __shared__ __align__(16) uint8_t s_c[2][kCTileRows][kCTileCols];
     __shared__ uint32_t s_img;
@@ -713,42 +794,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
     }
     const int dw = (W + hs - 1) / hs, dh = (H + vs - 1) / vs;
     if (hs == 2 && vs == 2 && dw > 2) {
-        // chroma tile: rows cy0-1 .. cy0+16, columns cx0-4 .. cx0+131 as aligned words; s_c column = chroma column - cx0 + 4.
-        // Warp q loads tile rows q, q + 8, ... of both components; a lane loads word `lane` and, for two lanes, word 32 + lane.
-        const int cx0 = (int)tx * (int)(kColorTileW / 2), cy0 = (int)ty * 8 * (int)kColorMcuRows;
-        constexpr int kWords = kCTileCols / 4;  // 34
-        const uint32_t cpitch = d.plane_pitch[1];
-        const int wmax = (int)(cpitch / 4) - 1, w0 = cx0 / 4 - 1;
-        const uint8_t* cb_base = w.planes + d.plane_off[1];
-        const uint8_t* cr_base = w.planes + d.plane_off[2];
-#pragma unroll
-        for (int rr = 0; rr < (kCTileRows + 7) / 8; ++rr) {
-            const int r = rowi + 8 * rr;
-            if (r < kCTileRows) {
-                const int gy = min(max(cy0 + r - 1, 0), dh - 1);
-                const uint32_t* gb = reinterpret_cast<const uint32_t*>(cb_base + (size_t)gy * cpitch);
-                const uint32_t* gr = reinterpret_cast<const uint32_t*>(cr_base + (size_t)gy * cpitch);
-                uint32_t* sb = reinterpret_cast<uint32_t*>(s_c[0][r]);
-                uint32_t* sr = reinterpret_cast<uint32_t*>(s_c[1][r]);
-                const int g0 = min(max(w0 + lane, 0), wmax);
-                sb[lane] = __ldg(gb + g0);
-                sr[lane] = __ldg(gr + g0);
-                if (lane < kWords - 32) {
-                    const int g1 = min(max(w0 + 32 + lane, 0), wmax);
-                    sb[32 + lane] = __ldg(gb + g1);
-                    sr[32 + lane] = __ldg(gr + g1);
-                }
-            }
-        }
-        __syncthreads();
-        // replicate the plane's first / last real column into the halo positions
-        if (threadIdx.x < 2 * kCTileRows) {
-            const int comp = threadIdx.x / kCTileRows, r = threadIdx.x - comp * kCTileRows;
-            if (cx0 == 0) s_c[comp][r][3] = s_c[comp][r][4];
-            const int last = dw - 1 - cx0;  // tile-local index of the last real column
-            if (last >= 0 && last < (int)(kColorTileW / 2)) s_c[comp][r][4 + last + 1] = s_c[comp][r][4 + last];
-        }
-        __syncthreads();
+        load_chroma_tile(s_c, w, d, (int)tx, (int)ty, dw, dh);
         if (x >= W) return;
         const int cl = lane * 4 + 4;  // s_c column of this thread's first chroma sample (a word boundary)
         const int npx = min(8, W - x);
@@ -756,9 +802,6 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
         // the tile is shifted up by one row -- it covers rows 64 ty - 1 .. 64 ty + 62 -- and a thread converts such a
         // pair at a time: the byte gathering is done once, the second row only swaps the weights.
         const int y_first = (int)ty * 8 * 2 * (int)kColorMcuRows - 1;
-        constexpr uint32_t kEvenA = 0x03090103u, kOddA = 0x01030309u;  // bytes: (near a, far a, near b, far b)
-        constexpr uint32_t kEvenB = 0x09030301u, kOddB = 0x03010903u;  // the same bytes with near and far exchanged
-        constexpr uint32_t kE = (uint32_t)(8 - 2048), kO = (uint32_t)(7 - 2048);  // rounding term minus 128 * 16
         auto luma = [&](int y) -> uint2 {
             return (y >= 0 && y < H) ? __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x)) : make_uint2(0, 0);
         };
@@ -771,25 +814,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
             const uint2 ya = nextA, yb = nextB;
             if (m + 1 < (int)kColorMcuRows) { nextA = luma(yA + 16); nextB = luma(yB + 16); }  // next pair's luma in flight
             int32_t cbA[8], crA[8], cbB[8], crB[8];
-#pragma unroll
-            for (int comp = 0; comp < 2; ++comp) {
-                const uint32_t* nr = reinterpret_cast<const uint32_t*>(&s_c[comp][p][cl]);
-                const uint32_t* fr = reinterpret_cast<const uint32_t*>(&s_c[comp][p + 1][cl]);
-                const uint32_t Ln = nr[-1], Mn = nr[0], Nn = nr[1], Lf = fr[-1], Mf = fr[0], Nf = fr[1];
-                const uint32_t I0 = __byte_perm(Mn, Mf, 0x5140), J = __byte_perm(Mn, Mf, 0x6251), I1 = __byte_perm(Mn, Mf, 0x7362);
-                const uint32_t Lp = __byte_perm(__byte_perm(Ln, Lf, 0x0073), I0, 0x5410);  // (c-1, c)
-                const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
-                int32_t* da = comp ? crA : cbA;
-                int32_t* db = comp ? crB : cbB;
-                da[0] = (int32_t)dp4a_u(Lp, kEvenA, kE) >> 4; da[1] = (int32_t)dp4a_u(I0, kOddA, kO) >> 4;
-                da[2] = (int32_t)dp4a_u(I0, kEvenA, kE) >> 4; da[3] = (int32_t)dp4a_u(J, kOddA, kO) >> 4;
-                da[4] = (int32_t)dp4a_u(J, kEvenA, kE) >> 4;  da[5] = (int32_t)dp4a_u(I1, kOddA, kO) >> 4;
-                da[6] = (int32_t)dp4a_u(I1, kEvenA, kE) >> 4; da[7] = (int32_t)dp4a_u(Rp, kOddA, kO) >> 4;
-                db[0] = (int32_t)dp4a_u(Lp, kEvenB, kE) >> 4; db[1] = (int32_t)dp4a_u(I0, kOddB, kO) >> 4;
-                db[2] = (int32_t)dp4a_u(I0, kEvenB, kE) >> 4; db[3] = (int32_t)dp4a_u(J, kOddB, kO) >> 4;
-                db[4] = (int32_t)dp4a_u(J, kEvenB, kE) >> 4;  db[5] = (int32_t)dp4a_u(I1, kOddB, kO) >> 4;
-                db[6] = (int32_t)dp4a_u(I1, kEvenB, kE) >> 4; db[7] = (int32_t)dp4a_u(Rp, kOddB, kO) >> 4;
-            }
+            chroma_pair(s_c, p, cl, cbA, crA, cbB, crB);
             uint32_t px[6];
             if (yA >= 0) {
                 ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
@@ -844,6 +869,187 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
 
 void launch_color(const JpegWave& w, uint32_t first_tile, uint32_t count, cudaStream_t s) {
     if (count) k_color<<<count, kColorThreads, 0, s>>>(w, first_tile);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Fused path for three-component 4:2:0 images (the common case): the luma samples never go to memory.
+//   k_idct_chroma  IDCT of the Cb and Cr blocks only, into the chroma planes (0.5 bytes per pixel instead of 1.5);
+//   k_luma_color   one CTA per 256 x 64 pixel tile (16 x 4 MCUs = 256 luma blocks, one per thread): luma coefficients
+//                  staged with asynchronous copies, the chroma tile (with its halo, which is why chroma cannot be
+//                  reconstructed tile by tile) loaded from the planes meanwhile, luma IDCT into shared memory, then
+//                  upsampling and colour conversion from shared memory, RGB out.
+// Traffic per pixel: 1 + 0.5 (chroma) + 2 + 0.5 + 3 (fused kernel) plus the zero write-back, against
+// 3 + 1.5 + 1.5 + 3 for the two general kernels.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct_chroma(JpegWave w, uint32_t first, uint32_t count, bool rezero) {
+    const uint32_t local = blockIdx.x * kIdctThreads + threadIdx.x;
+    const bool valid = local < count;
+    const uint32_t q = first + min(local, count - 1);
+    __shared__ __align__(16) uint4 s_coef[kIdctThreads / 32][256];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t o = owner_of(w.fused_chroma, q);
+    const JpegDesc& d = w.descs[w.fused_first + o];
+    const uint32_t ql = q - __ldg(w.fused_chroma.first + o);
+    const uint32_t mcu = ql >> 1, which = ql & 1u;
+    const uint32_t blk = (uint32_t)d.block_off + mcu * 6u + 4u + which;  // this lane's block in the coefficient array
+    // Lanes 2j and 2j + 1 hold the Cb and Cr block of one MCU: 256 consecutive bytes.  Step i copies the eight rows of
+    // blocks 4i .. 4i + 3 of the warp, lane l row l % 8 of block 4i + l / 8 (block addresses come from the owning lanes).
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t bb = i * 4 + (lane >> 3), r = lane & 7;
+        const uint32_t gb = __shfl_sync(0xFFFFFFFFu, blk, bb);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&s_coef[warp][bb * 8 + (r ^ (bb & 7))]);
+        const void* src = w.coef + (size_t)gb * 64 + r * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t my = mcu / d.mcux, mx = mcu - my * d.mcux;
+    const uint32_t comp = 1u + which;
+    const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[comp] * 32);
+    const uint32_t pitch = d.plane_pitch[comp];
+    uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(my * 8) * pitch + mx * 8;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    uint4 c[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c[r] = s_coef[warp][lane * 8 + (r ^ (lane & 7))];
+    if (rezero) {
+        uint32_t rowmask = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
+        if (!valid) rowmask = 0;  // lanes past the end stand in for the last block, which its own lane zeroes
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t src_lane = i * 4 + (lane >> 3);
+            const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, src_lane);
+            const uint32_t gb = __shfl_sync(0xFFFFFFFFu, blk, src_lane);
+            if ((m >> (lane & 7)) & 1u) reinterpret_cast<uint4*>(w.coef + (size_t)gb * 64)[lane & 7] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+        if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(lo, hi);
+    });
+}
+
+void launch_idct_chroma(const JpegWave& w, uint32_t first, uint32_t count, bool rezero, cudaStream_t s) {
+    if (count) k_idct_chroma<<<(count + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w, first, count, rezero);
+}
+
+constexpr int kFusedThreads = 256;
+constexpr int kLumaPitch = kColorTileW + 8;  // 8 * pitch = 64 (mod 128): the two block rows a half warp stores to fall into different banks
+constexpr int kLumaRows = 16 * (int)kColorMcuRows;
+
+struct FusedSmem {
+    union {
+        uint4 coef[kFusedThreads / 32][256];    // staged luma coefficients, 4 KB per warp (8 MCUs x 4 blocks)
+        uint8_t luma[kLumaRows][kLumaPitch];    // ... overwritten by the reconstructed luma tile
+    };
+    uint8_t c[2][kCTileRows][kCTileCols];
+};
+
+#ifndef DG_FUSED_MIN_CTAS
+#define DG_FUSED_MIN_CTAS 3
+#endif
+__global__ void __launch_bounds__(kFusedThreads, DG_FUSED_MIN_CTAS) k_luma_color(JpegWave w, uint32_t first_tile, bool rezero) {
+    __shared__ __align__(16) FusedSmem sm;
+    __shared__ uint32_t s_img;
+    if (threadIdx.x == 0) s_img = owner_of(w.fused_tiles, first_tile + blockIdx.x);
+    __syncthreads();
+    const uint32_t o = s_img;
+    const JpegDesc& d = w.descs[w.fused_first + o];
+    const uint32_t tile = first_tile + blockIdx.x - __ldg(w.fused_tiles.first + o);
+    const int W = (int)d.width, H = (int)d.height;
+    const uint32_t tiles_x = (d.width + kColorTileW - 1) / kColorTileW;
+    const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // ---- luma coefficients of the tile: warp q owns MCU row q / 2 of the tile and MCUs 8 (q % 2) .. + 7 of it; step i
+    //      copies the four luma blocks of MCU i, 512 consecutive bytes.  MCUs outside the image are replaced by the
+    //      nearest one inside (their results land in tile positions no output pixel reads).
+    const uint32_t mrow = warp >> 1, half = warp & 1u;
+    const uint32_t my = ty * kColorMcuRows + mrow, mx0 = tx * 16 + half * 8;
+    const uint32_t myc = min(my, d.mcuy - 1);
+    const int16_t* row_base = w.coef + ((size_t)d.block_off + (size_t)myc * d.mcux * 6u) * 64;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t bb = i * 4 + (lane >> 3), r = lane & 7;
+        const uint32_t mxc = min(mx0 + i, d.mcux - 1);
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&sm.coef[warp][bb * 8 + (r ^ (bb & 7))]);
+        const void* src = row_base + (size_t)mxc * 384 + lane * 8;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    // ---- chroma tile from the planes (written by k_idct_chroma), while the copies are in flight
+    const int dw = (W + 1) / 2, dh = (H + 1) / 2;
+    load_chroma_tile(sm.c, w, d, (int)tx, (int)ty, dw, dh);
+
+    // ---- luma IDCT: one block per thread
+    const uint32_t mcu_local = lane >> 2, k = lane & 3u;
+    const bool valid = my < d.mcuy && mx0 + mcu_local < d.mcux;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    uint4 c[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c[r] = sm.coef[warp][lane * 8 + (r ^ (lane & 7))];
+    if (rezero) {
+        uint32_t rowmask = 0;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
+        if (!valid) rowmask = 0;  // a stand-in MCU belongs to other lanes (or another CTA, which may not have read it yet)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
+            if ((m >> (lane & 7)) & 1u)
+                reinterpret_cast<uint4*>(const_cast<int16_t*>(row_base) + (size_t)(mx0 + i) * 384)[lane] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    __syncthreads();  // every warp has its coefficients in registers: the staging area becomes the luma tile
+    {
+        const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[0] * 32);
+        const uint32_t bx = half * 16 + mcu_local * 2 + (k & 1u), by = mrow * 2 + (k >> 1);
+        uint8_t* dst = &sm.luma[by * 8][bx * 8];
+        idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+            *reinterpret_cast<uint2*>(dst + r * kLumaPitch) = make_uint2(lo, hi);
+        });
+    }
+    __syncthreads();
+
+    // ---- upsampling + colour conversion.  Output rows 2j+1 and 2j+2 read the same two chroma rows with the near / far
+    //      weights exchanged, so a thread converts such a pair at a time (pair p of the tile = tile rows 2p-1 and 2p, chroma
+    //      tile rows p and p+1).  The tile's first row is the second half of pair 0 and its last row the first half of
+    //      pair 32: warp 0 converts those two halves in a fifth step.
+    const int x = (int)tx * (int)kColorTileW + (int)lane * 8;
+    if (x >= W) return;
+    const int npx = min(8, W - x);
+    const int cl = (int)lane * 4 + 4;
+    const int y0 = (int)ty * kLumaRows;
+    uint8_t* out = w.out + d.out_off;
+#pragma unroll 1
+    for (int m = 0; m < 5; ++m) {
+        const int p = (int)warp + 8 * m;
+        if (p > kLumaRows / 2) break;
+        const int yA = y0 + 2 * p - 1, yB = yA + 1;
+        const bool doA = p > 0 && yA < H, doB = p < kLumaRows / 2 && yB < H;
+        if (!doA && !doB) break;
+        int32_t cbA[8], crA[8], cbB[8], crB[8];
+        chroma_pair(sm.c, p, cl, cbA, crA, cbB, crB);
+        uint32_t px[6];
+        if (doA) {
+            const uint2 ya = *reinterpret_cast<const uint2*>(&sm.luma[2 * p - 1][lane * 8]);
+            ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
+            store_rgb8(out + ((size_t)yA * W + x) * 3, px, npx);
+        }
+        if (doB) {
+            const uint2 yb = *reinterpret_cast<const uint2*>(&sm.luma[2 * p][lane * 8]);
+            ycc_to_rgb8(yb.x, yb.y, cbB, crB, px);
+            store_rgb8(out + ((size_t)yB * W + x) * 3, px, npx);
+        }
+    }
+}
+
+void launch_luma_color(const JpegWave& w, uint32_t first_tile, uint32_t count, bool rezero, cudaStream_t s) {
+    if (count) k_luma_color<<<count, kFusedThreads, 0, s>>>(w, first_tile, rezero);
 }
 
 }  // namespace dg

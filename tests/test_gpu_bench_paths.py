@@ -119,3 +119,23 @@ def test_multi_wave_decode_and_resize_bit_exact():
                     assert_same(outs[i], want, f"pass {rerun} image {i}")
     finally:
         c.close()
+
+
+def test_general_kernels_still_decode_420_images():
+    # three-component 4:2:0 images normally take the fused kernels; with DATAGO_B200_FUSED=0 they go through the general
+    # IDCT and colour kernels (the path of every other sampling), which must give the same bytes
+    rng = np.random.default_rng(202)
+    datas = [jpeg(rng, 640, 480), jpeg(rng, 257, 131, rst=4), jpeg(rng, 17, 33), jpeg(rng, 1024, 768, q=70),
+             jpeg(rng, 100, 60, "4:4:4"), jpeg(rng, 90, 70, None, 80, 0, True)]
+    want = _oracle_all(datas)
+    with _with_env("DATAGO_B200_FUSED", "0"):
+        c = dg.Context(0, None)
+    try:
+        for i, (st, out, _) in enumerate(c.process(datas)):
+            assert st == 0
+            assert_same(out, want[i], f"general path image {i}")
+    finally:
+        c.close()
+    for i, (st, out, _) in enumerate(ctx().process(datas)):
+        assert st == 0
+        assert_same(out, want[i], f"fused path image {i}")
