@@ -1,24 +1,30 @@
-"""Benchmark of the image hot path on B200: decoded(+bucketed) images/s on seeded synthetic JPEGs.
+"""Benchmark of the image hot path on B200: decoded(+bucketed) images/s on seeded synthetic inputs.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c0|c1] [--images M] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c0|c1|c3|c4] [--images M] [--impl reference]
 
-A step is one pass of the path over the whole workload (default: the 8192-JPEG decode-throughput set).  `value` is
-measured with the compressed inputs already in HBM (CUDA events on the library's stream around K back-to-back passes);
-`e2e` goes through the public batch API from host JPEG bytes to host pixel buffers.  Multi-GPU runs are weak-scaled:
-every rank owns one workload-sized shard of an N-times larger job (contiguous rank slices, the rule datago's file
-source uses) and there is no collective on the data path; only the timing is reduced across ranks.
-`--impl reference` times the CPU implementation of the same path (the oracle port; the reference's Rust crates are not
-buildable here) on all host cores.
+A step is one pass of the path over the whole workload (default: the 8192-JPEG decode-throughput set, C2).  `value` is
+measured with the inputs already in HBM (CUDA events around K back-to-back passes); `e2e` goes through the public batch
+API from host bytes to host pixel buffers.  The default run then measures the local-file set (C0, decode + bucket
+crop-resize) and the resize-only set (C1) in the same process, shorter, and reports them under `configs`.
+Multi-GPU runs are weak-scaled: every rank owns one workload-sized shard of an N-times larger job (contiguous rank
+slices, the rule datago's file source uses); `--workload c3` instead splits one fixed set of tar shards over the ranks
+by key hash, datago's webdataset rule (strong scaling).  There is no collective on the data path; only the timing is
+reduced across ranks.  `--impl reference` times the CPU implementation of the same path (the oracle port; the
+reference's Rust crates cannot be built here) on all host cores.
 """
 import argparse
+import io
 import json
+import math
 import os
 import pickle
 import statistics
 import subprocess
 import sys
+import tarfile
 import threading
 import time
+from concurrent.futures import ThreadPoolExecutor
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -26,6 +32,13 @@ sys.path.insert(0, ROOT)
 import numpy as np  # noqa: E402
 
 METRIC = "decoded+bucketed images/s"
+LABELS = {
+    "c0": "C0 local-file set: {n} 4:2:0 q90 JPEGs 256..2048, decode + 1024/32 bucket crop-resize",
+    "c1": "C1 resize-only: {n} raw RGB buffers 512..4096, 512/16 buckets",
+    "c2": "C2 JPEG decode throughput: {n} baseline 4:2:0 JPEGs 512..1536, q75-95, half with restart interval 4, decode to RGB8",
+    "c3": "C3 webdataset-shaped: {n} samples (.jpg up to 2048 + .json) in local tar shards of 1000, key-hash dispatch, decode + 1024/32 bucket crop-resize",
+    "c4": "C4 multi-payload: {n} samples of a 4:4:4 JPEG up to 4096 plus a same-size L8 mask, both into the image's 2048/64 bucket",
+}
 
 
 def load_peaks():
@@ -35,30 +48,117 @@ def load_peaks():
     return 6650.0, "fallback"
 
 
-def dataset(workload, count, rank, world, barrier):
-    """The seeded workload, generated once per box (rank 0) and shared through /dev/shm."""
-    from datago_b200 import synth
-    cache = f"/dev/shm/datago_b200_{workload}_{count}.pkl"
+def load_traffic():
+    """DRAM bytes per pixel of the post-entropy kernels as ncu counted them on a small case (profiles/traffic.json)."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    return json.load(open(path)) if os.path.exists(path) else {}
+
+
+# ---- workloads ------------------------------------------------------------------------------------------------------
+class Workload:
+    """items: bytes (JPEG files) or numpy arrays (raw pixels); forced[i]: bucket key forced on item i or None;
+    samples: how many samples the items make up (C4: two items per sample)."""
+
+    def __init__(self, name, items, forced, samples, cfg):
+        self.name, self.items, self.forced, self.samples, self.cfg = name, items, forced, samples, cfg
+
+
+def _cached(tag, make, rank, barrier):
+    """Generated once per box by rank 0 and shared through /dev/shm."""
+    cache = f"/dev/shm/datago_b200_{tag}.pkl"
     if rank == 0 and not os.path.exists(cache):
-        procs = max(1, (os.cpu_count() or 8) - 1)
         t = time.time()
-        items = synth.make(workload, range(count), processes=procs)
+        obj = make()
         with open(cache + ".tmp", "wb") as f:
-            pickle.dump(items, f, protocol=4)
+            pickle.dump(obj, f, protocol=4)
         os.replace(cache + ".tmp", cache)
-        print(f"[bench] generated {count} {workload} items on {procs} processes in {time.time() - t:.1f}s", file=sys.stderr)
+        print(f"[bench] generated {tag} in {time.time() - t:.1f}s", file=sys.stderr)
     barrier()
     with open(cache, "rb") as f:
         return pickle.load(f)
+
+
+def shard_paths(count):
+    """C3: seeded tar shards of 1000 samples under /dev/shm (written once per box)."""
+    from datago_b200 import synth
+    n_shards = (count + 999) // 1000
+    d = f"/dev/shm/datago_b200_c3_{count}"
+    paths = [os.path.join(d, f"shard-{s:05d}.tar") for s in range(n_shards)]
+    if not all(os.path.exists(p) for p in paths):
+        os.makedirs(d, exist_ok=True)
+        t = time.time()
+        import multiprocessing as mp
+        jobs = [(paths[s] + ".tmp", s * 1000, min(1000, count - s * 1000)) for s in range(n_shards)]
+        with mp.get_context("fork").Pool(max(1, (os.cpu_count() or 8) - 1)) as pool:
+            pool.starmap(synth.write_shard, jobs)
+        for p in paths:
+            os.replace(p + ".tmp", p)
+        print(f"[bench] wrote {n_shards} C3 shards in {time.time() - t:.1f}s", file=sys.stderr)
+    return paths
+
+
+def load_workload(name, count, rank, world, barrier, ctx_for_keys=None):
+    from datago_b200 import synth
+    import datago_b200 as dg
+    cfg = synth.IMAGE_CONFIGS[name]
+    procs = max(1, (os.cpu_count() or 8) - 1)
+    if name == "c3":
+        # datago's webdataset rule: every rank walks every shard and keeps the samples whose key hashes to it
+        # (src/generator_wds.rs:140-148)
+        if rank == 0:
+            shard_paths(count)
+        barrier()
+        items = []
+        for p in shard_paths(count):
+            with tarfile.open(p) as tf:
+                for m in tf:
+                    stem, ext = os.path.splitext(m.name)
+                    if ext == ".jpg" and dg.key_rank(stem, world) == rank:
+                        items.append(tf.extractfile(m).read())
+        return Workload(name, items, None, len(items), cfg)
+    if name == "c4":
+        pairs = _cached(f"c4_{count}", lambda: synth.make("c4", range(count), processes=procs), rank, barrier)
+        start, end = dg.rank_slice(world * count, rank, world)
+        items, forced = [], []
+        for i in range(start, end):
+            jpg, mask = pairs[i % count]
+            info = dg.jpeg_probe(jpg)
+            key = ctx_for_keys.plan_geometry(info.width, info.height, 3).key.decode()
+            items += [jpg, mask]
+            forced += [None, key]  # the mask goes into the image's bucket (src/worker_wds.rs:68-76)
+        return Workload(name, items, forced, end - start, cfg)
+    items = _cached(f"{name}_{count}", lambda: synth.make(name, range(count), processes=procs), rank, barrier)
+    start, end = dg.rank_slice(world * count, rank, world)  # this rank's shard of the N x workload job
+    return Workload(name, [items[i % count] for i in range(start, end)], None, end - start, cfg)
+
+
+def workload_stats(wl):
+    """Pixels and algorithmic bytes of one pass: coefficients 2 B per MCU-padded sample, RGB 3 B per pixel."""
+    import datago_b200 as dg
+    st = dict(pixels=0, compressed=0, coef_bytes=0, plane_bytes=0, rgb_bytes=0, rst_compressed=0, rst_coef_bytes=0)
+    for it in wl.items:
+        if isinstance(it, (bytes, bytearray)):
+            i = dg.jpeg_probe(it)
+            blocks = i.mcux * i.mcuy * (1 if i.channels == 1 else i.hsamp * i.vsamp + 2)
+            st["pixels"] += i.width * i.height
+            st["compressed"] += i.scan_len
+            st["coef_bytes"] += blocks * 128      # 2 * s * P_mcu
+            st["plane_bytes"] += blocks * 64
+            st["rgb_bytes"] += i.width * i.height * i.channels
+            if i.restart_interval:
+                st["rst_compressed"] += i.scan_len
+                st["rst_coef_bytes"] += blocks * 128
+        else:
+            st["pixels"] += it.shape[0] * it.shape[1]
+            st["rgb_bytes"] += it.nbytes
+    return st
 
 
 class ClockSampler:
     QUERY = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index):
-        self.index = index
-        self.rows = []
-        self.proc = None
+        self.index, self.rows, self.proc = index, [], None
 
     def start(self):
         try:
@@ -89,60 +189,48 @@ class ClockSampler:
         self.thread.join(timeout=2)
         rows = list(self.rows)
         inside = [r for (t, r) in rows if getattr(self, "t0", 0) <= t <= getattr(self, "t1", float("inf"))]
-        self.rows = inside if len(inside) >= 3 else [r for (_, r) in rows]
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        rows = inside if len(inside) >= 3 else [r for (_, r) in rows]
+        num = lambda s: s.replace(".", "").isdigit()  # noqa: E731
+        sm = [float(r[0]) for r in rows if r and num(r[0])]
+        mx = [float(r[1]) for r in rows if len(r) > 1 and num(r[1])]
+        pw = [float(r[2]) for r in rows if len(r) > 2 and num(r[2])]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i] == "Active" for r in self.rows)]
-        pw = [float(r[2]) for r in self.rows if len(r) > 2 and r[2].replace(".", "").isdigit()]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 3 + i and r[3 + i] == "Active" for r in rows)]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons}
 
 
-def workload_stats(items, workload):
-    """Pixels and algorithmic bytes of one pass: coefficients 2 B per MCU-padded sample, planes 1 B per sample, RGB 3 B per pixel."""
-    import datago_b200 as dg
-    st = dict(images=len(items), pixels=0, compressed=0, coef_bytes=0, plane_bytes=0, rgb_bytes=0, ecs_bits=0)
-    for it in items:
-        if isinstance(it, (bytes, bytearray)):
-            i = dg.jpeg_probe(it)
-            bpm = 1 if i.channels == 1 else i.hsamp * i.vsamp + 2
-            blocks = i.mcux * i.mcuy * bpm
-            st["pixels"] += i.width * i.height
-            st["compressed"] += i.scan_len
-            st["coef_bytes"] += blocks * 128      # 2 * s * P_mcu
-            st["plane_bytes"] += blocks * 64
-            st["rgb_bytes"] += i.width * i.height * i.channels
-        else:
-            st["pixels"] += it.shape[0] * it.shape[1]
-            st["rgb_bytes"] += it.nbytes
-    return st
-
-
-def cpu_baseline(items, kind, cfg, budget_s=12.0):
-    """The oracle port on all host cores over a bounded sample of the workload."""
+# ---- CPU arm ----------------------------------------------------------------------------------------------------------
+def cpu_baseline(wl, budget_s=12.0):
+    """The oracle port on all host cores over a bounded sample of the workload (in samples per second)."""
     import oracle
     threads = os.cpu_count() or 1
-    probe_n = min(len(items), max(2 * threads, 8))
-    call = oracle.run_batch(items[:probe_n], kind, cfg, threads)
+    if wl.name == "c4":  # JPEGs decode + resize, masks resize into the same bucket (same size, same aspect ratio)
+        parts = [([x for x in wl.items if isinstance(x, bytes)], 1), ([x for x in wl.items if not isinstance(x, bytes)], 2)]
+    else:
+        parts = [(wl.items, {"c0": 1, "c1": 2, "c2": 0, "c3": 1}[wl.name])]
+    n_all = len(parts[0][0])
+    probe_n = min(n_all, max(2 * threads, 8))
     t = time.time()
-    call()
-    per_image = max(1e-4, (time.time() - t) / probe_n)  # seconds per image with all threads busy
-    n = int(min(len(items), max(probe_n, budget_s / per_image)))
-    call = oracle.run_batch(items[:n], kind, cfg, threads)
+    for items, kind in parts:
+        oracle.run_batch(items[:probe_n], kind, wl.cfg, threads)()
+    per = max(1e-4, (time.time() - t) / probe_n)
+    n = int(min(n_all, max(probe_n, budget_s / per)))
+    calls = [oracle.run_batch(items[:n], kind, wl.cfg, threads) for items, kind in parts]
     t = time.time()
-    ok = call()
+    ok = min(c() for c in calls)
     dt = time.time() - t
     return {"value": ok / dt, "unit": "images/s", "cores": threads, "kind": "port",
-            "sample": f"first {n} of {len(items)} items of the workload, {dt:.1f}s wall"}
+            "sample": f"first {n} of {n_all} samples of the workload, {dt:.1f}s wall; scalar C++ restatement, no SIMD decoder"}
 
 
-def pil_yardstick(items, budget_s=6.0):
+def pil_yardstick(items, budget_s=5.0):
     """libjpeg-turbo through Pillow on a thread pool: an independent SIMD-optimised CPU decoder, for scale."""
-    import io
-    from concurrent.futures import ThreadPoolExecutor
     from PIL import Image
     threads = os.cpu_count() or 1
+    items = [x for x in items if isinstance(x, bytes)]
+    if not items:
+        return None
 
     def one(b):
         return np.asarray(Image.open(io.BytesIO(b)).convert("RGB")).shape[0]
@@ -155,7 +243,264 @@ def pil_yardstick(items, budget_s=6.0):
         t = time.time()
         list(ex.map(one, items[:n2]))
         dt = time.time() - t
-    return {"value": n2 / dt, "unit": "images/s", "cores": threads, "sample": f"{n2} items"}
+    return {"value": n2 / dt, "unit": "images/s", "cores": threads, "sample": f"{n2} items, decode only, Python thread pool"}
+
+
+# ---- GPU arm ----------------------------------------------------------------------------------------------------------
+def parity_check(ctx, batch, wl, limit):
+    """Outside the timed region: payloads of the resident batch against the oracle (first, last, largest, evenly spread)."""
+    import oracle
+    n = len(wl.items)
+    size = lambda x: len(x) if isinstance(x, bytes) else x.size  # noqa: E731
+    pick = sorted({0, n - 1, max(range(n), key=lambda i: size(wl.items[i])), *range(0, n, max(1, n // max(1, limit - 3)))})[:limit]
+
+    def want(i):
+        x, key = wl.items[i], (wl.forced[i] if wl.forced else None)
+        if isinstance(x, bytes):
+            return oracle.jpeg_to_payload(x, wl.cfg, key)[0]
+        return oracle.crop_and_resize(wl.cfg, x, key)[0] if wl.cfg else x
+
+    with ThreadPoolExecutor(os.cpu_count() or 4) as ex:
+        wants = list(ex.map(want, pick))
+    bad = 0
+    for i, w in zip(pick, wants):
+        r = batch.result(i)
+        got = ctx.copy_to_host(r.device_data, int(r.nbytes)) if r.status == 0 else None
+        if got is None or got.size != w.size or not np.array_equal(got, w.reshape(-1)):
+            bad += 1
+    return {"images": len(pick), "mismatches": bad, "checked_against": "oracle, bit-exact"}
+
+
+def resize_bytes(ctx, wl):
+    """crop_and_resize: C * P_used + C * tw * th per image, P_used = the source pixels that map into the crop."""
+    import datago_b200 as dg
+    total = out = 0
+    for k, it in enumerate(wl.items):
+        if isinstance(it, (bytes, bytearray)):
+            i = dg.jpeg_probe(it)
+            w_, h_, c_ = i.width, i.height, i.channels
+        else:
+            h_, w_ = it.shape[:2]
+            c_ = 1 if it.ndim == 2 else it.shape[2]
+        p = ctx.plan_geometry(w_, h_, c_, wl.forced[k] if wl.forced else None)
+        scale = max(p.target_w / w_, p.target_h / h_)
+        used = min(w_, math.ceil(p.target_w / scale)) * min(h_, math.ceil(p.target_h / scale))
+        total += c_ * used + c_ * p.target_w * p.target_h
+        out += c_ * p.target_w * p.target_h
+    return total, out
+
+
+def measure(wl, local_rank, world, barrier, all_max, steps, warmup, e2e_steps, chunk, feeder_threads, parity_limit,
+            kernels_only, peak, traffic):
+    """One workload on this rank's GPU: resident passes, per-stage pass, end-to-end passes.  Returns the report dict."""
+    import torch
+    import datago_b200 as dg
+    cfg, items, forced = wl.cfg, wl.items, wl.forced
+    stats = workload_stats(wl)
+    stream = torch.cuda.Stream()
+    ctx = dg.Context(local_rank, cfg, stream=stream.cuda_stream)
+    out = {}
+
+    # -- inputs resident in HBM: K passes of dg_batch_run on an uploaded batch, CUDA events on a parent stream that the
+    #    library's stream waits on and is waited for
+    b = ctx.batch(items, forced, 0)
+    b.upload()
+    b.sync()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(1.0)  # nvidia-smi needs a moment before its first sample
+    for _ in range(warmup):
+        b.run()
+    b.sync()
+    failed = [i for i in range(len(b)) if b.result(i).status != 0]
+    assert not failed, f"{len(failed)} items failed, first {failed[:5]}"
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    parent, done = torch.cuda.Stream(), torch.cuda.Event()
+    torch.cuda.synchronize()
+    barrier()
+    t_begin = time.time()
+    e0.record(parent)
+    stream.wait_event(e0)
+    for _ in range(steps):
+        b.run()
+    done.record(stream)
+    parent.wait_event(done)
+    e1.record(parent)
+    torch.cuda.synchronize()
+    barrier()
+    sampler.window(t_begin, time.time())
+    elapsed_ms = all_max(e0.elapsed_time(e1))
+    out["clocks"] = sampler.stop()
+    b.sync()
+    out["gpu_launches"] = b.counters()["kernel_launches"] * steps
+    if parity_limit:
+        out["parity_check"] = parity_check(ctx, b, wl, parity_limit)
+    b.close()
+    n_samples = all_max(wl.samples, op="sum")
+    out["value"] = n_samples * steps / (elapsed_ms / 1000.0)
+    out["ms_per_step"] = elapsed_ms / steps
+    out["mpix_per_s"] = out["value"] * stats["pixels"] / max(1, wl.samples) / 1e6
+    if stats["compressed"]:
+        out["compressed_bits_per_pixel"] = round(8.0 * stats["compressed"] / stats["pixels"], 3)
+
+    # -- per-kernel durations: one more pass with CUDA events around every stage.  A timing batch keeps all waves on one
+    #    stream, so each event pair brackets a kernel that ran alone (the timed passes above overlap the waves).
+    tb = ctx.batch(items, forced, dg.BATCH_TIMING)
+    tb.upload()
+    tb.run()
+    tb.run()
+    tb.sync()
+    stage_ms = tb.stage_ms()  # of the last pass
+    tb.close()
+    bytes_of = {"unstuff": 2 * stats["compressed"],
+                "huff_restart": stats["rst_compressed"] + stats["rst_coef_bytes"],
+                "huff_spec": stats["compressed"] - stats["rst_compressed"] + stats["coef_bytes"] - stats["rst_coef_bytes"]}
+    stages = {}
+    for name, ms in stage_ms.items():
+        if ms < 0.02:
+            continue
+        stages[name] = {"ms": round(ms, 3)}
+        if bytes_of.get(name):
+            stages[name]["gbs"] = round(bytes_of[name] / ms / 1e6, 1)
+    out["stages"] = stages
+    out["stage_pass"] = {"ms_serial_sum": round(sum(stage_ms.values()), 3),
+                         "note": "stages timed in a one-stream pass; value is timed with the waves overlapped on two streams"}
+    # The graded figure: the stages after entropy decoding on their algorithmic bytes -- coefficients in (2 bytes per
+    # MCU-padded sample) plus pixels out (decoded RGB, or the bucket-sized payload when a resize follows, in which case
+    # the resize kernels belong to the stage); a resize-only workload is graded on source pixels used + payload.
+    post_ms = stage_ms.get("idct", 0.0) + stage_ms.get("color", 0.0)
+    resize_ms = stage_ms.get("resize_h", 0.0) + stage_ms.get("resize_v", 0.0) + stage_ms.get("resize_shift", 0.0)
+    roofline = None
+    if cfg and cfg.get("crop_and_resize") and resize_ms > 0:
+        rbytes, payload = resize_bytes(ctx, wl)
+        out["resize"] = {"ms": round(resize_ms, 3), "bytes": rbytes, "gbs": round(rbytes / resize_ms / 1e6, 1),
+                         "frac": round(rbytes / resize_ms / 1e6 / peak, 4)}
+        if post_ms > 0:
+            pbytes, pms, kern = stats["coef_bytes"] + payload, post_ms + resize_ms, "idct+color+resize"
+        else:
+            pbytes, pms, kern = rbytes, resize_ms, "resize_h+resize_v+resize_shift"
+    else:
+        pbytes, pms, kern = stats["coef_bytes"] + stats["rgb_bytes"], post_ms, "idct+color"
+    if pms > 0:
+        out["post_entropy"] = {"ms": round(pms, 3), "bytes": pbytes, "gbs": round(pbytes / pms / 1e6, 1),
+                               "frac": round(pbytes / pms / 1e6 / peak, 4)}
+        per_px = (traffic.get(wl.name) or {}).get("dram_bytes_per_pixel")
+        roofline = {"kernel": kern, "bound": "hbm", "achieved": out["post_entropy"]["gbs"], "peak": peak, "unit": "GB/s",
+                    "frac": out["post_entropy"]["frac"], "traffic": int(per_px * stats["pixels"]) if per_px else None,
+                    "algorithmic_bytes": pbytes,
+                    "longest_stage": max(stages, key=lambda k: stages[k]["ms"]) if stages else None}
+    out["roofline"] = roofline
+    huff_ms = stage_ms.get("huff_restart", 0.0) + stage_ms.get("huff_spec", 0.0)
+    if huff_ms:
+        sm_mhz = out["clocks"].get("sm_mhz") or 1965.0
+        out["huffman"] = {"ms": round(huff_ms, 3),
+                          "bits_per_cycle_per_sm": round(stats["compressed"] * 8 / (huff_ms / 1000.0 * sm_mhz * 1e6 * 148), 4)}
+    if kernels_only:
+        ctx.close()
+        return out
+
+    # -- end to end through the batch API: host bytes in, host pixels out.  Sub-batches alternate between two contexts
+    #    (two streams), the way a host batcher drives the library, so that the device-to-host copy of one sub-batch
+    #    overlaps the planning, upload and kernels of the next.
+    chunk = max(1, min(chunk, len(items)))
+    if wl.name == "c4":
+        chunk += chunk % 2  # keep the two payloads of a sample in one sub-batch
+    max_out = 0
+    for c0 in range(0, len(items), chunk):
+        with ctx.batch(items[c0:c0 + chunk], forced[c0:c0 + chunk] if forced else None, 0) as bb:
+            max_out = max(max_out, bb.packed_bytes())
+    lanes = [(ctx, torch.empty(max_out + 4096, dtype=torch.uint8).pin_memory().numpy()),
+             (dg.Context(local_rank, cfg), torch.empty(max_out + 4096, dtype=torch.uint8).pin_memory().numpy())]
+    h2d = d2h = 0
+
+    def finish(bb):
+        nonlocal h2d, d2h
+        bb.sync()
+        assert all(bb.result(i).status == 0 for i in range(0, len(bb), 97))
+        c = bb.counters()
+        h2d += c["h2d_bytes"]
+        d2h += c["d2h_bytes"]
+        bb.close()
+
+    def e2e_pass(to_host=True):
+        nonlocal h2d, d2h
+        h2d = d2h = 0
+        pending = [None, None]
+        for k, c0 in enumerate(range(0, len(items), chunk)):
+            lane_ctx, pin_np = lanes[k % 2]
+            if pending[k % 2] is not None:
+                finish(pending[k % 2])  # the pinned buffer of this lane is free again
+            bb = lane_ctx.batch(items[c0:c0 + chunk], forced[c0:c0 + chunk] if forced else None, 0 if to_host else dg.BATCH_COLLATE)
+            bb.upload()
+            bb.run()
+            if to_host:
+                bb.download_packed(pin_np)  # one copy; payload i is pin_np[result(i).packed_offset:][:nbytes]
+            pending[k % 2] = bb
+        for bb in pending:
+            if bb is not None:
+                finish(bb)
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            fn()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        barrier()
+        return n_samples * e2e_steps / all_max(dt)
+
+    e2e_pass()  # warm-up: grows the library's pinned and device block caches
+    v = timed(e2e_pass)
+    out["e2e"] = {"value": v, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                  "steps": e2e_steps, "batch": chunk, "streams": 2}
+    # Same, with the payloads left in HBM as per-bucket [n, h, w, c] arrays (what a training process on the same GPU
+    # consumes): host bytes in, only the per-image status words come back.
+    v = timed(lambda: e2e_pass(to_host=False))
+    out["e2e_device_payloads"] = {"value": v, "unit": "images/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                                  "note": "payloads stay on the device, collated per bucket; not the headline e2e"}
+    lanes[1][0].close()
+
+    # Same host-to-host job through the per-sample front end: worker threads submit single samples and wait for them,
+    # as datago's tokio workers would; the library cuts the batches (two lanes of up to 512 samples).
+    if feeder_threads > 0 and not forced:
+        flags = dg.BATCH_DECODE_ONLY if not (cfg and cfg.get("crop_and_resize")) else 0
+        with dg.Feeder(local_rank, cfg, lanes=2, max_batch=min(chunk, 512), max_wait_us=2000, queue_limit=4 * chunk, flags=flags) as feeder:
+            depth = 128  # samples each worker keeps in flight, so that the batches fill
+
+            def worker(k):
+                pending = []
+
+                def fin(t):
+                    r = feeder.wait(t)
+                    assert r.status == 0
+                    px = feeder.peek(t, r)  # the payload where the library's download left it: page-locked host memory
+                    assert px.size == r.nbytes and int(px.flat[0]) + int(px.flat[-1]) >= 0
+                    feeder.release(t)
+
+                for i in range(k, len(items), feeder_threads):
+                    if len(pending) == depth:
+                        fin(pending.pop(0))
+                    pending.append(feeder.submit(items[i]))
+                for t in pending:
+                    fin(t)
+
+            def feeder_pass():
+                ths = [threading.Thread(target=worker, args=(k,)) for k in range(feeder_threads)]
+                for th in ths:
+                    th.start()
+                for th in ths:
+                    th.join()
+
+            feeder_pass()  # warm-up
+            v = timed(feeder_pass)
+            st = feeder.stats()
+        out["e2e_feeder"] = {"value": v, "unit": "images/s", "threads": feeder_threads, "in_flight": feeder_threads * depth,
+                             "mean_batch": round(st["batched_items"] / max(1, st["batches"]), 1),
+                             "note": "per-sample dg_submit / dg_wait / dg_peek from Python worker threads; not the headline e2e"}
+    ctx.close()
+    return out
 
 
 def main():
@@ -164,11 +509,12 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c0", "c1", "c2"])
-    ap.add_argument("--images", type=int, default=0)
+    ap.add_argument("--workload", default="c2", choices=["c0", "c1", "c2", "c3", "c4"])
+    ap.add_argument("--images", type=int, default=0, help="samples in the workload (default: the configuration's own count; c3: 8000)")
     ap.add_argument("--e2e-chunk", type=int, default=1024)
     ap.add_argument("--feeder-threads", type=int, default=16, help="worker threads of the submit / wait measurement (0: skip)")
-    ap.add_argument("--contexts", type=int, default=1, help="library contexts the resident workload is split over")
+    ap.add_argument("--kernels-only", action="store_true", help="resident passes and the per-stage pass only (profiling runs)")
+    ap.add_argument("--no-side-configs", action="store_true", help="skip the shorter C0 and C1 measurements of the default run")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
@@ -176,31 +522,31 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    count = args.images or synth.COUNTS[args.workload]
-    cfg = synth.IMAGE_CONFIGS[args.workload]
-    kind = {"c0": 1, "c1": 2, "c2": 0}[args.workload]
-    config = {"workload": {"c0": f"C0 local-file set: {count} 4:2:0 q90 JPEGs 256..2048, decode + 1024/32 bucket crop-resize",
-                           "c1": f"C1 resize-only: {count} raw RGB buffers 512..4096, 512/16 buckets",
-                           "c2": f"C2 JPEG decode throughput: {count} baseline 4:2:0 JPEGs 512..1536, q75-95, half with restart interval 4, decode to RGB8"}[args.workload],
-              "images_per_gpu": count, "contexts": args.contexts, "sharding": "contiguous rank slices of an N x workload job, no collective",
+    # C3 at its full size is 64 shards; the default here is 8 of them so that generating the shards stays within minutes
+    count = args.images or (8000 if args.workload == "c3" else synth.COUNTS[args.workload])
+    strong = args.workload == "c3"
+    config = {"workload": LABELS[args.workload].format(n=count), "images_per_gpu": count if not strong else f"{count} / N by key hash",
+              "sharding": "key-hash dispatch of one fixed shard set (dg_key_rank), no collective" if strong else
+                          "contiguous rank slices of an N x workload job, no collective",
               "l2": "inputs and intermediates of one pass exceed the 126 MB L2 many times over; no explicit flush"}
 
     # ---------------- reference arm: the CPU path on the host cores ------------------------------------------------
     if args.impl == "reference":
         if rank != 0:
             return
-        items = dataset(args.workload, count, 0, 1, lambda: None)
-        vals = []
-        base = None
+        import datago_b200 as dg
+        keys = dg.Context(dg.DG_DEVICE_NONE, synth.IMAGE_CONFIGS[args.workload]) if args.workload == "c4" else None
+        wl = load_workload(args.workload, count, 0, 1, lambda: None, keys)
+        vals, base = [], None
         for step in range(args.warmup + args.steps):
-            base = cpu_baseline(items, kind, cfg, budget_s=8.0 if step >= args.warmup else 2.0)
+            base = cpu_baseline(wl, budget_s=8.0 if step >= args.warmup else 2.0)
             if step >= args.warmup:
                 vals.append(base["value"])
         v = statistics.mean(vals)
         base["value"] = v
         print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": "images/s", "n_gpus": args.gpus,
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * count / v,
-                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+                          "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "u8",
                           "data": "synthetic", "config": config, "cpu_baseline": base,
                           "e2e": {"value": v, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
@@ -222,303 +568,48 @@ def main():
         if world > 1:
             dist.barrier()
 
-    items = dataset(args.workload, count, rank, world, barrier)
-    quorum = world * count
-    start, end = dg.rank_slice(quorum, rank, world)  # this rank's shard of the N x workload job
-    items = [items[i % count] for i in range(start, end)]
-    stats = workload_stats(items, args.workload)
+    def all_max(x, op="max"):
+        if world == 1:
+            return x
+        t = torch.tensor([float(x)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+        return float(t.item())
 
-    stream = torch.cuda.Stream()
-    ctx = dg.Context(local_rank, cfg, stream=stream.cuda_stream)
     peak, peak_src = load_peaks()
-
-    # -- inputs resident in HBM ---------------------------------------------------------------------------------------
-    # The workload is split over `--contexts` library contexts (contiguous parts, one resident batch and one stream
-    # each), the way the library is driven in production (a feeder lane per context): a step is one pass over every
-    # part, queued back to back, so the parts' passes overlap each other within a step and from one step to the next.
-    # CUDA events on a parent stream bracket all K steps: every context stream waits for the start event, the end
-    # event waits for every context stream.
-    n_ctx = max(1, min(args.contexts, len(items)))
-    part = (len(items) + n_ctx - 1) // n_ctx
-    streams = [stream] + [torch.cuda.Stream() for _ in range(n_ctx - 1)]
-    ctxs = [ctx] + [dg.Context(local_rank, cfg, stream=st.cuda_stream) for st in streams[1:]]
-    batches = []
-    for k in range(n_ctx):
-        b = ctxs[k].batch(items[k * part:(k + 1) * part], None, 0)
-        b.upload()
-        b.sync()
-        batches.append(b)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    time.sleep(1.0)  # nvidia-smi needs a moment before its first sample
-    for _ in range(args.warmup):
-        for b in batches:
-            b.run()
-    for b in batches:
-        b.sync()
-        assert all(b.result(i).status == 0 for i in range(len(b))), "an image failed to decode"
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    parent = torch.cuda.Stream()
-    done = [torch.cuda.Event() for _ in streams]
-    torch.cuda.synchronize()
-    barrier()
-    t_begin = time.time()
-    e0.record(parent)
-    for st in streams:
-        st.wait_event(e0)
-    for _ in range(args.steps):
-        for b in batches:
-            b.run()
-    for st, ev in zip(streams, done):
-        ev.record(st)
-        parent.wait_event(ev)
-    e1.record(parent)
-    torch.cuda.synchronize()
-    barrier()
-    sampler.window(t_begin, time.time())
-    elapsed_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
-    launches = 0
-    for b in batches:
-        b.sync()
-        launches += b.counters()["kernel_launches"] * args.steps
-        b.close()
-    for c in ctxs[1:]:
-        c.close()
-    # Per-kernel durations: one more pass of the same workload with CUDA events around every stage.  A timing batch
-    # keeps all waves on one stream, so each event pair brackets a kernel that ran alone (the timed passes above
-    # overlap the waves on two streams).
-    tb = ctx.batch(items, None, dg.BATCH_TIMING)
-    tb.upload()
-    tb.run()
-    tb.run()
-    tb.sync()
-    stage_ms = tb.stage_ms()  # of the last pass
-    serial_ms = sum(stage_ms.values())
-    tb.close()
-    t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms = float(t.item())
-    value = world * len(items) * args.steps / (elapsed_ms / 1000.0)
-
-    # -- end to end through the batch API: host bytes in, host pixels out ------------------------------------------
-    # Sub-batches alternate between two contexts (two streams), the way a host batcher would drive the library, so
-    # that the device-to-host copy of one sub-batch overlaps the planning, upload and kernels of the next.
-    chunk = max(1, min(args.e2e_chunk, len(items)))
+    traffic = load_traffic()
+    keys = dg.Context(dg.DG_DEVICE_NONE, synth.IMAGE_CONFIGS[args.workload]) if args.workload == "c4" else None
+    wl = load_workload(args.workload, count, rank, world, barrier, keys)
     e2e_steps = max(1, min(args.steps, 5))
-    max_out = 0
-    for c0 in range(0, len(items), chunk):
-        with ctx.batch(items[c0:c0 + chunk], None, 0) as b:
-            max_out = max(max_out, b.packed_bytes())
-    lanes = [(ctx, torch.empty(max_out + 4096, dtype=torch.uint8).pin_memory().numpy()),
-             (dg.Context(local_rank, cfg), torch.empty(max_out + 4096, dtype=torch.uint8).pin_memory().numpy())]
-    h2d = d2h = 0
+    big = args.workload in ("c1", "c4")  # multi-megapixel items: the oracle needs seconds for a few of them
+    rep = measure(wl, local_rank, world, barrier, all_max, args.steps, args.warmup, e2e_steps, args.e2e_chunk,
+                  args.feeder_threads, 16 if big else 64, args.kernels_only, peak, traffic)
+    line = {"metric": METRIC, "value": rep.pop("value"), "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": rep.pop("ms_per_step"), "higher_is_better": True,
+            "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic", "config": config}
+    if rep.get("roofline"):
+        rep["roofline"]["peak_source"] = peak_src
+    line.update(rep)
+    if world == 1 and not args.no_cpu_baseline and not args.kernels_only:
+        line["cpu_baseline"] = cpu_baseline(wl)
+        y = pil_yardstick(wl.items)
+        if y:
+            line["cpu_baseline"]["pillow_libjpeg_turbo_decode"] = y
 
-    def finish(pending):
-        nonlocal h2d, d2h
-        b, outs = pending
-        b.sync()
-        assert all(b.result(i).status == 0 for i in range(0, len(b), 97))
-        c = b.counters()
-        h2d += c["h2d_bytes"]
-        d2h += c["d2h_bytes"]
-        b.close()
-
-    def e2e_pass(to_host=True):
-        nonlocal h2d, d2h
-        h2d = d2h = 0
-        pending = [None, None]
-        for k, c0 in enumerate(range(0, len(items), chunk)):
-            lane_ctx, pin_np = lanes[k % 2]
-            if pending[k % 2] is not None:
-                finish(pending[k % 2])  # the pinned buffer of this lane is free again
-            b = lane_ctx.batch(items[c0:c0 + chunk], None, 0 if to_host else dg.BATCH_COLLATE)
-            b.upload()
-            b.run()
-            if to_host:
-                b.download_packed(pin_np)  # one copy; payload i is pin_np[result(i).packed_offset:][:nbytes]
-            outs = pin_np
-            pending[k % 2] = (b, outs)
-        for pnd in pending:
-            if pnd is not None:
-                finish(pnd)
-
-    e2e_pass()  # warm-up: grows the library's pinned and device block caches
-    torch.cuda.synchronize()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_pass()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    barrier()
-    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * len(items) * e2e_steps / float(t.item())
-    e2e_h2d, e2e_d2h = h2d, d2h
-
-    # Same, with the payloads left in HBM as per-bucket [n, h, w, c] arrays (what a training process on the same GPU
-    # consumes): host bytes in, only the per-image status words come back.
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_pass(to_host=False)
-    torch.cuda.synchronize()
-    dev_s = time.perf_counter() - t0
-    barrier()
-    t = torch.tensor([dev_s], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_device = {"value": world * len(items) * e2e_steps / float(t.item()), "unit": "images/s",
-                  "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                  "note": "payloads stay on the device, collated per bucket; not the headline e2e"}
-
-    # Same host-to-host job through the per-sample front end: worker threads submit single samples and wait for
-    # them, as datago's tokio workers would; the library cuts the batches (two lanes of up to 512 samples).
-    import threading
-    n_workers = args.feeder_threads
-    feeder_value = None
-    if n_workers > 0:
-        flags = dg.BATCH_DECODE_ONLY if not (cfg and cfg.get("crop_and_resize")) else 0
-        with dg.Feeder(local_rank, cfg, lanes=2, max_batch=min(chunk, 512), max_wait_us=2000, queue_limit=4 * chunk, flags=flags) as feeder:
-            # samples each worker keeps in flight: the batches fill to what arrives within max_wait_us, so the workers
-            # have to keep a few hundred samples outstanding between them
-            depth = 128
-
-            def worker(k):
-                # each worker keeps `depth` samples in flight and reads every payload where the library's download
-                # left it (dg_peek: page-locked host memory), touching its first and last byte
-                mine = list(range(k, len(items), n_workers))
-                pending = []
-
-                def finish(t):
-                    r = feeder.wait(t)
-                    assert r.status == 0
-                    px = feeder.peek(t, r)
-                    assert px.size == r.nbytes and int(px.flat[0]) + int(px.flat[-1]) >= 0
-                    feeder.release(t)
-
-                for i in mine:
-                    if len(pending) == depth:
-                        finish(pending.pop(0))
-                    pending.append(feeder.submit(items[i]))
-                for t in pending:
-                    finish(t)
-
-            def feeder_pass():
-                ths = [threading.Thread(target=worker, args=(k,)) for k in range(n_workers)]
-                for th in ths:
-                    th.start()
-                for th in ths:
-                    th.join()
-
-            feeder_pass()  # warm-up
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(e2e_steps):
-                feeder_pass()
-            fs = time.perf_counter() - t0
-            barrier()
-            st = feeder.stats()
-        t = torch.tensor([fs], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        feeder_value = {"value": world * len(items) * e2e_steps / float(t.item()), "unit": "images/s", "threads": n_workers, "in_flight": n_workers * depth,
-                        "mean_batch": round(st["batched_items"] / max(1, st["batches"]), 1),
-                        "note": "per-sample dg_submit / dg_wait / dg_peek from Python worker threads, payloads in the library's page-locked host buffers; not the headline e2e"}
-
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    # -- roofline of the dominant kernel, from the stage events of the last timed pass -----------------------------
-    bytes_of = {
-        "unstuff": 2 * stats["compressed"],
-        "coef_clear": stats["coef_bytes"],
-        "huff_restart": None, "huff_spec": None,  # filled below (split by image class)
-        "idct": stats["coef_bytes"] + stats["plane_bytes"],
-        "color": stats["plane_bytes"] + stats["rgb_bytes"],
-    }
-    rst_items = [it for it in items if isinstance(it, (bytes, bytearray)) and dg.jpeg_probe(it).restart_interval]
-    rst_stats = workload_stats(rst_items, args.workload) if rst_items else dict(compressed=0, coef_bytes=0)
-    bytes_of["huff_restart"] = rst_stats["compressed"] + rst_stats["coef_bytes"]
-    bytes_of["huff_spec"] = (stats["compressed"] - rst_stats["compressed"]) + (stats["coef_bytes"] - rst_stats["coef_bytes"])
-    stages = {}
-    for name, ms in stage_ms.items():
-        if ms < 0.05:  # e.g. the coefficient clear, which only runs on a scratch block's first use
-            continue
-        b = bytes_of.get(name)
-        stages[name] = {"ms": round(ms, 3)}
-        if b:
-            stages[name]["gbs"] = round(b / ms / 1e6, 1)
-            stages[name]["frac"] = round(b / ms / 1e6 / peak, 4)
-    # The roofline object grades the longest HBM-graded stage (IDCT, colour, resize).  Entropy decoding is serial bit
-    # parsing: it is reported in bits per cycle (`huffman`) and, when it is the longest stage, named in `longest_stage`.
-    longest = max(stages, key=lambda k: stages[k]["ms"]) if stages else None
-    graded = [k for k in stages if not k.startswith("huff") and k != "unstuff"]
-    top = max(graded, key=lambda k: stages[k]["ms"]) if graded else longest
-    roofline = None
-    if top:
-        achieved = stages[top].get("gbs")
-        # DRAM bytes per launch: dram__bytes_read + dram__bytes_write of one ncu capture on a 256 / 1024-image case of
-        # this workload (profiles/), expressed per algorithmic byte and scaled to this pass by the units it processes
-        # (traffic grows in proportion to the image count).  The entropy kernels move fewer bytes than the dense
-        # coefficient array they fill: only the sectors that hold non-zero coefficients are written.
-        ncu_bytes_per_algorithmic_byte = {"idct": 1.205, "color": 0.958, "huff_restart": 0.66, "huff_spec": 0.63}
-        ratio = ncu_bytes_per_algorithmic_byte.get(top)
-        roofline = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": round(achieved / peak, 4) if achieved else None,
-                    "traffic": int(ratio * bytes_of[top]) if ratio and bytes_of.get(top) else None, "peak_source": peak_src,
-                    "longest_stage": longest}
-    post_ms = stage_ms.get("idct", 0.0) + stage_ms.get("color", 0.0)
-    roofline_top = top
-    post_bytes = stats["coef_bytes"] + stats["rgb_bytes"]
-    post = {"ms": round(post_ms, 3), "bytes": post_bytes, "gbs": round(post_bytes / post_ms / 1e6, 1) if post_ms else None,
-            "frac": round(post_bytes / post_ms / 1e6 / peak, 4) if post_ms else None}
-    # crop_and_resize: C * P_used + C * tw * th per image, P_used = the source pixels that map into the crop
-    resize = None
-    resize_ms = stage_ms.get("resize_h", 0.0) + stage_ms.get("resize_v", 0.0) + stage_ms.get("resize_shift", 0.0)
-    if cfg and cfg.get("crop_and_resize") and resize_ms > 0:
-        import math
-        rbytes = 0
-        for it in items:
-            if isinstance(it, (bytes, bytearray)):
-                i = dg.jpeg_probe(it)
-                w_, h_, c_ = i.width, i.height, i.channels
-            else:
-                h_, w_ = it.shape[:2]
-                c_ = 1 if it.ndim == 2 else it.shape[2]
-            p = ctx.plan_geometry(w_, h_, c_)
-            scale = max(p.target_w / w_, p.target_h / h_)
-            used = min(w_, math.ceil(p.target_w / scale)) * min(h_, math.ceil(p.target_h / scale))
-            rbytes += c_ * used + c_ * p.target_w * p.target_h
-        resize = {"ms": round(resize_ms, 3), "bytes": rbytes, "gbs": round(rbytes / resize_ms / 1e6, 1),
-                  "frac": round(rbytes / resize_ms / 1e6 / peak, 4)}
-    huff_ms = stage_ms.get("huff_restart", 0.0) + stage_ms.get("huff_spec", 0.0)
-    sm_mhz = clocks.get("sm_mhz") or 1965.0
-    huff = {"ms": round(huff_ms, 3),
-            "bits_per_cycle_per_sm": round(stats["compressed"] * 8 / (huff_ms / 1000.0 * sm_mhz * 1e6 * 148), 4) if huff_ms else None}
-
-    if roofline and roofline_top and roofline_top.startswith("resize") and resize:
-        # the resize passes share one algorithmic figure (source pixels used + payload), reported over their sum
-        roofline.update({"kernel": "resize_h+resize_v+resize_shift", "achieved": resize["gbs"], "frac": resize["frac"]})
-    line = {"metric": METRIC, "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u8", "data": "synthetic", "config": config,
-            "mpix_per_s": value * stats["pixels"] / len(items) / 1e6,
-            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": e2e_h2d, "d2h_bytes_per_step": e2e_d2h,
-                    "steps": e2e_steps, "batch": chunk, "streams": 2},
-            "e2e_device_payloads": e2e_device, "e2e_feeder": feeder_value,
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "stages": stages, "post_entropy": post, "resize": resize,
-            "huffman": huff, "stage_pass": {"ms_serial_sum": round(serial_ms, 3), "note": "stages timed in a one-stream pass over the whole workload; value is timed with the workload split over `contexts` contexts, each overlapping its waves on two streams"}}
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(items, kind, cfg)
-        if args.workload != "c1":
-            line["cpu_baseline"]["pillow_libjpeg_turbo_decode"] = pil_yardstick(items)
-    print(json.dumps(line))
+    # ---------------- the other single-GPU configurations, shorter, in the same process --------------------------------
+    if args.workload == "c2" and not args.images and world == 1 and not args.kernels_only and not args.no_side_configs:
+        configs = {}
+        for name in ("c0", "c1"):
+            side = load_workload(name, synth.COUNTS[name], 0, 1, lambda: None)
+            r = measure(side, local_rank, 1, lambda: None, lambda x, op="max": x, max(3, args.steps // 4), 3, 2, args.e2e_chunk,
+                        0, 8 if name == "c1" else 24, False, peak, traffic)
+            r["workload"] = LABELS[name].format(n=synth.COUNTS[name])
+            if not args.no_cpu_baseline:
+                r["cpu_baseline"] = cpu_baseline(side, budget_s=6.0)
+            configs[name] = r
+            del side
+        line["configs"] = configs
+    if rank == 0:
+        print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 

@@ -56,6 +56,7 @@ def lib():
                                              C.c_uint32, C.c_int, C.c_char_p, C.c_void_p, C.POINTER(Plan), C.c_int]
         _lib.orc_jpeg_info.argtypes = [C.c_char_p, C.c_size_t, C.POINTER(JpegInfo)]
         _lib.orc_jpeg_decode.argtypes = [C.c_char_p, C.c_size_t, C.c_void_p]
+        _lib.orc_jpeg_decode_variant.argtypes = [C.c_char_p, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_int]
         _lib.orc_jpeg_decode_stages.argtypes = [C.c_char_p, C.c_size_t] + [C.c_void_p] * 7
         _lib.orc_jpeg_to_payload.argtypes = [C.c_char_p, C.c_size_t, C.c_uint32, C.c_uint32, C.c_double, C.c_double,
                                              C.c_char_p, C.c_void_p, C.POINTER(Plan), C.c_int]
@@ -173,6 +174,18 @@ def jpeg_decode(data: bytes):
     shape = (info.height, info.width, 3) if info.channels == 3 else (info.height, info.width)
     out = np.empty(shape, np.uint8)
     rc = lib().orc_jpeg_decode(data, len(data), out.ctypes.data)
+    if rc:
+        raise OracleError(rc)
+    return out
+
+
+def jpeg_decode_variant(data: bytes, idct=0, upsample=0, color=0):
+    """Decode with another published IDCT (1: 12-bit stb-style), upsampling (1: two rounded passes, 2: bias 8 in both
+    phases) or colour arithmetic (1: 14-bit constants); (0, 0, 0) is jpeg_decode."""
+    info = jpeg_info(data)
+    shape = (info.height, info.width, 3) if info.channels == 3 else (info.height, info.width)
+    out = np.empty(shape, np.uint8)
+    rc = lib().orc_jpeg_decode_variant(data, len(data), out.ctypes.data, idct, upsample, color)
     if rc:
         raise OracleError(rc)
     return out

@@ -603,6 +603,71 @@ int decode_scan(const Jpeg& j, std::vector<int16_t> coef[3]) {
     return ORC_OK;
 }
 
+// Reconstruction variants.  The default (0, 0, 0) is the libjpeg family, which the test-suite pins bit-exactly against
+// libjpeg-turbo.  zune-jpeg, the decoder datago links, is not available here; the alternatives below are the other
+// published choices for the three steps whose arithmetic differs between baseline decoders, so that the distance
+// between the families can be measured (tests/test_oracle_variants.py prints and bounds it).
+//   idct:     0 = 13-bit "islow" (libjpeg jidctint);  1 = 12-bit constants, rounding 512 >> 10 after the column pass and
+//             65536 + (128 << 17) >> 17 after the row pass (the stb_image factorisation, which zune-jpeg's scalar IDCT
+//             is understood to follow)
+//   upsample: 0 = one rounding per sample, (3 * (3 near + far) + (3 near' + far') + 8 or 7) >> 4 (libjpeg "fancy" h2v2);
+//             1 = two passes with an 8-bit intermediate, (3 near + far + 2) >> 2 vertically, then the same horizontally;
+//             2 = one rounding with the bias 8 in both phases (stb_image)
+//   colour:   0 = 16-bit constants 91881 / 22554 / 46802 / 116130, rounding 32768 per chroma term (libjpeg);
+//             1 = 14-bit constants 22970 / 5638 / 11700 / 29032 on Y * 16384 with one rounding of 8192
+struct Variant { int idct = 0, upsample = 0, color = 0; };
+thread_local Variant g_variant;
+
+// 12-bit IDCT of the stb_image family: dequantise, columns (round 512, shift 10), rows (round 65536 + (128 << 17), shift 17).
+void idct_stb12(const int16_t* in, const uint16_t* q, uint8_t* out, int stride) {
+    auto f2f = [](double x) { return (int32_t)(x * 4096.0 + 0.5); };
+    int32_t val[64];
+    auto kernel = [&](int32_t s0, int32_t s1, int32_t s2, int32_t s3, int32_t s4, int32_t s5, int32_t s6, int32_t s7,
+                      int32_t& x0, int32_t& x1, int32_t& x2, int32_t& x3, int32_t& t0, int32_t& t1, int32_t& t2, int32_t& t3) {
+        int32_t p2 = s2, p3 = s6;
+        int32_t p1 = (p2 + p3) * f2f(0.5411961);
+        t2 = p1 + p3 * f2f(-1.847759065);
+        t3 = p1 + p2 * f2f(0.765366865);
+        p2 = s0; p3 = s4;
+        t0 = (p2 + p3) * 4096;
+        t1 = (p2 - p3) * 4096;
+        x0 = t0 + t3; x3 = t0 - t3; x1 = t1 + t2; x2 = t1 - t2;
+        t0 = s7; t1 = s5; t2 = s3; t3 = s1;
+        p3 = t0 + t2;
+        int32_t p4 = t1 + t3;
+        p1 = t0 + t3; p2 = t1 + t2;
+        int32_t p5 = (p3 + p4) * f2f(1.175875602);
+        t0 = t0 * f2f(0.298631336); t1 = t1 * f2f(2.053119869); t2 = t2 * f2f(3.072711026); t3 = t3 * f2f(1.501321110);
+        p1 = p5 + p1 * f2f(-0.899976223); p2 = p5 + p2 * f2f(-2.562915447);
+        p3 = p3 * f2f(-1.961570560); p4 = p4 * f2f(-0.390180644);
+        t3 += p1 + p4; t2 += p2 + p3; t1 += p2 + p4; t0 += p1 + p3;
+    };
+    for (int i = 0; i < 8; ++i) {
+        int32_t s[8];
+        for (int r = 0; r < 8; ++r) s[r] = (int32_t)in[r * 8 + i] * (int32_t)q[r * 8 + i];
+        int32_t x0, x1, x2, x3, t0, t1, t2, t3;
+        kernel(s[0], s[1], s[2], s[3], s[4], s[5], s[6], s[7], x0, x1, x2, x3, t0, t1, t2, t3);
+        x0 += 512; x1 += 512; x2 += 512; x3 += 512;
+        val[i] = (x0 + t3) >> 10; val[56 + i] = (x0 - t3) >> 10;
+        val[8 + i] = (x1 + t2) >> 10; val[48 + i] = (x1 - t2) >> 10;
+        val[16 + i] = (x2 + t1) >> 10; val[40 + i] = (x2 - t1) >> 10;
+        val[24 + i] = (x3 + t0) >> 10; val[32 + i] = (x3 - t0) >> 10;
+    }
+    for (int i = 0; i < 8; ++i) {
+        const int32_t* v = val + i * 8;
+        int32_t x0, x1, x2, x3, t0, t1, t2, t3;
+        kernel(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], x0, x1, x2, x3, t0, t1, t2, t3);
+        const int32_t rnd = 65536 + (128 << 17);
+        x0 += rnd; x1 += rnd; x2 += rnd; x3 += rnd;
+        auto c8 = [](int32_t x) { return (uint8_t)(x < 0 ? 0 : x > 255 ? 255 : x); };
+        uint8_t* o = out + i * stride;
+        o[0] = c8((x0 + t3) >> 17); o[7] = c8((x0 - t3) >> 17);
+        o[1] = c8((x1 + t2) >> 17); o[6] = c8((x1 - t2) >> 17);
+        o[2] = c8((x2 + t1) >> 17); o[5] = c8((x2 - t1) >> 17);
+        o[3] = c8((x3 + t0) >> 17); o[4] = c8((x3 - t0) >> 17);
+    }
+}
+
 // 13-bit "islow" integer IDCT with dequantisation, +128 and clamp.
 void idct_islow(const int16_t* in, const uint16_t* q, uint8_t* out, int stride) {
     const int CB = 13, P1 = 2;
@@ -661,7 +726,7 @@ int decode_to_planes(const uint8_t* d, size_t n, Decoded& o) {
         o.plane[c].assign((size_t)pitch * cp.bh * 8, 0);
         for (int by = 0; by < cp.bh; ++by)
             for (int bx = 0; bx < cp.bw; ++bx)
-                idct_islow(&o.coef[c][((size_t)by * cp.bw + bx) * 64], o.j.qt[cp.tq], &o.plane[c][(size_t)by * 8 * pitch + bx * 8], pitch);
+                (g_variant.idct == 1 ? idct_stb12 : idct_islow)(&o.coef[c][((size_t)by * cp.bw + bx) * 64], o.j.qt[cp.tq], &o.plane[c][(size_t)by * 8 * pitch + bx * 8], pitch);
     }
     return ORC_OK;
 }
@@ -677,9 +742,22 @@ struct Upsampler {
         if (far > dh - 1) far = dh - 1;
         return 3 * p[(size_t)cy * pitch + cx] + p[(size_t)far * pitch + cx];
     }
+    // two-pass variant: the vertical step rounds to 8 bits on its own
+    int vround(int cx, int y) const { return v == 1 ? p[(size_t)y * pitch + cx] : (colsum(cx, y) + 2) >> 2; }
     int at(int x, int y) const {
         if (h == 1 && v == 1) return p[(size_t)y * pitch + x];
         if (h == 2 && dw <= 2) return p[(size_t)(y / v) * pitch + (x >> 1)];  // libjpeg replicates when the plane is <= 2 wide
+        if (g_variant.upsample == 1) {
+            if (h == 1) return vround(x, y);
+            const int cx = x >> 1, t = vround(cx, y);
+            const int nb = (x & 1) ? std::min(cx + 1, dw - 1) : std::max(cx - 1, 0);
+            return (3 * t + vround(nb, y) + 2) >> 2;
+        }
+        if (g_variant.upsample == 2 && h == 2 && v == 2) {
+            const int cx = x >> 1, t = colsum(cx, y);
+            const int nb = (x & 1) ? std::min(cx + 1, dw - 1) : std::max(cx - 1, 0);
+            return (3 * t + colsum(nb, y) + 8) >> 4;
+        }
         if (h == 1) return (colsum(x, y) + ((y & 1) ? 2 : 1)) >> 2;  // h1v2: bias 1 on the upper row, 2 on the lower
         int cx = x >> 1;
         if (v == 1) {  // h2v1
@@ -718,6 +796,11 @@ int decode_rgb(const uint8_t* d, size_t n, uint8_t* out, Decoded& o) {
             int r = Y + ((91881 * cr + 32768) >> 16);
             int g = Y + ((-22554 * cb - 46802 * cr + 32768) >> 16);
             int b = Y + ((116130 * cb + 32768) >> 16);
+            if (g_variant.color == 1) {  // 14-bit constants, one rounding
+                r = (Y * 16384 + 22970 * cr + 8192) >> 14;
+                g = (Y * 16384 - 5638 * cb - 11700 * cr + 8192) >> 14;
+                b = (Y * 16384 + 29032 * cb + 8192) >> 14;
+            }
             uint8_t* px = out + ((size_t)y * W + x) * 3;
             px[0] = clamp8(r); px[1] = clamp8(g); px[2] = clamp8(b);
         }
@@ -748,6 +831,16 @@ ORC_API int orc_jpeg_info(const uint8_t* d, size_t n, orc_jpeg_info_t* info) {
 ORC_API int orc_jpeg_decode(const uint8_t* d, size_t n, uint8_t* out) {
     Decoded o;
     return decode_rgb(d, n, out, o);
+}
+
+// Decode with another published choice for the IDCT, the chroma upsampling and the colour constants (see Variant); used
+// only to measure how far the decoder families lie apart.
+ORC_API int orc_jpeg_decode_variant(const uint8_t* d, size_t n, uint8_t* out, int idct, int upsample, int color) {
+    g_variant = Variant{idct, upsample, color};
+    Decoded o;
+    const int rc = decode_rgb(d, n, out, o);
+    g_variant = Variant{};
+    return rc;
 }
 
 // Stage outputs for kernel-by-kernel parity: coefficients in scan order per component (blocks raster order within
