@@ -57,9 +57,30 @@ class ImagePayload:
         return np.frombuffer(self.data, np.uint8).reshape(self._shape())
 
     def to_pil_image(self):
-        """src/structs.rs:103-151"""
+        """src/structs.rs:103-151: mode L for one channel, RGBA for four, RGB otherwise."""
         from PIL import Image
-        return Image.fromarray(self.to_numpy_array())
+        a = self.to_numpy_array()
+        if self.channels == 1:
+            return Image.fromarray(a.reshape(self.height, self.width)).convert("L")
+        if self.channels == 4:
+            return Image.fromarray(a).convert("RGBA")
+        return Image.fromarray(a)
+
+    # PythonImagePayload (src/structs.rs:191-224): calling the payload gives the PIL image, get_payload() a copy of the
+    # plain record, and any other attribute is looked up on the PIL image, so a payload can be used where a PIL image
+    # is expected (payload.size, payload.resize(...), payload.mode ...).
+    def __call__(self):
+        return self.to_pil_image()
+
+    def get_payload(self):
+        return ImagePayload(bytes(self.data), self.original_height, self.original_width, self.height, self.width,
+                            self.channels, self.bit_depth, self.is_encoded, self._device_ptr, self._keepalive)
+
+    def __getattr__(self, attr):
+        # only reached for names the payload itself does not have
+        if attr.startswith("_"):
+            raise AttributeError(attr)
+        return getattr(self.to_pil_image(), attr)
 
     @property
     def __cuda_array_interface__(self):
@@ -93,6 +114,37 @@ class Sample:
     @property
     def attributes(self):
         return json.dumps(self._attributes)
+
+
+def sample_to_python_types(sample):
+    """src/structs.rs:279-351: the sample as a dict of plain Python types with PIL images; attribute values that are
+    not strings arrive JSON-encoded."""
+    return {
+        "id": sample.id, "source": sample.source, "duplicate_state": sample.duplicate_state,
+        "attributes": {k: (v if isinstance(v, str) else json.dumps(v)) for k, v in sample._attributes.items()},
+        "tags": list(sample.tags), "coca_embedding": list(sample.coca_embedding),
+        "latents": {k: {"data": bytes(v.data), "len": v.len} for k, v in sample.latents.items()},
+        "image": sample.image.to_pil_image(),
+        "masks": {k: m.to_pil_image() for k, m in sample.masks.items()},
+        "additional_images": {k: m.to_pil_image() for k, m in sample.additional_images.items()},
+    }
+
+
+_logging_initialised = False
+
+
+def initialize_logging(log_level=None):
+    """src/client.rs:253-263: set up the logger once; False when it had been set up before.  The level comes from
+    `log_level`, else from RUST_LOG (the variable the reference's env_logger reads), else "error"."""
+    global _logging_initialised
+    if _logging_initialised:
+        return False
+    level = (os.environ.get("RUST_LOG") or log_level or "error").split(",")[0].strip().upper()
+    level = {"WARN": "WARNING", "TRACE": "DEBUG", "OFF": "CRITICAL"}.get(level, level)
+    logging.basicConfig(level=getattr(logging, level, logging.ERROR), format="[%(asctime)s %(levelname)s %(name)s] %(message)s")
+    log.setLevel(getattr(logging, level, logging.ERROR))
+    _logging_initialised = True
+    return True
 
 
 # ---- generators ---------------------------------------------------------------------------------------------------------
@@ -230,6 +282,11 @@ class DatagoClient:
         if s is None:
             self.stop()
         return s
+
+    def get_sample_auto_convert(self):
+        """src/client.rs:207-215: the next sample as a dict of Python types with PIL images, or None."""
+        s = self.get_sample()
+        return None if s is None else sample_to_python_types(s)
 
     def stop(self):
         self._stop.set()

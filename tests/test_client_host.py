@@ -6,6 +6,7 @@ import json
 import os
 import tarfile
 
+import numpy as np
 import pytest
 
 import oracle
@@ -74,3 +75,39 @@ def test_tar_key_hash_sharding_is_disjoint_and_covers(tmp_path):
         assert all(oracle.key_hash(k) % 4 == rank for k in mine)
         seen += mine
     assert sorted(seen) == keys
+
+
+def test_image_payload_behaves_like_the_reference_python_payload():
+    # src/structs.rs:191-224: __call__ -> PIL image, get_payload -> the plain record, other attributes -> the PIL image
+    from datago_b200.client import ImagePayload
+    a = np.arange(5 * 7 * 3, dtype=np.uint8).reshape(5, 7, 3)
+    p = ImagePayload(a.tobytes(), 50, 70, 5, 7, 3, 8, False)
+    assert p().size == (7, 5) and p().mode == "RGB"
+    assert p.size == (7, 5) and p.mode == "RGB"          # delegated to the PIL image
+    assert p.resize((3, 2)).size == (3, 2)
+    q = p.get_payload()
+    assert q is not p and q.data == p.data and (q.height, q.width, q.channels, q.original_width) == (5, 7, 3, 70)
+    assert np.array_equal(p.to_numpy_array(), a)
+    g = ImagePayload(a[:, :, 0].tobytes(), 5, 7, 5, 7, 1, 8, False)
+    assert g().mode == "L" and g.to_numpy_array().shape == (5, 7)
+    rgba = ImagePayload(np.zeros((2, 2, 4), np.uint8).tobytes(), 2, 2, 2, 2, 4, 8, False)
+    assert rgba().mode == "RGBA"
+    with pytest.raises(AttributeError):
+        p.__cuda_array_interface__
+    with pytest.raises(AttributeError):
+        p.no_such_attribute_anywhere
+
+
+def test_sample_auto_convert_and_logging():
+    # src/structs.rs:279-351, src/client.rs:253-263
+    from datago_b200 import client
+    a = np.full((4, 6, 3), 9, np.uint8)
+    s = client.Sample("k1", "src", client.ImagePayload(a.tobytes(), 4, 6, 4, 6, 3, 8, False), {"json": "{\"a\": 1}", "n": 3})
+    s.additional_images["k1.mask"] = client.ImagePayload(a[:, :, 0].tobytes(), 4, 6, 4, 6, 1, 8, False)
+    d = client.sample_to_python_types(s)
+    assert d["id"] == "k1" and d["source"] == "src" and d["duplicate_state"] == 0
+    assert d["attributes"] == {"json": "{\"a\": 1}", "n": "3"}
+    assert d["image"].size == (6, 4) and d["additional_images"]["k1.mask"].mode == "L"
+    assert d["masks"] == {} and d["latents"] == {} and d["tags"] == [] and d["coca_embedding"] == []
+    first = client.initialize_logging("warn")
+    assert client.initialize_logging() is False or first is False   # a second call reports that logging was set up already
