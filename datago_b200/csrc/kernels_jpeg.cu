@@ -459,6 +459,16 @@ __device__ __forceinline__ void idct8_lo4(int32_t x0, int32_t x1, int32_t x2, in
     o[2] = (t12 + o1) >> SHIFT; o[5] = (t12 - o1) >> SHIFT; o[3] = (t13 + o0) >> SHIFT; o[4] = (t13 - o0) >> SHIFT;
 }
 
+// ... and with x2 = x3 = 0 as well.
+template <int32_t RND, int SHIFT>
+__device__ __forceinline__ void idct8_lo2(int32_t x0, int32_t x1, int32_t (&o)[8]) {
+    const int32_t t0 = x0 * 8192 + RND;
+    const int32_t o0 = x1 * (F_1_175 - F_0_899), o1 = x1 * (F_1_175 - F_0_390), o2 = x1 * F_1_175,
+                  o3 = x1 * (F_1_501 - F_0_899 - F_0_390 + F_1_175);
+    o[0] = (t0 + o3) >> SHIFT; o[7] = (t0 - o3) >> SHIFT; o[1] = (t0 + o2) >> SHIFT; o[6] = (t0 - o2) >> SHIFT;
+    o[2] = (t0 + o1) >> SHIFT; o[5] = (t0 - o1) >> SHIFT; o[3] = (t0 + o0) >> SHIFT; o[4] = (t0 - o0) >> SHIFT;
+}
+
 // packs sat_u8 of four ints into one word, first argument in the lowest byte
 __device__ __forceinline__ uint32_t pack_sat_u8(int32_t a, int32_t b, int32_t c, int32_t d) {
     uint32_t hi, r;
@@ -476,19 +486,24 @@ __device__ __forceinline__ void dequant_pair(uint32_t cw, uint32_t qw, int32_t& 
 constexpr int32_t kRound1 = 1 << 10, kRound2 = (1 << 17) + (128 << 18);
 constexpr int kIdctThreads = 128;
 
-// Dequantise + inverse DCT of the calling lane's block; c = its eight coefficient rows, qq = the quantiser rows in the
-// dp2a layout.  emit(r, lo, hi) receives row r of the result as two words of four saturated samples.  The short cuts
-// are taken per warp (all 32 blocks 4x4-sparse / DC only), so every lane of a warp must call this.
-template <class Emit>
-__device__ __forceinline__ void idct_block(const uint4 (&c)[8], const uint4* __restrict__ qq, Emit&& emit) {
+// How much of a block is non-zero decides how much of the butterfly is needed.
+enum : int { kClsFull = 0, kCls4x4 = 1, kCls2x2 = 2, kClsDc = 3 };
+__device__ __forceinline__ int block_class(const uint4 (&c)[8]) {
     const uint32_t hi_rows = c[4].x | c[4].y | c[4].z | c[4].w | c[5].x | c[5].y | c[5].z | c[5].w | c[6].x | c[6].y |
                              c[6].z | c[6].w | c[7].x | c[7].y | c[7].z | c[7].w;
     const uint32_t hi_cols = c[0].z | c[0].w | c[1].z | c[1].w | c[2].z | c[2].w | c[3].z | c[3].w;
-    const bool sparse = __all_sync(0xFFFFFFFFu, (hi_rows | hi_cols) == 0);
-    const uint32_t ac = (c[0].x >> 16) | c[0].y | c[1].x | c[1].y | c[2].x | c[2].y | c[3].x | c[3].y;
-    const bool dc_only = sparse && __all_sync(0xFFFFFFFFu, ac == 0);
-    if (dc_only) {
-        // flat blocks (a quarter of the warps on smooth content): both passes reduce to shifts of the DC term
+    if (hi_rows | hi_cols) return kClsFull;
+    if (c[0].y | c[1].y | c[2].x | c[2].y | c[3].x | c[3].y) return kCls4x4;
+    return ((c[0].x >> 16) | c[1].x) ? kCls2x2 : kClsDc;
+}
+
+// Dequantise + inverse DCT of the calling lane's block; c = its coefficient rows (only the part class `cls` covers is
+// read), qq = the quantiser rows in the dp2a layout.  emit(r, lo, hi) receives row r of the result as two words of
+// four saturated samples.  cls must be the same for all lanes of the warp and no sparser than any lane's block.
+template <class Emit>
+__device__ __forceinline__ void idct_block(const uint4 (&c)[8], const uint4* __restrict__ qq, int cls, Emit&& emit) {
+    if (cls == kClsDc) {
+        // flat blocks: both passes reduce to shifts of the DC term
         int32_t lo, hi;
         dequant_pair(c[0].x, __ldg(reinterpret_cast<const uint32_t*>(qq)), lo, hi);
         const int32_t wsv = (lo * 8192 + kRound1) >> 11;
@@ -496,11 +511,28 @@ __device__ __forceinline__ void idct_block(const uint4 (&c)[8], const uint4* __r
         const uint32_t px4 = pack_sat_u8(v, v, v, v);
 #pragma unroll
         for (int r = 0; r < 8; ++r) emit(r, px4, px4);
-    } else if (sparse) {
+    } else if (cls == kCls2x2) {
+        int32_t x[2][2], ws[8][2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) dequant_pair(c[r].x, __ldg(reinterpret_cast<const uint32_t*>(qq + r)), x[r][0], x[r][1]);
+#pragma unroll
+        for (int col = 0; col < 2; ++col) {
+            int32_t o[8];
+            idct8_lo2<kRound1, 11>(x[0][col], x[1][col], o);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) ws[r][col] = o[r];
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            int32_t o[8];
+            idct8_lo2<kRound2, 18>(ws[r][0], ws[r][1], o);
+            emit(r, pack_sat_u8(o[0], o[1], o[2], o[3]), pack_sat_u8(o[4], o[5], o[6], o[7]));
+        }
+    } else if (cls == kCls4x4) {
         int32_t x[4][4], ws[8][4];
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const uint4 qv = __ldg(qq + r);
+            const uint2 qv = __ldg(reinterpret_cast<const uint2*>(qq + r));
             dequant_pair(c[r].x, qv.x, x[r][0], x[r][1]);
             dequant_pair(c[r].y, qv.y, x[r][2], x[r][3]);
         }
@@ -543,6 +575,8 @@ __device__ __forceinline__ void idct_block(const uint4 (&c)[8], const uint4* __r
     }
 }
 
+// the class a whole warp can run: the least sparse of its lanes' classes
+__device__ __forceinline__ int warp_class(int cls) { return (int)__reduce_min_sync(0xFFFFFFFFu, (unsigned)cls); }
 
 #ifndef DG_IDCT_MIN_CTAS
 #define DG_IDCT_MIN_CTAS 7
@@ -603,7 +637,7 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct(JpegWav
     const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[comp] * 32);
     uint8_t* dst = w.planes + d.plane_off[comp] + (size_t)(by * 8) * d.plane_pitch[comp] + bx * 8;
     const uint32_t pitch = d.plane_pitch[comp];
-    idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+    idct_block(c, qq, warp_class(block_class(c)), [&](int r, uint32_t lo, uint32_t hi) {
         if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(lo, hi);
     });
 }
@@ -654,8 +688,13 @@ __device__ __forceinline__ void store_rgb8(uint8_t* o, const uint32_t (&px)[6], 
     if (npx == 8 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) {
         uint2* o2 = reinterpret_cast<uint2*>(o);
         __stcs(o2, make_uint2(px[0], px[1])); __stcs(o2 + 1, make_uint2(px[2], px[3])); __stcs(o2 + 2, make_uint2(px[4], px[5]));
-    } else {
-        for (int i = 0; i < npx * 3; ++i) o[i] = (uint8_t)(px[i >> 2] >> (8 * (i & 3)));
+    } else {  // ragged right edge or an odd row start: byte by byte, the word index resolved at compile time
+        const int nb = npx * 3;
+#pragma unroll
+        for (int wi = 0; wi < 6; ++wi)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (wi * 4 + k < nb) o[wi * 4 + k] = (uint8_t)(px[wi] >> (8 * k));
     }
 }
 
@@ -692,9 +731,9 @@ constexpr int kCTileRows = 8 * (int)kColorMcuRows + 2;  // chroma rows of a 4:2:
 // - cx0 + 4.  Coordinates are clamped to the real plane extent (dw x dh samples) and the first / last real column is
 // replicated into the halo position, which is what the edge rules of the triangle filter amount to.
 // Warp q loads tile rows q, q + 8, ... of both components; a lane loads word `lane` and, for two lanes, word 32 + lane.
-// Every thread of the CTA (256) must call this; the tile is complete when it returns.
-__device__ __forceinline__ void load_chroma_tile(uint8_t (&s_c)[2][kCTileRows][kCTileCols], const JpegWave& w, const JpegDesc& d,
-                                                 int tx, int ty, int dw, int dh) {
+// Two steps, both by every thread of the CTA (256), with a __syncthreads() after each: chroma_tile_fetch, chroma_tile_edges.
+__device__ __forceinline__ void chroma_tile_fetch(uint8_t (&s_c)[2][kCTileRows][kCTileCols], const JpegWave& w, const JpegDesc& d,
+                                                  int tx, int ty, int dh) {
     const int lane = threadIdx.x & 31, rowi = threadIdx.x >> 5;
     const int cx0 = tx * (int)(kColorTileW / 2), cy0 = ty * 8 * (int)kColorMcuRows;
     constexpr int kWords = kCTileCols / 4;  // 34
@@ -721,13 +760,23 @@ __device__ __forceinline__ void load_chroma_tile(uint8_t (&s_c)[2][kCTileRows][k
             }
         }
     }
-    __syncthreads();
+}
+
+__device__ __forceinline__ void chroma_tile_edges(uint8_t (&s_c)[2][kCTileRows][kCTileCols], int tx, int dw) {
+    const int cx0 = tx * (int)(kColorTileW / 2);
     if (threadIdx.x < 2 * kCTileRows) {
         const int comp = threadIdx.x / kCTileRows, r = threadIdx.x - comp * kCTileRows;
         if (cx0 == 0) s_c[comp][r][3] = s_c[comp][r][4];
         const int last = dw - 1 - cx0;  // tile-local index of the last real column
         if (last >= 0 && last < (int)(kColorTileW / 2)) s_c[comp][r][4 + last + 1] = s_c[comp][r][4 + last];
     }
+}
+
+__device__ __forceinline__ void load_chroma_tile(uint8_t (&s_c)[2][kCTileRows][kCTileCols], const JpegWave& w, const JpegDesc& d,
+                                                 int tx, int ty, int dw, int dh) {
+    chroma_tile_fetch(s_c, w, d, tx, ty, dh);
+    __syncthreads();
+    chroma_tile_edges(s_c, tx, dw);
     __syncthreads();
 }
 
@@ -926,7 +975,7 @@ __global__ void __launch_bounds__(kIdctThreads, DG_IDCT_MIN_CTAS) k_idct_chroma(
             if ((m >> (lane & 7)) & 1u) reinterpret_cast<uint4*>(w.coef + (size_t)gb * 64)[lane & 7] = make_uint4(0, 0, 0, 0);
         }
     }
-    idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+    idct_block(c, qq, warp_class(block_class(c)), [&](int r, uint32_t lo, uint32_t hi) {
         if (valid) *reinterpret_cast<uint2*>(dst + (size_t)r * pitch) = make_uint2(lo, hi);
     });
 }
@@ -953,6 +1002,8 @@ struct FusedSmem {
 __global__ void __launch_bounds__(kFusedThreads, DG_FUSED_MIN_CTAS) k_luma_color(JpegWave w, uint32_t first_tile, bool rezero) {
     __shared__ __align__(16) FusedSmem sm;
     __shared__ uint32_t s_img;
+    __shared__ uint32_t s_count[kFusedThreads / 32];
+    __shared__ uint8_t s_perm[kFusedThreads], s_pcls[kFusedThreads];
     if (threadIdx.x == 0) s_img = owner_of(w.fused_tiles, first_tile + blockIdx.x);
     __syncthreads();
     const uint32_t o = s_img;
@@ -982,34 +1033,82 @@ __global__ void __launch_bounds__(kFusedThreads, DG_FUSED_MIN_CTAS) k_luma_color
 
     // ---- chroma tile from the planes (written by k_idct_chroma), while the copies are in flight
     const int dw = (W + 1) / 2, dh = (H + 1) / 2;
-    load_chroma_tile(sm.c, w, d, (int)tx, (int)ty, dw, dh);
+    chroma_tile_fetch(sm.c, w, d, (int)tx, (int)ty, dh);
 
-    // ---- luma IDCT: one block per thread
-    const uint32_t mcu_local = lane >> 2, k = lane & 3u;
+    // ---- luma IDCT, one block per thread.  How much of the butterfly a block needs depends on where its non-zero
+    //      coefficients end, and a warp runs the path its least sparse lane needs; so the tile's 256 blocks are first
+    //      sorted by class (counting sort, classes of the lanes' own blocks) and thread t then reconstructs the t-th
+    //      block of that order: all but at most three warps of the CTA are uniform.
+    const uint32_t mcu_local = lane >> 2;
     const bool valid = my < d.mcuy && mx0 + mcu_local < d.mcux;
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
-    uint4 c[8];
+    int cls;
+    uint32_t ballot_mine;
+    {
+        uint4 c[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) c[r] = sm.coef[warp][lane * 8 + (r ^ (lane & 7))];
-    if (rezero) {
-        uint32_t rowmask = 0;
+        for (int r = 0; r < 8; ++r) c[r] = sm.coef[warp][lane * 8 + (r ^ (lane & 7))];
+        cls = block_class(c);
+        if (rezero) {
+            uint32_t rowmask = 0;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
-        if (!valid) rowmask = 0;  // a stand-in MCU belongs to other lanes (or another CTA, which may not have read it yet)
+            for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
+            if (!valid) rowmask = 0;  // a stand-in MCU belongs to other lanes (or another CTA, which may not have read it yet)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
-            if ((m >> (lane & 7)) & 1u)
-                reinterpret_cast<uint4*>(const_cast<int16_t*>(row_base) + (size_t)(mx0 + i) * 384)[lane] = make_uint4(0, 0, 0, 0);
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
+                if ((m >> (lane & 7)) & 1u)
+                    reinterpret_cast<uint4*>(const_cast<int16_t*>(row_base) + (size_t)(mx0 + i) * 384)[lane] = make_uint4(0, 0, 0, 0);
+            }
         }
     }
-    __syncthreads();  // every warp has its coefficients in registers: the staging area becomes the luma tile
+    {
+        const uint32_t b0 = __ballot_sync(0xFFFFFFFFu, cls == 0), b1 = __ballot_sync(0xFFFFFFFFu, cls == 1),
+                       b2 = __ballot_sync(0xFFFFFFFFu, cls == 2);
+        if (lane == 0) s_count[warp] = (uint32_t)__popc(b0) | ((uint32_t)__popc(b1) << 10) | ((uint32_t)__popc(b2) << 20);
+        ballot_mine = cls == 0 ? b0 : cls == 1 ? b1 : cls == 2 ? b2 : ~(b0 | b1 | b2);
+    }
+    __syncthreads();  // class counts and the chroma tile are in shared memory
+    {
+        // per-class counts in 10-bit fields (a sum is at most 256; the fourth class is the rest): before this warp, in total
+        uint32_t before = 0, total = 0;
+#pragma unroll
+        for (int i = 0; i < kFusedThreads / 32; ++i) { const uint32_t v = s_count[i]; if (i < (int)warp) before += v; total += v; }
+        const uint32_t t0 = total & 1023u, t1 = (total >> 10) & 1023u, t2 = total >> 20;
+        const uint32_t p0 = before & 1023u, p1 = (before >> 10) & 1023u, p2 = before >> 20;
+        uint32_t pos = cls == 0 ? p0 : cls == 1 ? t0 + p1 : cls == 2 ? t0 + t1 + p2 : t0 + t1 + t2 + (warp * 32u - p0 - p1 - p2);
+        pos += __popc(ballot_mine & ((1u << lane) - 1u));
+        s_perm[pos & 255u] = (uint8_t)threadIdx.x;
+        s_pcls[pos & 255u] = (uint8_t)cls;
+    }
+    chroma_tile_edges(sm.c, (int)tx, dw);
+    __syncthreads();
+    const uint32_t blk = s_perm[threadIdx.x];
+    const int wcls = warp_class((int)s_pcls[threadIdx.x]);
+    uint4 c[8];
+    {
+        const uint32_t bw = blk >> 5, bl = blk & 31u;
+        const uint4* rows = &sm.coef[bw][bl * 8];
+        if (wcls == kClsFull) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) c[r] = rows[r ^ (bl & 7)];
+        } else if (wcls == kCls4x4) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) { const uint2 v = *reinterpret_cast<const uint2*>(&rows[r ^ (bl & 7)]); c[r].x = v.x; c[r].y = v.y; }
+        } else {
+            c[0].x = rows[0 ^ (bl & 7)].x;
+            c[1].x = rows[1 ^ (bl & 7)].x;
+        }
+    }
+    __syncthreads();  // every thread has its coefficients in registers: the staging area becomes the luma tile
     {
         const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[0] * 32);
-        const uint32_t bx = half * 16 + mcu_local * 2 + (k & 1u), by = mrow * 2 + (k >> 1);
+        // position of block blk in the tile, from the lane / warp that staged it
+        const uint32_t bw = blk >> 5, bl = blk & 31u;
+        const uint32_t bx = (bw & 1u) * 16 + (bl >> 2) * 2 + (bl & 1u), by = (bw >> 1) * 2 + ((bl >> 1) & 1u);
         uint8_t* dst = &sm.luma[by * 8][bx * 8];
-        idct_block(c, qq, [&](int r, uint32_t lo, uint32_t hi) {
+        idct_block(c, qq, wcls, [&](int r, uint32_t lo, uint32_t hi) {
             *reinterpret_cast<uint2*>(dst + r * kLumaPitch) = make_uint2(lo, hi);
         });
     }
