@@ -313,6 +313,7 @@ class Batch:
 
     def __init__(self, ctx, inputs, forced_keys=None, flags=0, to_rgb8=None):
         self.ctx = ctx
+        self._flags = flags
         self._n = len(inputs)
         self._items = (Item * max(1, self._n))()
         as_bytes = (_ItemBytes * max(1, self._n)).from_buffer(self._items)
@@ -448,12 +449,16 @@ class Batch:
         return raw.view(np.int16).reshape(int(nb.value), 64)
 
     def debug_decoded(self, i):
+        """The full-size decoded image of JPEG item i (single-wave batches, after sync).  When a resize reads it, its
+        rows are padded to 16 bytes in device memory; the padding is dropped here."""
         r = self.result(i)
         dec = C.c_void_p()
         _check(lib().dg_batch_debug(self._h, i, None, None, C.byref(dec)))
-        n = r.original_width * r.original_height * r.channels
-        raw = self.ctx.copy_to_host(dec.value, n)
-        return raw.reshape((r.original_height, r.original_width, 3) if r.channels == 3 else (r.original_height, r.original_width))
+        h, w, c = r.original_height, r.original_width, r.channels
+        resized = self.ctx.image_config is not None and not (self._flags & BATCH_DECODE_ONLY) and not r.plan.identity
+        pitch = (w * c + 15) // 16 * 16 if resized else w * c
+        raw = self.ctx.copy_to_host(dec.value, pitch * h).reshape(h, pitch)[:, :w * c]
+        return np.ascontiguousarray(raw).reshape((h, w, 3) if c == 3 else (h, w))
 
 
 class Feeder:

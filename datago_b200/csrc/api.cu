@@ -135,6 +135,9 @@ struct dg_ctx {
     // Three-component 4:2:0 images take the fused path (luma never leaves the SM); DATAGO_B200_FUSED=0 sends them through
     // the general IDCT and colour kernels instead (for measurements and for testing that path on the common sampling).
     bool fused_path = true;
+    // Horizontal resize passes run on the tensor cores where their geometry fits; DATAGO_B200_HMMA=0 keeps them on the
+    // dp2a kernel (measurements, and the test-suite's coverage of that kernel).
+    bool hmma = true;
     // Largest decoded image accepted (width * height * channels bytes); the `image` crate's default allocation limit is 512 MiB.
     uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
@@ -180,6 +183,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
     if (const char* mb = getenv("DATAGO_B200_L2_GROUP_MB")) { long v = atol(mb); if (v >= 1) c->l2_group_bytes = (size_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_TABLE_CACHE_MB")) { long v = atol(mb); if (v >= 0) c->table_cache_cap = (size_t)v << 20; }
     if (const char* v = getenv("DATAGO_B200_FUSED")) c->fused_path = atoi(v) != 0;
+    if (const char* v = getenv("DATAGO_B200_HMMA")) c->hmma = atoi(v) != 0;
     if (const char* mb = getenv("DATAGO_B200_MAX_IMAGE_MB")) { long v = atol(mb); if (v >= 1) c->max_image_bytes = (uint64_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
@@ -323,6 +327,8 @@ struct ItemPlan {
     uint32_t c_out = 0;                 // the conversion writes the c_out = 3 channel payload at out_off
     size_t pipe_off = 0;                // where decode / resize / copy put their result (== out_off unless to_rgb)
     size_t raw_in_off = 0;              // raw pixel inputs: offset in the input arena
+    uint32_t src_pitch = 0;             // bytes per row of the image a resize reads (raw input or decoded JPEG): rows are
+                                        // padded to 16 bytes when a resize follows, tight otherwise
     JpegHeader* hdr = nullptr;
     int wave = -1, wave_local = -1;     // JPEG index inside its wave
     size_t coef_off_blocks = 0, decoded_off = 0;
@@ -341,6 +347,7 @@ struct WavePlan {
     std::vector<std::array<uint32_t, 4>> fgroups;
     std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
     std::vector<uint32_t> pass_first[4];
+    uint32_t mma_tiles[4] = {0, 0, 0, 0};  // tiles of the passes that take the tensor-core kernel; those passes come first
     std::vector<CopyJob> copies;
     std::vector<uint32_t> copy_first;
     std::vector<ToRgbJob> torgb;
@@ -538,11 +545,24 @@ struct PassDraft {
 
 }  // namespace
 
+// Whether the tensor-core horizontal pass can take outputs [t0, t0 + out_w) of table T: the source bytes under every
+// 8-byte output tile and under every 64-byte strip must fit what a CTA stages (see conv_h_mma in kernels_resize.cu).
+static bool hmma_fits(const FilterTable& T, uint32_t t0, uint32_t out_w, uint32_t C, int32_t origin) {
+    const uint32_t row_bytes = out_w * C;
+    auto lo = [&](uint32_t j) { return ((T.start[t0 + j / C] - origin) * (int32_t)C) & ~15; };
+    auto hi = [&](uint32_t j) { const uint32_t x = std::min(out_w - 1, j / C); return (T.start[t0 + x] + T.size[t0 + x] - origin) * (int32_t)C; };
+    for (uint32_t j = 0; j < row_bytes; j += 8)
+        if (hi(j + 7) - lo(j) > (int32_t)kHMmaMaxBand) return false;
+    for (uint32_t j = 0; j < row_bytes; j += kHMmaStrip)
+        if (hi(j + kHMmaStrip - 1) - lo(j) > (int32_t)kHMmaMaxSpan) return false;
+    return true;
+}
+
 // Plans the resize of one image: appends passes / copy jobs to the wave.  src: device pointer of the source image
 // (tight pitch), dst: device pointer of the payload (tight pitch), mid: scratch for intermediates.
 // caller_owned_src: the source is memory of the caller with nothing guaranteed around it (the batch path's sources sit
 // in padded arenas of the library): the pass that reads it is then planned so that no load leaves the image's bytes.
-static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C, const uint8_t* src, uint8_t* dst,
+static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C, const uint8_t* src, uint32_t src_pitch, uint8_t* dst,
                         uint8_t* mid_base, size_t* mid_used, bool caller_owned_src = false) {
     const uint32_t w = p.src_w, h = p.src_h, tw = p.target_w, th = p.target_h;
     auto add_copy = [&](const uint8_t* s, uint32_t pitch, uint32_t row_bytes, uint32_t rows) {
@@ -550,7 +570,7 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         j.src = s; j.dst = dst; j.src_pitch = pitch; j.row_bytes = row_bytes; j.rows = rows; j.tile_first = 0;
         wv.copies.push_back(j);
     };
-    if (p.identity) { add_copy(src, w * C, w * C, h); return; }
+    if (p.identity) { add_copy(src, src_pitch, w * C, h); return; }
     const bool h1 = p.new_w != w, v1 = p.new_h != h;
     const bool h2 = (double)tw != p.crop_w || p.crop_left != std::round(p.crop_left);
     const bool v2 = (double)th != p.crop_h || p.crop_top != std::round(p.crop_top);
@@ -568,7 +588,7 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
     if (v1) { ma = T_v1->start[ra]; mb = T_v1->last_in(ra, rb); } else { ma = ra; mb = rb; }
 
     struct Buf { const uint8_t* ptr; uint32_t pitch; int col0, row0; };  // origin in the current coordinate system
-    Buf cur{src, w * C, 0, 0};
+    Buf cur{src, src_pitch, 0, 0};
     const int n_pass = (int)h1 + (int)v1 + (int)h2 + (int)v2;
     int done = 0;
     auto next_dst = [&](uint32_t out_w, uint32_t out_h, uint32_t* pitch) -> uint8_t* {
@@ -585,10 +605,11 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         cp.src = s; cp.dst = d; cp.src_pitch = spitch; cp.dst_pitch = dpitch; cp.out_w = out_w; cp.out_h = out_h;
         cp.channels = C; cp.src_origin = origin; cp.t0 = t0; cp.tab_n = (uint32_t)T->n; cp.window = (uint32_t)T->window;
         cp.precision = (uint32_t)T->precision; cp.tab_off = tab_off;
-        const bool guarded = caller_owned_src && s >= src && s < src + (size_t)w * h * C;
+        const bool guarded = caller_owned_src && s >= src && s < src + (size_t)src_pitch * h;
         if (horizontal) {
             cp.fast = 1;
             if (guarded) { cp.guard_lo = src; cp.guard_hi = src + (size_t)w * h * C; }
+            else if (pl.ctx->hmma && (((uintptr_t)s | spitch) & 15) == 0 && hmma_fits(*T, t0, out_w, C, origin)) cp.fast = 2;
         } else {
             const uintptr_t bits = (uintptr_t)s | (uintptr_t)d | spitch | dpitch;
             cp.fast = (bits & 15) == 0 && (uint32_t)T->window <= kVFastMaxWindow && (size_t)align_up((size_t)out_w * C, 16) <= spitch &&
@@ -629,7 +650,7 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         cur = Buf{d, pitch, 0, 0};
     }
     if (n_pass == 0)  // same scale, integral crop: a strided copy
-        add_copy(src + ((size_t)ra * w + ca) * C, w * C, tw * C, th);
+        add_copy(src + (size_t)ra * src_pitch + (size_t)ca * C, src_pitch, tw * C, th);
 }
 
 // worst-case scratch of the intermediates of one image's resize
@@ -717,6 +738,8 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         it.to_rgb = want_rgb && it.c != 3;
         it.c_out = it.to_rgb ? 3 : it.c;
         it.out_bytes = (size_t)it.out_w * it.out_h * it.c_out;
+        it.src_pitch = it.w * it.c;
+        if (transform && !it.plan.identity && (it.c == 1 || it.c == 3)) it.src_pitch = (uint32_t)align_up((size_t)it.w * it.c, 16);
     };
     parallel_items(n, inspect);
     size_t blob = 0, rawin = 0, outb = 0;
@@ -726,7 +749,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         it.out_off = outb;
         outb += align_up(it.out_bytes, 256);
         if (it.is_jpeg) blob += align_up(b->headers[i].scan_len, 16) + 16;
-        else { it.raw_in_off = rawin; rawin += align_up((size_t)it.w * it.h * it.c, 256); b->raw_src[i] = items[i].data; }
+        else { it.raw_in_off = rawin; rawin += align_up((size_t)it.src_pitch * it.h, 256); b->raw_src[i] = items[i].data; }
     }
     if (flags & DG_BATCH_COLLATE) {
         // Re-lay the output arena bucket by bucket (buckets in order of first appearance, items in batch order):
@@ -776,7 +799,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                 const JpegHeader& h = *it.hdr;
                 it.nblocks = h.mcux * h.mcuy * (h.ncomp == 1 ? 1 : h.hs * h.vs + 2);
                 need_coef[i] = (size_t)it.nblocks * 128;
-                if (transform) need_big[i] += align_up((size_t)it.w * it.h * it.c, 256);
+                if (transform) need_big[i] += align_up((size_t)it.src_pitch * it.h, 256);
             }
             if (transform) need_big[i] += resize_mid_bound(it.plan, it.c);
             total_coef += need_coef[i];
@@ -846,8 +869,8 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             d.nseg = h.restart ? (mcus + h.restart - 1) / h.restart : 1;
             d.seg_off = (uint32_t)segs; segs += d.nseg;
             d.item = (uint32_t)i;
-            if (transform) { d.out_off = decoded; it.decoded_off = decoded; decoded += align_up((size_t)it.w * it.h * it.c, 256); }
-            else d.out_off = it.pipe_off;
+            if (transform) { d.out_off = decoded; it.decoded_off = decoded; decoded += align_up((size_t)it.src_pitch * it.h, 256); d.out_pitch = it.src_pitch; }
+            else { d.out_off = it.pipe_off; d.out_pitch = it.w * it.c; }
             built.push_back(d);
             built_item.push_back(i);
         }
@@ -969,7 +992,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                 const uint8_t* src = it.is_jpeg ? kBaseS + wv.off_decoded + it.decoded_off : baseP + b->off_rawin + it.raw_in_off;
                 uint8_t* dst = baseP + b->off_out + it.pipe_off;
                 const uint8_t* converted_from = dst;
-                if (transform) plan_resize(pl, wv, it.plan, it.c, src, dst, kBaseS + wv.off_mid, &mid_used);
+                if (transform) plan_resize(pl, wv, it.plan, it.c, src, it.src_pitch, dst, kBaseS + wv.off_mid, &mid_used);
                 else if (!it.is_jpeg) {  // raw pixels, no transform: the payload is the input (JPEGs decode straight into dst)
                     if (it.to_rgb) converted_from = src;  // the conversion reads the input itself
                     else {
@@ -989,10 +1012,13 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             for (int s = 0; s < 4; ++s) {
                 uint32_t t = 0;
                 wv.pass_first[s].push_back(0);
+                if (!(s & 1)) std::stable_partition(wv.passes[s].begin(), wv.passes[s].end(), [](const ConvPass& cp) { return cp.fast == 2; });
+                wv.mma_tiles[s] = 0;
                 for (ConvPass& cp : wv.passes[s]) {
                     cp.tile_first = t;
                     t += conv_tiles(cp, (s & 1) != 0);
                     wv.pass_first[s].push_back(t);
+                    if (!(s & 1) && cp.fast == 2) wv.mma_tiles[s] = t;
                 }
             }
             uint32_t t = 0;
@@ -1081,16 +1107,27 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         });
     }
     if (rawin) {
-        struct Piece { uint8_t* dst; const uint8_t* src; size_t len; };
+        struct Piece { uint8_t* dst; const uint8_t* src; size_t len; uint32_t rows, pitch; };  // rows == 0: one flat run of len bytes
         std::vector<Piece> pieces;  // 4 MB pieces, so that a few large images still spread over the threads
         for (int i = 0; i < n; ++i) {
             const ItemPlan& it = b->items[i];
             if (it.status || it.is_jpeg || !b->raw_src[i]) continue;
-            const size_t bytes = (size_t)it.w * it.h * it.c;
-            for (size_t o = 0; o < bytes; o += (size_t)4 << 20)
-                pieces.push_back({b->h_pin + b->off_rawin + it.raw_in_off + o, b->raw_src[i] + o, std::min(bytes - o, (size_t)4 << 20)});
+            const size_t row = (size_t)it.w * it.c, bytes = row * it.h;
+            uint8_t* dst = b->h_pin + b->off_rawin + it.raw_in_off;
+            if (it.src_pitch == row) {
+                for (size_t o = 0; o < bytes; o += (size_t)4 << 20)
+                    pieces.push_back({dst + o, b->raw_src[i] + o, std::min(bytes - o, (size_t)4 << 20), 0, 0});
+            } else {  // rows are re-pitched on the way: a piece is a run of whole rows
+                const size_t rows_per = std::max<size_t>(1, ((size_t)4 << 20) / row);
+                for (size_t y = 0; y < it.h; y += rows_per)
+                    pieces.push_back({dst + y * it.src_pitch, b->raw_src[i] + y * row, row, (uint32_t)std::min<size_t>(rows_per, it.h - y), it.src_pitch});
+            }
         }
-        HostPool::get().run(pieces.size(), [&](size_t k) { memcpy(pieces[k].dst, pieces[k].src, pieces[k].len); }, 1);
+        HostPool::get().run(pieces.size(), [&](size_t k) {
+            const Piece& pc = pieces[k];
+            if (!pc.rows) { memcpy(pc.dst, pc.src, pc.len); return; }
+            for (uint32_t y = 0; y < pc.rows; ++y) memcpy(pc.dst + (size_t)y * pc.pitch, pc.src + (size_t)y * pc.len, pc.len);
+        }, 1);
     }
     b->raw_src.clear();  // caller memory is not needed after this call
     memcpy(b->h_pin + staged_head, b->meta.bytes.data(), b->meta.bytes.size());
@@ -1281,7 +1318,7 @@ static int batch_run_locked(dg_batch* b) {
                 CU(mark(kStageOf[st], true));
                 const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
                 if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
-                else launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, s);
+                else launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s);
                 ++b->launches;
                 CU(mark(kStageOf[st], false));
             }
@@ -1540,7 +1577,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
     Planner pl{ctx, nullptr};
     WavePlan wv;
     size_t mid_used = 0;
-    plan_resize(pl, wv, plan, channels, device_src, device_dst, mid_base, &mid_used, true);
+    plan_resize(pl, wv, plan, channels, device_src, w * channels, device_dst, mid_base, &mid_used, true);
     if (mid_used > mid_bound) return fail(DG_E_TOO_LARGE, "internal: intermediates exceed their bound");
     Meta m;
     std::vector<uint32_t> packed(pl.table_words_total);
@@ -1551,10 +1588,11 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
     for (int s = 0; s < 4; ++s) {
         uint32_t t = 0;
         wv.pass_first[s].push_back(0);
-        for (ConvPass& cp : wv.passes[s]) {
+        for (ConvPass& cp : wv.passes[s]) {  // at most one pass per stage here, so the tensor-core passes trivially come first
             cp.tile_first = t;
             t += conv_tiles(cp, (s & 1) != 0);
             wv.pass_first[s].push_back(t);
+            if (!(s & 1) && cp.fast == 2) wv.mma_tiles[s] = t;
         }
         m_passes[s] = m.put(wv.passes[s], 16);
         m_pass[s] = put_owner_map(m, wv.pass_first[s]);
@@ -1590,7 +1628,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
         if (wv.passes[st].empty()) continue;
         const ConvPass* passes = (const ConvPass*)(scratch + m_passes[st]);
         if (st & 1) launch_conv_v(passes, map_at(m_pass[st]), tables, s);
-        else launch_conv_h(passes, map_at(m_pass[st]), tables, s);
+        else launch_conv_h(passes, map_at(m_pass[st]), tables, wv.mma_tiles[st], s);
     }
     if (!wv.copies.empty()) launch_copy((const CopyJob*)(scratch + m_copies), map_at(m_copy), s);
     CU(cudaGetLastError());

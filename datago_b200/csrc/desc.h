@@ -54,7 +54,8 @@ struct JpegDesc {
     uint32_t plane_pitch[3];
     uint32_t plane_rows[3];
     uint32_t item;                // index in the batch (status word, result)
-    uint32_t pad;
+    uint32_t out_pitch;           // bytes per row of the decoded image: width * channels for a payload, padded to 16 bytes
+                                  // when a resize reads it (rows then start on 16-byte boundaries for asynchronous copies)
 };
 
 // One 1-D convolution pass over a region of one image (u8, 1 or 3 interleaved channels).
@@ -72,7 +73,7 @@ struct ConvPass {
     uint64_t tab_off;               // word offset in the table pool: start[tab_n] | size[tab_n] | int16 k[window][tab_n]
     uint32_t tile_first;            // first CTA tile of this pass in the launch (prefix sum)
     uint32_t tiles_x;               // tiles per row of tiles
-    uint32_t fast;                  // 1: the staged / vectorised kernel path applies (see kernels_resize.cu)
+    uint32_t fast;                  // vertical: 1 = the vectorised path applies; horizontal: 2 = the tensor-core path (see kernels_resize.cu)
     uint32_t pad;
     // Set when `src` is memory the library does not own (no slack behind it): the horizontal pass then loads no byte
     // outside [guard_lo, guard_hi).  Both null for sources inside the library's own padded arenas.

@@ -65,8 +65,12 @@ inline uint32_t color_tiles(uint32_t width, uint32_t mcuy) {
     // row, so that every pair of output rows that shares its two chroma rows falls into one tile
     return ((width + kColorTileW - 1) / kColorTileW) * (mcuy / kColorMcuRows + 1);
 }
+#ifndef DG_FUSED_MCU_ROWS
+#define DG_FUSED_MCU_ROWS 4
+#endif
+constexpr uint32_t kFusedMcuRows = DG_FUSED_MCU_ROWS;  // MCU rows of a tile of the fused kernel (64 threads per MCU row)
 inline uint32_t fused_tiles(uint32_t width, uint32_t mcuy) {  // the fused kernel's tiles are aligned to MCU rows
-    return ((width + kColorTileW - 1) / kColorTileW) * ((mcuy + kColorMcuRows - 1) / kColorMcuRows);
+    return ((width + kColorTileW - 1) / kColorTileW) * ((mcuy + kFusedMcuRows - 1) / kFusedMcuRows);
 }
 
 // ---- resize ---------------------------------------------------------------------------------------------------------
@@ -74,18 +78,23 @@ constexpr uint32_t kConvTileW = 64, kConvTileH = 16;    // horizontal pass: outp
 constexpr uint32_t kVTileBytes = 256, kVTileH = 4;      // vertical pass, plain path: output bytes x rows per CTA
 constexpr uint32_t kVFastBytes = 1024, kVFastRows = 32; // vertical pass, vector path: 64 x 16-byte columns, 4 x 8 rows
 constexpr uint32_t kVFastMaxWindow = 128;
+// horizontal pass on the tensor cores (ConvPass::fast == 2): output bytes per strip x rows per CTA; limits of what a CTA
+// can stage -- source bytes under one 8-byte output tile, and under a whole strip
+constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 512, kHMmaMaxBand = 256, kHMmaMaxSpan = 1024;
 inline uint32_t conv_tiles_x(const ConvPass& p, bool vertical) {
+    if (!vertical && p.fast == 2) return (p.out_w * p.channels + kHMmaStrip - 1) / kHMmaStrip;
     if (!vertical) return (p.out_w + kConvTileW - 1) / kConvTileW;
     const uint32_t row_bytes = p.out_w * p.channels;
     return p.fast ? (row_bytes + kVFastBytes - 1) / kVFastBytes : (row_bytes + kVTileBytes - 1) / kVTileBytes;
 }
 inline uint32_t conv_tiles(const ConvPass& p, bool vertical) {
-    const uint32_t rows = !vertical ? kConvTileH : p.fast ? kVFastRows : kVTileH;
+    const uint32_t rows = !vertical ? (p.fast == 2 ? kHMmaRows : kConvTileH) : p.fast ? kVFastRows : kVTileH;
     return conv_tiles_x(p, vertical) * ((p.out_h + rows - 1) / rows);
 }
 constexpr uint32_t kCopyTileBytes = 4096;
 
-void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
+// the passes that take the tensor-core kernel (fast == 2) come first in `passes` and own tiles [0, mma_tiles)
+void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s);
 void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
 void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s);
 constexpr uint32_t kToRgbTilePx = 2048;  // pixels per CTA of the RGB8 conversion

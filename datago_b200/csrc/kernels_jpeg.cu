@@ -732,8 +732,10 @@ constexpr int kCTileRows = 8 * (int)kColorMcuRows + 2;  // chroma rows of a 4:2:
 // replicated into the halo position, which is what the edge rules of the triangle filter amount to.
 // Warp q loads tile rows q, q + 8, ... of both components; a lane loads word `lane` and, for two lanes, word 32 + lane.
 // Two steps, both by every thread of the CTA (256), with a __syncthreads() after each: chroma_tile_fetch, chroma_tile_edges.
-__device__ __forceinline__ void chroma_tile_fetch(uint8_t (&s_c)[2][kCTileRows][kCTileCols], const JpegWave& w, const JpegDesc& d,
+template <int ROWS>
+__device__ __forceinline__ void chroma_tile_fetch(uint8_t (&s_c)[2][ROWS][kCTileCols], const JpegWave& w, const JpegDesc& d,
                                                   int tx, int ty, int dh) {
+    constexpr int kCTileRows = ROWS;
     const int lane = threadIdx.x & 31, rowi = threadIdx.x >> 5;
     const int cx0 = tx * (int)(kColorTileW / 2), cy0 = ty * 8 * (int)kColorMcuRows;
     constexpr int kWords = kCTileCols / 4;  // 34
@@ -762,7 +764,9 @@ __device__ __forceinline__ void chroma_tile_fetch(uint8_t (&s_c)[2][kCTileRows][
     }
 }
 
-__device__ __forceinline__ void chroma_tile_edges(uint8_t (&s_c)[2][kCTileRows][kCTileCols], int tx, int dw) {
+template <int ROWS>
+__device__ __forceinline__ void chroma_tile_edges(uint8_t (&s_c)[2][ROWS][kCTileCols], int tx, int dw) {
+    constexpr int kCTileRows = ROWS;
     const int cx0 = tx * (int)(kColorTileW / 2);
     if (threadIdx.x < 2 * kCTileRows) {
         const int comp = threadIdx.x / kCTileRows, r = threadIdx.x - comp * kCTileRows;
@@ -783,7 +787,8 @@ __device__ __forceinline__ void load_chroma_tile(uint8_t (&s_c)[2][kCTileRows][k
 // Triangle upsampling of the chroma for 8 pixels of two output rows that read the same two chroma rows: row A has
 // tile row p as its near row and p + 1 as its far row, row B the other way round (output rows 2j+1 and 2j+2 of the
 // image).  cl = s_c column of the thread's first chroma sample (a word boundary).  Results are sample - 128.
-__device__ __forceinline__ void chroma_pair(const uint8_t (&s_c)[2][kCTileRows][kCTileCols], int p, int cl, int32_t (&cbA)[8],
+template <bool WANT_A = true, bool WANT_B = true, int ROWS = kCTileRows>
+__device__ __forceinline__ void chroma_pair(const uint8_t (&s_c)[2][ROWS][kCTileCols], int p, int cl, int32_t (&cbA)[8],
                                             int32_t (&crA)[8], int32_t (&cbB)[8], int32_t (&crB)[8]) {
     constexpr uint32_t kEvenA = 0x03090103u, kOddA = 0x01030309u;  // bytes: (near a, far a, near b, far b)
     constexpr uint32_t kEvenB = 0x09030301u, kOddB = 0x03010903u;  // the same bytes with near and far exchanged
@@ -798,14 +803,18 @@ __device__ __forceinline__ void chroma_pair(const uint8_t (&s_c)[2][kCTileRows][
         const uint32_t Rp = __byte_perm(I1, __byte_perm(Nn, Nf, 0x0040), 0x5432);  // (c+3, c+4)
         int32_t* da = comp ? crA : cbA;
         int32_t* db = comp ? crB : cbB;
-        da[0] = (int32_t)dp4a_u(Lp, kEvenA, kE) >> 4; da[1] = (int32_t)dp4a_u(I0, kOddA, kO) >> 4;
-        da[2] = (int32_t)dp4a_u(I0, kEvenA, kE) >> 4; da[3] = (int32_t)dp4a_u(J, kOddA, kO) >> 4;
-        da[4] = (int32_t)dp4a_u(J, kEvenA, kE) >> 4;  da[5] = (int32_t)dp4a_u(I1, kOddA, kO) >> 4;
-        da[6] = (int32_t)dp4a_u(I1, kEvenA, kE) >> 4; da[7] = (int32_t)dp4a_u(Rp, kOddA, kO) >> 4;
-        db[0] = (int32_t)dp4a_u(Lp, kEvenB, kE) >> 4; db[1] = (int32_t)dp4a_u(I0, kOddB, kO) >> 4;
-        db[2] = (int32_t)dp4a_u(I0, kEvenB, kE) >> 4; db[3] = (int32_t)dp4a_u(J, kOddB, kO) >> 4;
-        db[4] = (int32_t)dp4a_u(J, kEvenB, kE) >> 4;  db[5] = (int32_t)dp4a_u(I1, kOddB, kO) >> 4;
-        db[6] = (int32_t)dp4a_u(I1, kEvenB, kE) >> 4; db[7] = (int32_t)dp4a_u(Rp, kOddB, kO) >> 4;
+        if (WANT_A) {
+            da[0] = (int32_t)dp4a_u(Lp, kEvenA, kE) >> 4; da[1] = (int32_t)dp4a_u(I0, kOddA, kO) >> 4;
+            da[2] = (int32_t)dp4a_u(I0, kEvenA, kE) >> 4; da[3] = (int32_t)dp4a_u(J, kOddA, kO) >> 4;
+            da[4] = (int32_t)dp4a_u(J, kEvenA, kE) >> 4;  da[5] = (int32_t)dp4a_u(I1, kOddA, kO) >> 4;
+            da[6] = (int32_t)dp4a_u(I1, kEvenA, kE) >> 4; da[7] = (int32_t)dp4a_u(Rp, kOddA, kO) >> 4;
+        }
+        if (WANT_B) {
+            db[0] = (int32_t)dp4a_u(Lp, kEvenB, kE) >> 4; db[1] = (int32_t)dp4a_u(I0, kOddB, kO) >> 4;
+            db[2] = (int32_t)dp4a_u(I0, kEvenB, kE) >> 4; db[3] = (int32_t)dp4a_u(J, kOddB, kO) >> 4;
+            db[4] = (int32_t)dp4a_u(J, kEvenB, kE) >> 4;  db[5] = (int32_t)dp4a_u(I1, kOddB, kO) >> 4;
+            db[6] = (int32_t)dp4a_u(I1, kEvenB, kE) >> 4; db[7] = (int32_t)dp4a_u(Rp, kOddB, kO) >> 4;
+        }
     }
 }
 
@@ -835,7 +844,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
             const int y = y_base + rowi + 8 * k;
             if (y >= H) break;
             const uint2 v = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
-            uint8_t* o = out + (size_t)y * W + x;
+            uint8_t* o = out + (size_t)y * d.out_pitch + x;
             if (npx == 8 && (reinterpret_cast<uintptr_t>(o) & 7u) == 0) __stcs(reinterpret_cast<uint2*>(o), v);
             else for (int i = 0; i < npx; ++i) o[i] = (uint8_t)((i < 4 ? v.x : v.y) >> (8 * (i & 3)));
         }
@@ -867,11 +876,11 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
             uint32_t px[6];
             if (yA >= 0) {
                 ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
-                store_rgb8(out + ((size_t)yA * W + x) * 3, px, npx);
+                store_rgb8(out + (size_t)yA * d.out_pitch + x * 3, px, npx);
             }
             if (yB < H) {
                 ycc_to_rgb8(yb.x, yb.y, cbB, crB, px);
-                store_rgb8(out + ((size_t)yB * W + x) * 3, px, npx);
+                store_rgb8(out + (size_t)yB * d.out_pitch + x * 3, px, npx);
             }
         }
         return;
@@ -893,7 +902,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
             const uint2 yv = __ldg(reinterpret_cast<const uint2*>(yp + (size_t)y * ypitch + x));
             uint32_t px[6];
             ycc_to_rgb8(yv.x, yv.y, cbv, crv, px);
-            store_rgb8(out + ((size_t)y * W + x) * 3, px, npx);
+            store_rgb8(out + (size_t)y * d.out_pitch + x * 3, px, npx);
         }
         return;
     }
@@ -908,7 +917,7 @@ __global__ void __launch_bounds__(kColorThreads, 4) k_color(JpegWave w, uint32_t
         for (int i = 0; i < npx; ++i) {
             const int Y = __ldg(yp + (size_t)y * ypitch + x + i);
             const int cb = cbp.at(x + i, y) - 128, cr = crp.at(x + i, y) - 128;
-            uint8_t* o = out + ((size_t)y * W + x + i) * 3;
+            uint8_t* o = out + (size_t)y * d.out_pitch + (x + i) * 3;
             o[0] = (uint8_t)min(max(Y + ((91881 * cr + 32768) >> 16), 0), 255);
             o[1] = (uint8_t)min(max(Y + ((-22554 * cb - 46802 * cr + 32768) >> 16), 0), 255);
             o[2] = (uint8_t)min(max(Y + ((116130 * cb + 32768) >> 16), 0), 255);
@@ -984,171 +993,262 @@ void launch_idct_chroma(const JpegWave& w, uint32_t first, uint32_t count, bool 
     if (count) k_idct_chroma<<<(count + kIdctThreads - 1) / kIdctThreads, kIdctThreads, 0, s>>>(w, first, count, rezero);
 }
 
-constexpr int kFusedThreads = 256;
+constexpr int kFusedThreads = 64 * (int)kFusedMcuRows;
+constexpr int kFusedWarps = kFusedThreads / 32;
+constexpr int kFTileRows = 8 * (int)kFusedMcuRows + 2;  // chroma rows of a tile plus one halo row above and below
 constexpr int kLumaPitch = kColorTileW + 8;  // 8 * pitch = 64 (mod 128): the two block rows a half warp stores to fall into different banks
-constexpr int kLumaRows = 16 * (int)kColorMcuRows;
+constexpr int kLumaRows = 16 * (int)kFusedMcuRows;
 
-struct FusedSmem {
-    union {
-        uint4 coef[kFusedThreads / 32][256];    // staged luma coefficients, 4 KB per warp (8 MCUs x 4 blocks)
-        uint8_t luma[kLumaRows][kLumaPitch];    // ... overwritten by the reconstructed luma tile
-    };
-    uint8_t c[2][kCTileRows][kCTileCols];
+// What a CTA needs to know about one tile, gathered by one thread while the others work on the previous tile.
+struct TileInfo {
+    const int16_t* coef;   // first coefficient block of the image
+    const uint8_t* cb;     // chroma planes
+    const uint8_t* cr;
+    uint8_t* out;          // decoded image
+    const uint4* qq;       // luma quantiser rows (dp2a layout)
+    uint32_t mcux, mcuy, width, height, cpitch, tx, ty, opitch;  // opitch: bytes per row of the decoded image
 };
 
-#ifndef DG_FUSED_MIN_CTAS
-#define DG_FUSED_MIN_CTAS 3
-#endif
-__global__ void __launch_bounds__(kFusedThreads, DG_FUSED_MIN_CTAS) k_luma_color(JpegWave w, uint32_t first_tile, bool rezero) {
-    __shared__ __align__(16) FusedSmem sm;
-    __shared__ uint32_t s_img;
-    __shared__ uint32_t s_count[kFusedThreads / 32];
-    __shared__ uint8_t s_perm[kFusedThreads], s_pcls[kFusedThreads];
-    if (threadIdx.x == 0) s_img = owner_of(w.fused_tiles, first_tile + blockIdx.x);
-    __syncthreads();
-    const uint32_t o = s_img;
+struct FusedSmem {
+    uint4 coef[kFusedThreads / 32][256];          // staged luma coefficients of the tile being set up, 4 KB per warp
+    uint8_t luma[kLumaRows][kLumaPitch];          // reconstructed luma tile
+    uint8_t c[2][2][kFTileRows][kCTileCols];      // chroma tiles of this tile and of the next one
+    TileInfo info[2];
+    uint32_t count[kFusedThreads / 32];
+    uint8_t perm[kFusedThreads], pcls[kFusedThreads];
+};
+
+__device__ __forceinline__ void fill_tile_info(TileInfo& t, const JpegWave& w, uint32_t tile_index) {
+    const uint32_t o = owner_of(w.fused_tiles, tile_index);
     const JpegDesc& d = w.descs[w.fused_first + o];
-    const uint32_t tile = first_tile + blockIdx.x - __ldg(w.fused_tiles.first + o);
-    const int W = (int)d.width, H = (int)d.height;
+    const uint32_t tile = tile_index - __ldg(w.fused_tiles.first + o);
     const uint32_t tiles_x = (d.width + kColorTileW - 1) / kColorTileW;
-    const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
+    t.ty = tile / tiles_x;
+    t.tx = tile - t.ty * tiles_x;
+    t.coef = w.coef + (size_t)d.block_off * 64;
+    t.cb = w.planes + d.plane_off[1];
+    t.cr = w.planes + d.plane_off[2];
+    t.out = w.out + d.out_off;
+    t.qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[0] * 32);
+    t.mcux = d.mcux; t.mcuy = d.mcuy; t.width = d.width; t.height = d.height; t.cpitch = d.plane_pitch[1];
+    t.opitch = d.out_pitch;
+}
+
+// Queues the asynchronous copies of one tile's inputs (one commit group per thread).
+//   luma coefficients: warp q owns MCU row q / 2 of the tile and MCUs 8 (q % 2) .. + 7 of it; step i copies the four luma
+//     blocks of MCU i, 512 consecutive bytes, lane l row l % 8 of block l / 8 (into the XOR-swizzled layout the IDCT reads
+//     back).  MCUs outside the image are replaced by the nearest one inside: their results land in tile positions no
+//     output pixel reads.
+//   chroma tile: rows cy0-1 .. cy0+8*rows, columns cx0-4 .. cx0+131 as aligned words, coordinates clamped to the plane.
+__device__ __forceinline__ void queue_tile_copies(FusedSmem& sm, const TileInfo& t, int buf) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-
-    // ---- luma coefficients of the tile: warp q owns MCU row q / 2 of the tile and MCUs 8 (q % 2) .. + 7 of it; step i
-    //      copies the four luma blocks of MCU i, 512 consecutive bytes.  MCUs outside the image are replaced by the
-    //      nearest one inside (their results land in tile positions no output pixel reads).
-    const uint32_t mrow = warp >> 1, half = warp & 1u;
-    const uint32_t my = ty * kColorMcuRows + mrow, mx0 = tx * 16 + half * 8;
-    const uint32_t myc = min(my, d.mcuy - 1);
-    const int16_t* row_base = w.coef + ((size_t)d.block_off + (size_t)myc * d.mcux * 6u) * 64;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t bb = i * 4 + (lane >> 3), r = lane & 7;
-        const uint32_t mxc = min(mx0 + i, d.mcux - 1);
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&sm.coef[warp][bb * 8 + (r ^ (bb & 7))]);
-        const void* src = row_base + (size_t)mxc * 384 + lane * 8;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-
-    // ---- chroma tile from the planes (written by k_idct_chroma), while the copies are in flight
-    const int dw = (W + 1) / 2, dh = (H + 1) / 2;
-    chroma_tile_fetch(sm.c, w, d, (int)tx, (int)ty, dh);
-
-    // ---- luma IDCT, one block per thread.  How much of the butterfly a block needs depends on where its non-zero
-    //      coefficients end, and a warp runs the path its least sparse lane needs; so the tile's 256 blocks are first
-    //      sorted by class (counting sort, classes of the lanes' own blocks) and thread t then reconstructs the t-th
-    //      block of that order: all but at most three warps of the CTA are uniform.
-    const uint32_t mcu_local = lane >> 2;
-    const bool valid = my < d.mcuy && mx0 + mcu_local < d.mcux;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
-    int cls;
-    uint32_t ballot_mine;
     {
-        uint4 c[8];
+        const uint32_t mrow = warp >> 1, half = warp & 1u;
+        const uint32_t myc = min(t.ty * kFusedMcuRows + mrow, t.mcuy - 1), mx0 = t.tx * 16 + half * 8;
+        const int16_t* row_base = t.coef + (size_t)myc * t.mcux * 384;
 #pragma unroll
-        for (int r = 0; r < 8; ++r) c[r] = sm.coef[warp][lane * 8 + (r ^ (lane & 7))];
-        cls = block_class(c);
-        if (rezero) {
-            uint32_t rowmask = 0;
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t bb = i * 4 + (lane >> 3), r = lane & 7;
+            const uint32_t mxc = min(mx0 + i, t.mcux - 1);
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(&sm.coef[warp][bb * 8 + (r ^ (bb & 7))]);
+            const void* src = row_base + (size_t)mxc * 384 + lane * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+    }
+    {
+        const int dh = ((int)t.height + 1) / 2;
+        const int cx0 = (int)t.tx * (int)(kColorTileW / 2), cy0 = (int)t.ty * 8 * (int)kFusedMcuRows;
+        constexpr int kWords = kCTileCols / 4;  // 34
+        const int wmax = (int)(t.cpitch / 4) - 1, w0 = cx0 / 4 - 1;
+        const int g0 = min(max(w0 + (int)lane, 0), wmax), g1 = min(max(w0 + 32 + (int)lane, 0), wmax);
 #pragma unroll
-            for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
-            if (!valid) rowmask = 0;  // a stand-in MCU belongs to other lanes (or another CTA, which may not have read it yet)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
-                if ((m >> (lane & 7)) & 1u)
-                    reinterpret_cast<uint4*>(const_cast<int16_t*>(row_base) + (size_t)(mx0 + i) * 384)[lane] = make_uint4(0, 0, 0, 0);
+        for (int rr = 0; rr < (kFTileRows + kFusedWarps - 1) / kFusedWarps; ++rr) {
+            const int r = (int)warp + kFusedWarps * rr;
+            if (r < kFTileRows) {
+                const int gy = min(max(cy0 + r - 1, 0), dh - 1);
+                const uint32_t* gb = reinterpret_cast<const uint32_t*>(t.cb + (size_t)gy * t.cpitch);
+                const uint32_t* gr = reinterpret_cast<const uint32_t*>(t.cr + (size_t)gy * t.cpitch);
+                const uint32_t sb = (uint32_t)__cvta_generic_to_shared(&sm.c[buf][0][r][0]);
+                const uint32_t sr = (uint32_t)__cvta_generic_to_shared(&sm.c[buf][1][r][0]);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sb + lane * 4), "l"(gb + g0) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sr + lane * 4), "l"(gr + g0) : "memory");
+                if (lane < kWords - 32) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sb + (32 + lane) * 4), "l"(gb + g1) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sr + (32 + lane) * 4), "l"(gr + g1) : "memory");
+                }
             }
         }
     }
-    {
-        const uint32_t b0 = __ballot_sync(0xFFFFFFFFu, cls == 0), b1 = __ballot_sync(0xFFFFFFFFu, cls == 1),
-                       b2 = __ballot_sync(0xFFFFFFFFu, cls == 2);
-        if (lane == 0) s_count[warp] = (uint32_t)__popc(b0) | ((uint32_t)__popc(b1) << 10) | ((uint32_t)__popc(b2) << 20);
-        ballot_mine = cls == 0 ? b0 : cls == 1 ? b1 : cls == 2 ? b2 : ~(b0 | b1 | b2);
-    }
-    __syncthreads();  // class counts and the chroma tile are in shared memory
-    {
-        // per-class counts in 10-bit fields (a sum is at most 256; the fourth class is the rest): before this warp, in total
-        uint32_t before = 0, total = 0;
-#pragma unroll
-        for (int i = 0; i < kFusedThreads / 32; ++i) { const uint32_t v = s_count[i]; if (i < (int)warp) before += v; total += v; }
-        const uint32_t t0 = total & 1023u, t1 = (total >> 10) & 1023u, t2 = total >> 20;
-        const uint32_t p0 = before & 1023u, p1 = (before >> 10) & 1023u, p2 = before >> 20;
-        uint32_t pos = cls == 0 ? p0 : cls == 1 ? t0 + p1 : cls == 2 ? t0 + t1 + p2 : t0 + t1 + t2 + (warp * 32u - p0 - p1 - p2);
-        pos += __popc(ballot_mine & ((1u << lane) - 1u));
-        s_perm[pos & 255u] = (uint8_t)threadIdx.x;
-        s_pcls[pos & 255u] = (uint8_t)cls;
-    }
-    chroma_tile_edges(sm.c, (int)tx, dw);
-    __syncthreads();
-    const uint32_t blk = s_perm[threadIdx.x];
-    const int wcls = warp_class((int)s_pcls[threadIdx.x]);
-    uint4 c[8];
-    {
-        const uint32_t bw = blk >> 5, bl = blk & 31u;
-        const uint4* rows = &sm.coef[bw][bl * 8];
-        if (wcls == kClsFull) {
-#pragma unroll
-            for (int r = 0; r < 8; ++r) c[r] = rows[r ^ (bl & 7)];
-        } else if (wcls == kCls4x4) {
-#pragma unroll
-            for (int r = 0; r < 4; ++r) { const uint2 v = *reinterpret_cast<const uint2*>(&rows[r ^ (bl & 7)]); c[r].x = v.x; c[r].y = v.y; }
-        } else {
-            c[0].x = rows[0 ^ (bl & 7)].x;
-            c[1].x = rows[1 ^ (bl & 7)].x;
-        }
-    }
-    __syncthreads();  // every thread has its coefficients in registers: the staging area becomes the luma tile
-    {
-        const uint4* qq = reinterpret_cast<const uint4*>(w.qt32 + (size_t)d.qt[0] * 32);
-        // position of block blk in the tile, from the lane / warp that staged it
-        const uint32_t bw = blk >> 5, bl = blk & 31u;
-        const uint32_t bx = (bw & 1u) * 16 + (bl >> 2) * 2 + (bl & 1u), by = (bw >> 1) * 2 + ((bl >> 1) & 1u);
-        uint8_t* dst = &sm.luma[by * 8][bx * 8];
-        idct_block(c, qq, wcls, [&](int r, uint32_t lo, uint32_t hi) {
-            *reinterpret_cast<uint2*>(dst + r * kLumaPitch) = make_uint2(lo, hi);
-        });
-    }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
 
-    // ---- upsampling + colour conversion.  Output rows 2j+1 and 2j+2 read the same two chroma rows with the near / far
-    //      weights exchanged, so a thread converts such a pair at a time (pair p of the tile = tile rows 2p-1 and 2p, chroma
-    //      tile rows p and p+1).  The tile's first row is the second half of pair 0 and its last row the first half of
-    //      pair 32: warp 0 converts those two halves in a fifth step.
-    const int x = (int)tx * (int)kColorTileW + (int)lane * 8;
-    if (x >= W) return;
-    const int npx = min(8, W - x);
-    const int cl = (int)lane * 4 + 4;
-    const int y0 = (int)ty * kLumaRows;
-    uint8_t* out = w.out + d.out_off;
+// The full butterfly needs twice the registers of everything else in the fused kernel and runs for a few per cent of
+// the blocks: it lives in a function of its own, so that it does not set the register count of the whole kernel.
+__device__ __noinline__ void idct_full_to_tile(const uint4* rows, uint32_t swz, const uint4* qq, uint8_t* dst) {
+    uint4 c[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) c[r] = rows[r ^ swz];
+    idct_block(c, qq, kClsFull, [&](int r, uint32_t lo, uint32_t hi) {
+        *reinterpret_cast<uint2*>(dst + r * kLumaPitch) = make_uint2(lo, hi);
+    });
+}
+
+// Persistent: CTA b handles tiles b, b + gridDim.x, ...  While a tile is being reconstructed, the inputs of the CTA's
+// next tile are already on their way into shared memory, so no CTA waits for DRAM except on its first tile.
+#ifndef DG_FUSED_MIN_CTAS
+#define DG_FUSED_MIN_CTAS (12 / DG_FUSED_MCU_ROWS)
+#endif
+__global__ void __launch_bounds__(kFusedThreads, DG_FUSED_MIN_CTAS) k_luma_color(JpegWave w, uint32_t first_tile, uint32_t count, bool rezero) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    FusedSmem& sm = *reinterpret_cast<FusedSmem*>(smem_raw);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t mrow = warp >> 1, half = warp & 1u, mcu_local = lane >> 2;
+
+    if (threadIdx.x == 0) fill_tile_info(sm.info[0], w, first_tile + blockIdx.x);
+    __syncthreads();
+    queue_tile_copies(sm, sm.info[0], 0);
+
+    int cur = 0;
+    for (uint32_t tile = blockIdx.x; tile < count; tile += gridDim.x, cur ^= 1) {
+        const bool has_next = tile + gridDim.x < count;
+        const TileInfo& t = sm.info[cur];  // read where needed: a copy in registers would not fit beside the butterfly
+        const int W = (int)t.width, H = (int)t.height;
+
+        // ---- this tile's inputs have been on their way since the previous tile was being reconstructed
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();  // the coefficients a warp reads were copied by its own lanes
+
+        // ---- luma IDCT, one block per thread.  How much of the butterfly a block needs depends on where its non-zero
+        //      coefficients end, and a warp runs the path its least sparse lane needs; so the tile's 256 blocks are first
+        //      sorted by class (counting sort, classes of the lanes' own blocks) and thread i then reconstructs the i-th
+        //      block of that order: all but at most three warps of the CTA are uniform.
+        const uint32_t my = t.ty * kFusedMcuRows + mrow, mx0 = t.tx * 16 + half * 8;
+        const bool valid = my < t.mcuy && mx0 + mcu_local < t.mcux;
+        int cls;
+        uint32_t ballot_mine;
+        {
+            uint4 c[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) c[r] = sm.coef[warp][lane * 8 + (r ^ (lane & 7))];
+            cls = block_class(c);
+            if (rezero) {
+                // the rows found non-zero are written back as zeros, which leaves the coefficient buffer clean for the next
+                // wave that uses it; lane l of step i owns row l % 8 of block l / 8 of MCU i, as in the copy
+                uint32_t rowmask = 0;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) rowmask |= ((c[r].x | c[r].y | c[r].z | c[r].w) != 0 ? 1u : 0u) << r;
+                if (!valid) rowmask = 0;  // a stand-in MCU belongs to other lanes (or another CTA, which may not have read it yet)
+                int16_t* row_base = const_cast<int16_t*>(t.coef) + (size_t)min(my, t.mcuy - 1) * t.mcux * 384;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t m = __shfl_sync(0xFFFFFFFFu, rowmask, i * 4 + (lane >> 3));
+                    if ((m >> (lane & 7)) & 1u)
+                        reinterpret_cast<uint4*>(row_base + (size_t)(mx0 + i) * 384)[lane] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+        {
+            const uint32_t b0 = __ballot_sync(0xFFFFFFFFu, cls == 0), b1 = __ballot_sync(0xFFFFFFFFu, cls == 1),
+                           b2 = __ballot_sync(0xFFFFFFFFu, cls == 2);
+            if (lane == 0) sm.count[warp] = (uint32_t)__popc(b0) | ((uint32_t)__popc(b1) << 10) | ((uint32_t)__popc(b2) << 20);
+            ballot_mine = cls == 0 ? b0 : cls == 1 ? b1 : cls == 2 ? b2 : ~(b0 | b1 | b2);
+        }
+        __syncthreads();  // class counts are in shared memory, and so is the chroma tile (every thread waited for its copies)
+        // every thread has left the previous tile behind: its descriptor slot can take the next tile's
+        if (threadIdx.x == 0 && has_next) fill_tile_info(sm.info[cur ^ 1], w, first_tile + tile + gridDim.x);
+        {
+            // per-class counts in 10-bit fields (a sum is at most 256; the fourth class is the rest): before this warp, in total
+            uint32_t before = 0, total = 0;
+#pragma unroll
+            for (int i = 0; i < kFusedThreads / 32; ++i) { const uint32_t v = sm.count[i]; if (i < (int)warp) before += v; total += v; }
+            const uint32_t t0 = total & 1023u, t1 = (total >> 10) & 1023u, t2 = total >> 20;
+            const uint32_t p0 = before & 1023u, p1 = (before >> 10) & 1023u, p2 = before >> 20;
+            uint32_t pos = cls == 0 ? p0 : cls == 1 ? t0 + p1 : cls == 2 ? t0 + t1 + p2 : t0 + t1 + t2 + (warp * 32u - p0 - p1 - p2);
+            pos += __popc(ballot_mine & ((1u << lane) - 1u));
+            sm.perm[pos & (kFusedThreads - 1)] = (uint8_t)threadIdx.x;
+            sm.pcls[pos & (kFusedThreads - 1)] = (uint8_t)cls;
+        }
+        chroma_tile_edges(sm.c[cur], (int)t.tx, (W + 1) / 2);
+        __syncthreads();
+        {
+            const uint32_t blk = sm.perm[threadIdx.x];
+            const int wcls = warp_class((int)sm.pcls[threadIdx.x]);
+            // where block blk was staged, and where it lies in the tile (from the lane / warp that staged it)
+            const uint32_t bw = blk >> 5, bl = blk & 31u, swz = bl & 7u;
+            const uint4* rows = &sm.coef[bw][bl * 8];
+            const uint32_t bx = (bw & 1u) * 16 + (bl >> 2) * 2 + (bl & 1u), by = (bw >> 1) * 2 + ((bl >> 1) & 1u);
+            uint8_t* dst = &sm.luma[by * 8][bx * 8];
+            if (wcls == kClsFull) {
+                idct_full_to_tile(rows, swz, t.qq, dst);
+            } else {
+                uint4 c[8];
+                if (wcls == kCls4x4) {
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) { const uint2 v = *reinterpret_cast<const uint2*>(&rows[r ^ swz]); c[r].x = v.x; c[r].y = v.y; }
+                } else {
+                    c[0].x = rows[0 ^ swz].x;
+                    c[1].x = rows[1 ^ swz].x;
+                }
+                idct_block(c, t.qq, wcls, [&](int r, uint32_t lo, uint32_t hi) {
+                    *reinterpret_cast<uint2*>(dst + r * kLumaPitch) = make_uint2(lo, hi);
+                });
+            }
+        }
+        __syncthreads();  // the luma tile is complete and the staged coefficients have all been consumed
+        // the next tile's inputs travel while this tile is converted
+        if (has_next) queue_tile_copies(sm, sm.info[cur ^ 1], cur ^ 1);
+
+        // ---- upsampling + colour conversion.  Output rows 2j+1 and 2j+2 read the same two chroma rows with the near / far
+        //      weights exchanged, so a thread converts such a pair at a time (pair p of the tile = tile rows 2p-1 and 2p,
+        //      chroma tile rows p and p+1).  The tile's first row is the second half of pair 0 and its last row the first
+        //      half of the pair after the last whole one: warp 0 converts those two halves in an extra step.
+        const int x = (int)t.tx * (int)kColorTileW + (int)lane * 8;
+        if (x < W) {
+            const int npx = min(8, W - x);
+            const int cl = (int)lane * 4 + 4;
+            const int y0 = (int)t.ty * kLumaRows;
 #pragma unroll 1
-    for (int m = 0; m < 5; ++m) {
-        const int p = (int)warp + 8 * m;
-        if (p > kLumaRows / 2) break;
-        const int yA = y0 + 2 * p - 1, yB = yA + 1;
-        const bool doA = p > 0 && yA < H, doB = p < kLumaRows / 2 && yB < H;
-        if (!doA && !doB) break;
-        int32_t cbA[8], crA[8], cbB[8], crB[8];
-        chroma_pair(sm.c, p, cl, cbA, crA, cbB, crB);
-        uint32_t px[6];
-        if (doA) {
-            const uint2 ya = *reinterpret_cast<const uint2*>(&sm.luma[2 * p - 1][lane * 8]);
-            ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
-            store_rgb8(out + ((size_t)yA * W + x) * 3, px, npx);
+            for (int m = 0; m <= kLumaRows / 2 / kFusedWarps; ++m) {
+                const int p = (int)warp + kFusedWarps * m;
+                if (p > kLumaRows / 2) break;
+                const int yA = y0 + 2 * p - 1, yB = yA + 1;
+                const bool doA = p > 0 && yA < H, doB = p < kLumaRows / 2 && yB < H;
+                if (!doA && !doB) break;
+                int32_t cbA[8], crA[8], cbB[8], crB[8];
+                chroma_pair<true, true, kFTileRows>(sm.c[cur], p, cl, cbA, crA, cbB, crB);
+                uint32_t px[6];
+                if (doA) {
+                    const uint2 ya = *reinterpret_cast<const uint2*>(&sm.luma[2 * p - 1][lane * 8]);
+                    ycc_to_rgb8(ya.x, ya.y, cbA, crA, px);
+                    store_rgb8(t.out + (size_t)yA * t.opitch + x * 3, px, npx);
+                }
+                if (doB) {
+                    const uint2 yb = *reinterpret_cast<const uint2*>(&sm.luma[2 * p][lane * 8]);
+                    ycc_to_rgb8(yb.x, yb.y, cbB, crB, px);
+                    store_rgb8(t.out + (size_t)yB * t.opitch + x * 3, px, npx);
+                }
+            }
         }
-        if (doB) {
-            const uint2 yb = *reinterpret_cast<const uint2*>(&sm.luma[2 * p][lane * 8]);
-            ycc_to_rgb8(yb.x, yb.y, cbB, crB, px);
-            store_rgb8(out + ((size_t)yB * W + x) * 3, px, npx);
-        }
+        // The next iteration writes sm.luma, sm.c[cur] and sm.info[cur] only behind its first barrier, which every thread
+        // reaches after this phase.
     }
 }
 
 void launch_luma_color(const JpegWave& w, uint32_t first_tile, uint32_t count, bool rezero, cudaStream_t s) {
-    if (count) k_luma_color<<<count, kFusedThreads, 0, s>>>(w, first_tile, rezero);
+    if (!count) return;
+    // per device, once: the kernel's shared memory exceeds the default limit; the grid is sized from the SM count
+    static int sm_count[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!sm_count[dev]) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cudaFuncSetAttribute(k_luma_color, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FusedSmem));
+        sm_count[dev] = n > 0 ? n : 148;
+    }
+    const uint32_t grid = min(count, (uint32_t)(sm_count[dev] * DG_FUSED_MIN_CTAS));
+    k_luma_color<<<grid, kFusedThreads, sizeof(FusedSmem), s>>>(w, first_tile, count, rezero);
 }
 
 }  // namespace dg

@@ -209,7 +209,8 @@ DG_API int dg_batch_counters(const dg_batch* b, uint64_t* h2d_bytes, uint64_t* d
  * rounds, subsequence decodes (guess + re-decodes + write pass).  Synchronises the stream. */
 DG_API int dg_batch_huffman_stats(dg_batch* b, uint64_t out[3]);
 /* Intermediate device buffers, for stage-by-stage parity tests: coefficient words (int16, scan order) and, for
- * decode+resize batches, the full-size decoded image of item i. */
+ * decode+resize batches, the full-size decoded image of item i (its rows padded to a multiple of 16 bytes unless the
+ * item's plan is an identity). */
 DG_API int dg_batch_debug(const dg_batch* b, int i, const int16_t** coef, uint64_t* nblocks, const uint8_t** decoded);
 DG_API void dg_batch_destroy(dg_batch* b);
 

@@ -183,3 +183,32 @@ def test_filter_table_cache_can_be_dropped_at_any_time(monkeypatch):
         for a, (st, out, r) in zip(raws, ctx(C1).process(raws)):
             assert_same(out, oracle.crop_and_resize(C1, a)[0], f"cached {a.shape}")
     small.close()
+
+
+def test_both_horizontal_kernels_agree_with_the_oracle():
+    # horizontal passes run on the tensor-core kernel where their geometry fits; DATAGO_B200_HMMA=0 keeps every pass on
+    # the dp2a kernel.  Both must give the oracle's bytes: a mix of scales (up, slightly down, 8x down), channel counts,
+    # odd widths, and a pass too wide for the tensor-core path (downscale beyond 10x) in the same batch.
+    import os
+    rng = np.random.default_rng(26)
+    sizes = [(640, 480, 3), (4096, 4096, 3), (3000, 777, 3), (513, 1025, 1), (300, 200, 3), (4001, 1999, 1), (1201, 900, 3)]
+    raws = [rng.integers(0, 256, (h, w, c) if c == 3 else (h, w), dtype=np.uint8) for (w, h, c) in sizes]
+    wide = rng.integers(0, 256, (700, 9000, 3), dtype=np.uint8)   # 9000 -> 720: 12.5x, beyond what a CTA can stage
+    raws.append(wide)
+    wants = [oracle.crop_and_resize(C1, a)[0] for a in raws]
+    old = os.environ.get("DATAGO_B200_HMMA")
+    try:
+        for flag in ("1", "0"):
+            os.environ["DATAGO_B200_HMMA"] = flag
+            c = dg.Context(0, C1)
+            try:
+                for i, (st, out, _) in enumerate(c.process(raws)):
+                    assert st == 0
+                    assert_same(out, wants[i], f"HMMA={flag} item {i} {raws[i].shape}")
+            finally:
+                c.close()
+    finally:
+        if old is None:
+            os.environ.pop("DATAGO_B200_HMMA", None)
+        else:
+            os.environ["DATAGO_B200_HMMA"] = old
