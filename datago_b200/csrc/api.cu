@@ -138,6 +138,7 @@ struct dg_ctx {
     // Horizontal resize passes run on the tensor cores where their geometry fits; DATAGO_B200_HMMA=0 keeps them on the
     // dp2a kernel (measurements, and the test-suite's coverage of that kernel).
     bool hmma = true;
+    unsigned int conv_timeouts_seen = 0;
     // Largest decoded image accepted (width * height * channels bytes); the `image` crate's default allocation limit is 512 MiB.
     uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
@@ -396,6 +397,7 @@ struct dg_batch {
     uint64_t h2d = 0, d2h = 0;
     uint32_t launches = 0;
     bool uploaded = false, ran = false;
+    bool used_hmma = false;  // a pass of this batch ran on the tensor-core resize kernel, whose waits are bounded
     std::vector<StageEvent> events;
     float stage_ms[DG_STAGE_COUNT] = {0};
 };
@@ -1318,7 +1320,7 @@ static int batch_run_locked(dg_batch* b) {
                 CU(mark(kStageOf[st], true));
                 const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
                 if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
-                else launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s);
+                else { launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s); b->used_hmma = b->used_hmma || wv.mma_tiles[st] != 0; }
                 ++b->launches;
                 CU(mark(kStageOf[st], false));
             }
@@ -1391,6 +1393,14 @@ extern "C" int dg_batch_sync(dg_batch* b) {
         b->d2h += (size_t)b->n * 4;
     }
     CU(cudaStreamSynchronize(ctx->stream));
+    if (b->ran && b->used_hmma) {
+        // the tensor-core resize pass bounds its waits for asynchronous copies; a wait that ran out left garbage behind
+        const unsigned int t = read_conv_timeouts(ctx->stream);
+        if (t != ctx->conv_timeouts_seen) {
+            ctx->conv_timeouts_seen = t;
+            return fail(DG_E_CUDA, "resize: a copy into shared memory did not complete in time (%u CTAs gave up); the batch's pixels are not valid", t);
+        }
+    }
     if (b->ran) {
         for (int i = 0; i < b->n; ++i)
             if (b->items[i].status == DG_OK && b->h_status[i]) b->items[i].status = device_status_to_code(b->h_status[i]);

@@ -95,6 +95,8 @@ constexpr uint32_t kCopyTileBytes = 4096;
 
 // the passes that take the tensor-core kernel (fast == 2) come first in `passes` and own tiles [0, mma_tiles)
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s);
+// CTAs of the tensor-core horizontal pass that ran out of patience waiting for a copy since the library was loaded
+unsigned int read_conv_timeouts(cudaStream_t s);
 void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
 void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s);
 constexpr uint32_t kToRgbTilePx = 2048;  // pixels per CTA of the RGB8 conversion

@@ -143,27 +143,28 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
 // byte, w = 256 hi + lo, so that the product runs on the 8-bit integer tensor-core path with 32-bit accumulation:
 // out = 256 (src x hi) + (src x lo), which is exact -- the result equals the dp2a kernel's bit for bit.
 //   CTA  = one strip of 64 output bytes x up to 512 rows of one pass; warp q owns output bytes 8q .. 8q+7 of the strip.
-//   B    = the warp's slice of Wt (source bytes under its eight outputs, at most 256), both limbs, built once per CTA in
-//          shared memory from the filter table and read as mma.m16n8k32 fragments;
+//   B    = the warp's slice of Wt (source bytes under its eight outputs, at most 256), both limbs: every lane gathers its
+//          mma.m16n8k32 fragments from the filter table once and keeps them in registers for all rows of the CTA;
 //   A    = 32 source rows of the strip's band per chunk, brought in by 16-byte asynchronous copies into a ring of up to
 //          four chunks (the planner only sends passes here whose source rows start on 16-byte boundaries), so the copies
 //          of the next chunks are in flight while a chunk is multiplied; read with ldmatrix;
-//   D    = two 16-row tiles per warp and chunk; merged, rounded, clamped, collected in shared memory and written out
-//          as 16-byte pieces.
+//   D    = two 16-row tiles per warp and chunk; merged, rounded, saturated, turned by 90 degrees through the warp's own
+//          piece of shared memory and written out as eight bytes per row.  Warps never wait for each other: the only
+//          synchronisation in the loop is the pair of barriers of each ring slot.
 // The interleaved channel layout costs two thirds of the multiplies (zeros in Wt), which the tensor cores have to
 // spare; in exchange the source needs no de-interleaving and the result is produced in its final byte order.
-constexpr int kHMmaThreads = 256;
-constexpr int kHMmaPitchB = (int)kHMmaMaxBand + 16;  // per output byte; + 16 spreads the eight rows of a fragment over the banks
+constexpr int kHMmaConsumers = 256;   // eight warps multiply
+constexpr int kHMmaProducers = 64;    // two warps only move source rows into the ring
+constexpr int kHMmaThreads = kHMmaConsumers + kHMmaProducers;
 constexpr int kHMmaChunk = 32;                       // rows per chunk (two mma row tiles)
-constexpr int kHMmaRing = 45056;                     // bytes of the A ring: three chunks at a 4.5x reduction, one at the widest band
-constexpr int kHMmaOutPitch = (int)kHMmaStrip + 16;
+constexpr int kHMmaRing = 98304;                     // bytes of the A ring: two CTAs per SM keep ~190 KB of source rows in flight
+constexpr int kHMmaMaxStages = 8;
 
 struct HMmaSmem {
-    uint8_t B[kHMmaThreads / 32][2][8][kHMmaPitchB];
-    uint8_t out[kHMmaChunk][kHMmaOutPitch];
+    uint8_t out[kHMmaConsumers / 32][kHMmaChunk][8];  // per warp: the eight output bytes of a chunk's rows, before they go out row by row
     uint8_t A[kHMmaRing];
 };
-static_assert(kHMmaChunk * ((int)kHMmaMaxSpan + 32) <= kHMmaRing, "the ring must hold one chunk of the widest band");
+static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 32) <= kHMmaRing, "the ring must hold two chunks of the widest band");
 
 __device__ __forceinline__ void mma_u8s8(int32_t (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -174,143 +175,203 @@ __device__ __forceinline__ void mma_u8u8(int32_t (&d)[4], const uint32_t (&a)[4]
                  : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables) {
+// mbarrier helpers: one barrier per ring slot counts the bytes of the bulk copies into it
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// one row of a chunk: `bytes` (a multiple of 16) from 16-byte aligned global memory to 16-byte aligned shared memory
+__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+constexpr uint32_t kHMmaWaitLimit = 1u << 22;  // polls of a ring slot's barrier before a CTA gives up on it
+
+__global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
+                                                                unsigned int* timeouts) {
     extern __shared__ __align__(16) unsigned char conv_h_smem[];
     HMmaSmem& sm = *reinterpret_cast<HMmaSmem*>(conv_h_smem);
-    const ConvPass& p = passes[owner_of_tile(map, blockIdx.x)];
-    const uint32_t tile = blockIdx.x - p.tile_first;
-    const uint32_t ty = tile / p.tiles_x, tx = tile - ty * p.tiles_x;
-    const Table tb = table_of(p, tables);
+    __shared__ __align__(8) unsigned long long s_bar[2 * kHMmaMaxStages];  // per ring slot: "filled" (bytes arrived) and "drained" (all warps done reading)
+    const ConvPass& pg = passes[owner_of_tile(map, blockIdx.x)];
+    // everything the loops need from the descriptor, once (the asynchronous-copy statements below are memory barriers
+    // for the compiler, which would otherwise fetch these fields again after each of them)
+    const uint8_t* const p_src = pg.src;
+    uint8_t* const p_dst = pg.dst;
+    const uint32_t src_pitch = pg.src_pitch, dst_pitch = pg.dst_pitch, out_w = pg.out_w, out_h = pg.out_h, C = pg.channels;
+    const uint32_t t0 = pg.t0, tab_n = pg.tab_n, precision = pg.precision, tiles_x = pg.tiles_x;
+    const int32_t origin = pg.src_origin;
+    const uint32_t tile = blockIdx.x - pg.tile_first;
+    const Table tb = table_of(pg, tables);
+    const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t C = p.channels, row_bytes = p.out_w * C;
+    const uint32_t row_bytes = out_w * C;
     const uint32_t j0 = tx * kHMmaStrip;                          // first output byte of the strip
     const uint32_t jn0 = j0 + warp * 8;                           // ... of this warp's tile
-    const uint32_t y_first = ty * kHMmaRows, y_end = min(p.out_h, y_first + kHMmaRows);
+    const uint32_t y_first = ty * kHMmaRows, y_end = min(out_h, y_first + kHMmaRows);
     // source byte range of the strip, in bytes from the start of a source row of the pass
-    const uint32_t xs0 = j0 / C, xs1 = min(p.out_w - 1, (j0 + kHMmaStrip - 1) / C);
-    const int32_t strip_lo = ((__ldg(tb.start + p.t0 + xs0) - p.src_origin) * (int32_t)C) & ~15;
-    const int32_t strip_hi = (__ldg(tb.start + p.t0 + xs1) + __ldg(tb.size + p.t0 + xs1) - p.src_origin) * (int32_t)C;
+    const uint32_t xs0 = j0 / C, xs1 = min(out_w - 1, (j0 + kHMmaStrip - 1) / C);
+    const int32_t strip_lo = ((__ldg(tb.start + t0 + xs0) - origin) * (int32_t)C) & ~15;
+    const int32_t strip_hi = (__ldg(tb.start + t0 + xs1) + __ldg(tb.size + t0 + xs1) - origin) * (int32_t)C;
     const uint32_t span16 = (uint32_t)(strip_hi - strip_lo + 15) >> 4;   // 16-byte pieces per staged row
     const uint32_t pitch_a = (span16 | 1u) * 16;                         // an odd number of pieces: ldmatrix rows hit different banks
     const uint32_t stage_bytes = kHMmaChunk * pitch_a;
-    const uint32_t nstage = min(4u, (uint32_t)kHMmaRing / stage_bytes);  // >= 1 by the planner's span limit
-    // ... and of this warp's eight output bytes (a warp past the end of the row only helps with the copies)
+    const uint32_t nstage = min((uint32_t)kHMmaMaxStages, (uint32_t)kHMmaRing / stage_bytes);  // >= 2 by the planner's span limit
+    // ... and of this warp's eight output bytes (a warp past the end of the row has no tile)
     const bool warp_active = jn0 < row_bytes;
     int32_t band_lo = strip_lo;
     uint32_t ksteps = 0;
     if (warp_active) {
-        const uint32_t xw0 = jn0 / C, xw1 = min(p.out_w - 1, (jn0 + 7) / C);
-        band_lo = ((__ldg(tb.start + p.t0 + xw0) - p.src_origin) * (int32_t)C) & ~15;
-        const int32_t band_hi = (__ldg(tb.start + p.t0 + xw1) + __ldg(tb.size + p.t0 + xw1) - p.src_origin) * (int32_t)C;
+        const uint32_t xw0 = jn0 / C, xw1 = min(out_w - 1, (jn0 + 7) / C);
+        band_lo = ((__ldg(tb.start + t0 + xw0) - origin) * (int32_t)C) & ~15;
+        const int32_t band_hi = (__ldg(tb.start + t0 + xw1) + __ldg(tb.size + t0 + xw1) - origin) * (int32_t)C;
         ksteps = (uint32_t)(band_hi - band_lo + 31) >> 5;
     }
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&s_bar[0]);
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < (uint32_t)kHMmaMaxStages; ++i) { mbar_init(bar0 + 8 * i, kHMmaProducers); mbar_init(bar0 + 8 * (kHMmaMaxStages + i), kHMmaConsumers / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
 
-    // queues the copies of chunk c (rows y_first + 32 c ...) into its ring slot; one commit group per call and thread
+    // Ring protocol.  Chunk c (rows y_first + 32 c ...) lives in slot c % nstage.  The two producer warps fill a slot
+    // with 16-byte asynchronous copies and let the slot's "filled" barrier count them in (one deferred arrival per
+    // producer thread); a consumer warp waits for "filled", multiplies, and arrives on the slot's "drained" barrier,
+    // which the producers wait for before they fill the slot again.  Every wait is bounded: a CTA that runs out of
+    // patience counts a timeout (reported by the host) instead of hanging the GPU.
     const uint32_t nchunks = (y_end - y_first + kHMmaChunk - 1) / kHMmaChunk;
-    auto queue_chunk = [&](uint32_t c) {
-        if (c < nchunks) {
-            uint8_t* slot = sm.A + (c % nstage) * stage_bytes;
-#pragma unroll 1
-            for (uint32_t r = warp; r < (uint32_t)kHMmaChunk; r += kHMmaThreads / 32) {
-                const uint32_t y = min(y_first + c * kHMmaChunk + r, p.out_h - 1);  // rows past the end repeat the last one
-                const uint8_t* src = p.src + (size_t)y * p.src_pitch + strip_lo;
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slot + r * pitch_a);
-                for (uint32_t v = lane; v < span16; v += 32)
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + v * 16), "l"(src + v * 16) : "memory");
-            }
+    const uint32_t a_base = (uint32_t)__cvta_generic_to_shared(sm.A);
+    bool gave_up = false;
+    auto wait_for = [&](uint32_t bar, uint32_t parity) {
+        uint32_t polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kHMmaWaitLimit) { gave_up = true; break; }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    for (uint32_t c = 0; c + 1 < nstage; ++c) queue_chunk(c);
+    if (warp >= kHMmaConsumers / 32) {
+        // ---- producers: thread q of 64 copies pieces q % 2, q % 2 + 2, ... of row q / 2 of every chunk
+        const uint32_t q = threadIdx.x - kHMmaConsumers, r = q >> 1;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t slot = c % nstage, use = c / nstage;
+            if (use > 0) wait_for(bar0 + 8 * (kHMmaMaxStages + slot), (use - 1) & 1u);
+            const uint32_t y = min(y_first + c * kHMmaChunk + r, out_h - 1);  // rows past the end repeat the last one
+            const uint8_t* src = p_src + (size_t)y * src_pitch + strip_lo;
+            const uint32_t dst = a_base + slot * stage_bytes + r * pitch_a;
+            for (uint32_t v = q & 1u; v < span16; v += 2)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + v * 16), "l"(src + v * 16) : "memory");
+            // the barrier counts this thread in once the copies it has issued so far have landed
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * slot) : "memory");
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
+        return;
+    }
 
-    // ---- B: zero, then scatter the weights of the warp's eight output bytes; lane l fills output byte l / 4, taps l % 4, + 4, ...
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    const int32_t half = 1 << (precision - 1);
+    const bool dst8 = ((reinterpret_cast<uintptr_t>(p_dst) | dst_pitch) & 7u) == 0;
+    // ldmatrix: lanes 0-7 give the rows of tile rows 0-7 at k, lanes 8-15 rows 8-15 at k, 16-23 rows 0-7 at k + 16, ...
+    const uint32_t a_lane = ((lane & 7u) + ((lane >> 3) & 1u) * 8) * pitch_a + (uint32_t)(band_lo - strip_lo) + (lane >> 4) * 16;
+    // ---- B fragments, gathered straight from the filter table and kept in registers for all chunks.  A lane holds, for
+    //      output byte g of the warp's tile and k step ks, source bytes 32 ks + 4 t .. + 3 and + 16 .. + 19 of the band;
+    //      source byte kk carries tap (kk - first) / C of that output when that is a whole number inside the window.
+    uint32_t bfr[8][4];
     {
-        uint4* z = reinterpret_cast<uint4*>(&sm.B[warp][0][0][0]);
-        for (uint32_t i = lane; i < sizeof(sm.B[0]) / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
-        __syncwarp();
-        const uint32_t n = lane >> 2, j = jn0 + n;
-        if (j < row_bytes) {
-            const uint32_t x = j / C, c = j - x * C;
-            const int32_t first = (__ldg(tb.start + p.t0 + x) - p.src_origin) * (int32_t)C + (int32_t)c - band_lo;
-            const int32_t taps = __ldg(tb.size + p.t0 + x);
-            const int16_t* k = tb.k + p.t0 + x;
-#pragma unroll 4
-            for (int32_t i = (int32_t)(lane & 3u); i < taps; i += 4) {
-                const int32_t wv = __ldg(k + (size_t)i * p.tab_n);
-                const uint32_t at = (uint32_t)(first + i * (int32_t)C);
-                sm.B[warp][0][n][at] = (uint8_t)(wv >> 8);    // signed high byte
-                sm.B[warp][1][n][at] = (uint8_t)(wv & 255);   // unsigned low byte
+        const uint32_t j = jn0 + g;
+        const bool live = warp_active && j < row_bytes;
+        const uint32_t x = live ? j / C : 0, ch = j - x * C;
+        const int32_t first = live ? (__ldg(tb.start + t0 + x) - origin) * (int32_t)C + (int32_t)ch - band_lo : 0;
+        const int32_t taps = live ? __ldg(tb.size + t0 + x) : 0;
+        const int16_t* k = tb.k + t0 + x;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
+            if ((uint32_t)ks < ksteps) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int32_t d = 32 * ks + 16 * hf + 4 * (int32_t)t4 + e - first;
+                        const int32_t i = C == 3 ? d / 3 : d;
+                        if (d >= 0 && i < taps && i * (int32_t)C == d) {
+                            const int32_t wv = __ldg(k + (size_t)i * tab_n);
+                            hi[hf] |= ((uint32_t)(wv >> 8) & 255u) << (8 * e);   // signed high byte
+                            lo[hf] |= ((uint32_t)wv & 255u) << (8 * e);          // unsigned low byte
+                        }
+                    }
             }
+            bfr[ks][0] = hi[0]; bfr[ks][1] = hi[1]; bfr[ks][2] = lo[0]; bfr[ks][3] = lo[1];
         }
     }
-    const uint32_t g = lane >> 2, t4 = lane & 3u;
-    const int32_t half = 1 << (p.precision - 1);
-    const bool dst16 = ((reinterpret_cast<uintptr_t>(p.dst) | p.dst_pitch) & 15u) == 0;
-    const uint32_t a_off = (uint32_t)(band_lo - strip_lo);
-    // ldmatrix: lanes 0-7 give the rows of tile rows 0-7 at k, lanes 8-15 rows 8-15 at k, 16-23 rows 0-7 at k + 16, ...
-    const uint32_t a_lane = ((lane & 7u) + ((lane >> 3) & 1u) * 8) * pitch_a + a_off + (lane >> 4) * 16;
-    const uint8_t* bh = &sm.B[warp][0][g][4 * t4];
-    const uint8_t* bl = &sm.B[warp][1][g][4 * t4];
-
     for (uint32_t c = 0; c < nchunks; ++c) {
-        queue_chunk(c + nstage - 1);  // into the slot the previous iteration finished with
-        if (nstage == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
-        else if (nstage == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-        else if (nstage == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();  // chunk c has landed for every thread (first pass: B is complete as well)
+        const uint32_t slot = c % nstage;
+        wait_for(bar0 + 8 * slot, (c / nstage) & 1u);  // chunk c is the (c / nstage)-th filling of its slot
+        int32_t acc_hi[2][4], acc_lo[2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { acc_hi[mt][i] = 0; acc_lo[mt][i] = half; }
         if (warp_active) {
-            int32_t acc_hi[2][4], acc_lo[2][4];
+            const uint32_t a_addr = a_base + slot * stage_bytes + a_lane;
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt)
+            for (int ks = 0; ks < 8; ++ks) {
+                if ((uint32_t)ks < ksteps) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { acc_hi[mt][i] = 0; acc_lo[mt][i] = half; }
-            const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sm.A + (c % nstage) * stage_bytes) + a_lane;
-#pragma unroll 1
-            for (uint32_t ks = 0; ks < ksteps; ++ks) {
-                const uint32_t bh0 = *reinterpret_cast<const uint32_t*>(bh + ks * 32), bh1 = *reinterpret_cast<const uint32_t*>(bh + ks * 32 + 16);
-                const uint32_t bl0 = *reinterpret_cast<const uint32_t*>(bl + ks * 32), bl1 = *reinterpret_cast<const uint32_t*>(bl + ks * 32 + 16);
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    uint32_t a[4];
-                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(a_addr + (uint32_t)mt * 16 * pitch_a + ks * 32));
-                    mma_u8s8(acc_hi[mt], a, bh0, bh1);
-                    mma_u8u8(acc_lo[mt], a, bl0, bl1);
+                    for (int mt = 0; mt < 2; ++mt) {
+                        uint32_t a[4];
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(a_addr + (uint32_t)mt * 16 * pitch_a + ks * 32));
+                        mma_u8s8(acc_hi[mt], a, bfr[ks][0], bfr[ks][1]);
+                        mma_u8u8(acc_lo[mt], a, bfr[ks][2], bfr[ks][3]);
+                    }
                 }
             }
-            // ---- merge the limbs, round, clamp; accumulator i of a tile is row g + 8 (i / 2), output byte 2 t + i % 2
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kHMmaMaxStages + slot));  // this warp is done with the slot
+        if (warp_active) {
+            // ---- merge the limbs, round, saturate; accumulator i of a tile is row g + 8 (i / 2), output byte 2 t + i % 2.
+            //      The warp's 32 x 8 bytes pass through its own piece of shared memory, so that a lane can write out the
+            //      eight bytes of one row.
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint32_t v0 = clip8(acc_hi[mt][2 * h] * 256 + acc_lo[mt][2 * h], p.precision);
-                    const uint32_t v1 = clip8(acc_hi[mt][2 * h + 1] * 256 + acc_lo[mt][2 * h + 1], p.precision);
-                    *reinterpret_cast<uint16_t*>(&sm.out[mt * 16 + g + 8 * h][warp * 8 + 2 * t4]) = (uint16_t)(v0 | (v1 << 8));
+                    const int32_t v0 = (acc_hi[mt][2 * h] * 256 + acc_lo[mt][2 * h]) >> precision;
+                    const int32_t v1 = (acc_hi[mt][2 * h + 1] * 256 + acc_lo[mt][2 * h + 1]) >> precision;
+                    uint32_t pk;
+                    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(pk) : "r"(v1), "r"(v0), "r"(0));
+                    *reinterpret_cast<uint16_t*>(&sm.out[warp][mt * 16 + g + 8 * h][2 * t4]) = (uint16_t)pk;
                 }
-        }
-        __syncthreads();  // the out tile is complete; slot c % nstage is free for the copies the next iteration queues
-        // ---- write the chunk out: thread i takes 16 bytes of row i / 4
-        if (threadIdx.x < kHMmaChunk * (kHMmaStrip / 16)) {
-            const uint32_t r = threadIdx.x >> 2, qd = threadIdx.x & 3u, y = y_first + c * kHMmaChunk + r, jb = j0 + qd * 16;
-            if (y < y_end && jb < row_bytes) {
-                uint8_t* o = p.dst + (size_t)y * p.dst_pitch + jb;
-                const uint4 v = *reinterpret_cast<const uint4*>(&sm.out[r][qd * 16]);
-                if (dst16 && jb + 16 <= row_bytes) {
-                    *reinterpret_cast<uint4*>(o) = v;
+            __syncwarp();
+            const uint32_t y = y_first + c * kHMmaChunk + lane;
+            if (y < y_end) {
+                const uint2 v = *reinterpret_cast<const uint2*>(&sm.out[warp][lane][0]);
+                uint8_t* o = p_dst + (size_t)y * dst_pitch + jn0;
+                if (dst8 && jn0 + 8 <= row_bytes) {
+                    *reinterpret_cast<uint2*>(o) = v;
                 } else {
-                    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
-                    const uint32_t nb = min(16u, row_bytes - jb);
+                    const uint32_t nb = min(8u, row_bytes - jn0);
 #pragma unroll
-                    for (int wi = 0; wi < 4; ++wi)
-#pragma unroll
-                        for (int kb = 0; kb < 4; ++kb)
-                            if ((uint32_t)(wi * 4 + kb) < nb) o[wi * 4 + kb] = (uint8_t)(vw[wi] >> (8 * kb));
+                    for (int kb = 0; kb < 8; ++kb)
+                        if ((uint32_t)kb < nb) o[kb] = (uint8_t)((kb < 4 ? v.x : v.y) >> (8 * (kb & 3)));
                 }
             }
+            __syncwarp();  // the warp's piece of shared memory is rewritten by the next chunk
         }
-        // the out tile is rewritten only after the next iteration's first barrier
     }
+    if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
 }
 
 __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t first_tile) {
@@ -329,6 +390,24 @@ __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes
     else conv_h_rows<1, false>(p, tb, x, y0);
 }
 
+// Counts CTAs of the tensor-core pass that gave up waiting for a copy (never expected; the counter exists so that a wait
+// can be bounded without the failure going unnoticed).  One counter per device.
+static __device__ unsigned int g_conv_timeouts;
+static unsigned int* conv_timeouts() {
+    static unsigned int* ptr[64] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!ptr[dev]) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr[dev]), g_conv_timeouts);
+    return ptr[dev];
+}
+unsigned int read_conv_timeouts(cudaStream_t s) {
+    unsigned int v = 0;
+    cudaMemcpyFromSymbolAsync(&v, g_conv_timeouts, sizeof v, 0, cudaMemcpyDeviceToHost, s);
+    cudaStreamSynchronize(s);
+    return v;
+}
+
 // Horizontal passes of one stage: the tensor-core passes come first in `passes` and own tiles [0, mma_tiles) of the map,
 // the others the rest.
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s) {
@@ -342,7 +421,7 @@ void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
             cudaFuncSetAttribute(k_conv_h_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(HMmaSmem));
             configured[dev] = true;
         }
-        k_conv_h_mma<<<mma_tiles, kHMmaThreads, sizeof(HMmaSmem), s>>>(passes, map, tables);
+        k_conv_h_mma<<<mma_tiles, kHMmaThreads, sizeof(HMmaSmem), s>>>(passes, map, tables, conv_timeouts());
     }
     if (map.total > mma_tiles) k_conv_h<<<map.total - mma_tiles, kConvHThreads, 0, s>>>(passes, map, tables, mma_tiles);
 }
