@@ -392,6 +392,7 @@ struct dg_batch {
     size_t off_meta = 0, off_status = 0, off_blob = 0, off_rawin = 0, off_out = 0, persist_bytes = 0;
     size_t blob_bytes = 0, rawin_bytes = 0, out_bytes = 0, pin_bytes = 0;
     size_t arena_bytes = 0;  // out_bytes plus the pre-conversion images of DG_ITEM_TO_RGB8 items (never downloaded)
+    uint32_t n_huff = 0;
     size_t m_huff = 0, m_qt = 0, m_tables = 0, meta_total = 0;  // meta_total: meta.bytes plus the filter tables behind it
     std::vector<const uint8_t*> raw_src;  // caller memory of raw items (used inside dg_batch_create only)
     uint64_t h2d = 0, d2h = 0;
@@ -1042,6 +1043,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         Meta& m = b->meta;
         m.bytes.clear();
         b->m_huff = m.put(pl.huff_pool, 16);
+        b->n_huff = (uint32_t)pl.huff_pool.size();
         b->m_qt = m.put(pl.qt_pool, 16);
         for (WavePlan& wv : b->waves) {
             wv.m_descs = m.put(wv.descs, 16);
@@ -1242,6 +1244,7 @@ static int batch_run_locked(dg_batch* b) {
             w.status = (uint32_t*)(b->d_persist + b->off_status);
             w.spec_stats = (unsigned long long*)(b->d_persist + b->off_status + align_up((size_t)b->n * 4, 8));
             w.huff = (const HuffTable*)(meta + b->m_huff);
+            w.n_huff = b->n_huff;
             w.qt32 = (const uint32_t*)(meta + b->m_qt);
             w.spec_list = (const uint32_t*)(meta + wv.m_spec);
             w.n_spec = (uint32_t)wv.spec_list.size();

@@ -17,9 +17,14 @@ constexpr uint32_t huff_pack(uint32_t len, uint32_t sym) {
 }
 
 // One Huffman table (DC or AC) prepared for the device (T.81 Annex C code assignment).
-struct HuffTable {
+struct alignas(16) HuffTable {
     // next 9 bits -> packed symbol (see huff_pack), 0 = the code is longer than 9 bits
     uint32_t lut[1 << kLutBits];
+    // Codes longer than the fast table, without a search: limit[i] is the smallest 16-bit window (code bits left-aligned)
+    // that does not start with a code of at most 10 + i bits, i = 0..6; canonical codes grow with their length, so the
+    // length of the code at the head of window v is 10 + the number of i < 6 with v >= limit[i], and v >= limit[6]
+    // means that no code matches.  limit[7] is unused.  (16-byte aligned: read as two vectors.)
+    uint32_t limit[8];
     int32_t maxcode[18];          // [l], l = 1..16: largest code of length l, -1 if none; [17] = INT_MAX
     int32_t valoff[17];           // [l]: index of the first symbol of length l minus its first code
     uint8_t vals[256];

@@ -180,6 +180,13 @@ bool build_huff_table(const JpegHeader::RawHuff& raw, HuffTable& out) {
         code <<= 1;
     }
     out.maxcode[17] = INT_MAX;
+    // left-aligned end of the code space used by lengths <= l (the first code of the next length, shifted to 16 bits)
+    uint32_t used = 0;  // in units of 2^-16 of the code space
+    for (int l = 1; l <= 16; ++l) {
+        used += (uint32_t)raw.bits[l] << (16 - l);
+        if (l >= 10) out.limit[l - 10] = used;
+    }
+    out.limit[7] = 0xFFFFFFFFu;
     return true;
 }
 

@@ -28,6 +28,7 @@ struct JpegWave {
     uint32_t* status;        // [items of the batch]
     unsigned long long* spec_stats;  // [0] chunks, [1] synchronisation rounds, [2] subsequence decodes (all passes)
     const HuffTable* huff;   // table pool
+    uint32_t n_huff;         // tables in the pool
     const uint32_t* qt32;    // quantisation pool, 32 words per table: word i holds q[2i] in byte 0 and q[2i+1] in byte 3
     // speculative (no restart marker) images and restart-interval images of this wave
     const uint32_t* spec_list; uint32_t n_spec;
@@ -80,7 +81,7 @@ constexpr uint32_t kVFastBytes = 1024, kVFastRows = 32; // vertical pass, vector
 constexpr uint32_t kVFastMaxWindow = 128;
 // horizontal pass on the tensor cores (ConvPass::fast == 2): output bytes per strip x rows per CTA; limits of what a CTA
 // can stage -- source bytes under one 8-byte output tile, and under a whole strip
-constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 512, kHMmaMaxBand = 256, kHMmaMaxSpan = 1024;
+constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 2048, kHMmaMaxBand = 256, kHMmaMaxSpan = 1024;
 inline uint32_t conv_tiles_x(const ConvPass& p, bool vertical) {
     if (!vertical && p.fast == 2) return (p.out_w * p.channels + kHMmaStrip - 1) / kHMmaStrip;
     if (!vertical) return (p.out_w + kConvTileW - 1) / kConvTileW;

@@ -144,13 +144,18 @@ __device__ __forceinline__ uint32_t shr_clamp(uint32_t x, uint32_t n) {  // shif
     return r;
 }
 
-// codes longer than the fast table: canonical search over the remaining lengths
+// Codes longer than the fast table.  No search: the code length follows from six comparisons against the table's
+// left-aligned limits (see HuffTable::limit), the symbol from the canonical offset of that length.  The lanes of a
+// warp sit at unrelated places of their streams, so whenever one of them meets a long code all of them pay for this
+// path: it has to be short.
 template <bool WRITE>
-__device__ __noinline__ uint32_t huff_long_code(const HuffTable* t, uint32_t top, uint32_t& err) {
-    uint32_t len = kLutBits + 1;
-    while (len <= 16 && (int32_t)(top >> (32 - len)) > t->maxcode[len]) ++len;
-    if (len > 16) { if (WRITE) err |= kStBadCode; return huff_pack(16, 0); }
-    return huff_pack(len, t->vals[(int32_t)(top >> (32 - len)) + t->valoff[len]]);
+__device__ __forceinline__ uint32_t huff_long_code(const HuffTable* t, uint32_t top, uint32_t& err) {
+    const uint32_t v = top >> 16;
+    const uint4 la = *reinterpret_cast<const uint4*>(&t->limit[0]);
+    const uint4 lb = *reinterpret_cast<const uint4*>(&t->limit[4]);
+    const uint32_t len = 10u + (v >= la.x) + (v >= la.y) + (v >= la.z) + (v >= la.w) + (v >= lb.x) + (v >= lb.y);
+    if (v >= lb.z) { if (WRITE) err |= kStBadCode; return huff_pack(16, 0); }
+    return huff_pack(len, t->vals[(int32_t)(v >> (16u - len)) + t->valoff[len]]);
 }
 
 // Decodes the symbols that start in [p, end_bit) while fewer than max_slots slots have been consumed.
@@ -206,10 +211,22 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
 
 // ---- restart-interval images: one thread per segment -----------------------------------------------------------
 constexpr int kRestartThreads = 128;
+constexpr uint32_t kRestartSharedTables = 8;  // a pool of at most this many Huffman tables is staged in shared memory
 
 __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
     __shared__ uint8_t s_nat[64];
+    __shared__ __align__(16) HuffTable s_tab[kRestartSharedTables];
     if (threadIdx.x < 64) s_nat[threadIdx.x] = kNatural[threadIdx.x];
+    // The segments of a CTA belong to several images, but files written by the same encoder share their tables and the
+    // pool holds each distinct table once: a small pool is copied whole, so that the per-symbol table look-ups (on the
+    // critical path of every lane) are shared-memory reads; a larger pool is read in place.
+    const bool staged = w.n_huff <= kRestartSharedTables;
+    if (staged) {
+        const uint32_t words = w.n_huff * (uint32_t)(sizeof(HuffTable) / 4);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(w.huff);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(&s_tab[0]);
+        for (uint32_t i = threadIdx.x; i < words; i += kRestartThreads) dst[i] = __ldg(src + i);
+    }
     __syncthreads();
     const uint32_t g = blockIdx.x * kRestartThreads + threadIdx.x;
     if (g >= w.restart_segs.total) return;
@@ -226,7 +243,7 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
     const uint32_t mcus = d.mcux * d.mcuy;
     const uint32_t m0 = k * d.restart, m1 = min(m0 + d.restart, mcus);
     HuffCtx hc;
-    hc.base = reinterpret_cast<const char*>(w.huff);
+    hc.base = staged ? reinterpret_cast<const char*>(&s_tab[0]) : reinterpret_cast<const char*>(w.huff);
     hc.dc_off0 = d.dc_tab[0] * (uint32_t)sizeof(HuffTable); hc.ac_off0 = d.ac_tab[0] * (uint32_t)sizeof(HuffTable);
     hc.dc_off1 = d.dc_tab[1] * (uint32_t)sizeof(HuffTable); hc.ac_off1 = d.ac_tab[1] * (uint32_t)sizeof(HuffTable);
     hc.dc_off2 = d.dc_tab[2] * (uint32_t)sizeof(HuffTable); hc.ac_off2 = d.ac_tab[2] * (uint32_t)sizeof(HuffTable);
@@ -269,7 +286,13 @@ struct SpecState {
     uint32_t n[T];                     // slots consumed
     int32_t dc[3][T];                  // sums of DC differences per component
     uint32_t list[T];                  // subsequences to re-decode this round
+    // The same after the first symbol that ends kSyncCheckBits or more into the subsequence: a re-decode from a
+    // corrected entry state that arrives here in the state its predecessor had here has synchronised with it, and
+    // the rest of the subsequence need not be decoded again.
+    uint32_t ck_p[T], ck_sm[T], ck_n[T];
+    int32_t ck_dc[3][T];
 };
+constexpr uint32_t kSyncCheckBits = 256;
 
 template <int T, int MIN_CTAS>
 __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
@@ -277,7 +300,7 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
     const JpegDesc& d = w.descs[img];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    __shared__ HuffTable s_tab[6];
+    __shared__ __align__(16) HuffTable s_tab[6];
     __shared__ uint8_t s_nat[64];
     __shared__ SpecState<T> st;
     __shared__ Scan4 s_warp[T / 32];
@@ -314,10 +337,24 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
     uint32_t err = 0;
 
     // decode subsequence j of the chunk from its recorded entry state and record exit state and sums
-    auto decode_into_state = [&](uint32_t chunk, int j) {
+    auto decode_into_state = [&](uint32_t chunk, int j, bool first_time) {
         uint32_t p = st.entry_p[j], sm = st.entry_sm[j], n = 0, dummy = 0;
         int32_t a = 0, b = 0, c = 0;
         const uint32_t end_bit = min((chunk + j + 1) * kSubseqBits, total_bits);
+        const uint32_t check_bit = min((chunk + j) * kSubseqBits + kSyncCheckBits, end_bit);
+        decode_span<false>(words, nwords, p, check_bit, total_bits, sm, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, s_nat, dummy);
+        if (!first_time && p == st.ck_p[j] && sm == st.ck_sm[j]) {
+            // synchronised: from here on the previous decode of this subsequence stands; only the part before the
+            // check point contributes differently to the slot count and the DC sums
+            st.n[j] = n + (st.n[j] - st.ck_n[j]);
+            st.dc[0][j] = a + (st.dc[0][j] - st.ck_dc[0][j]);
+            st.dc[1][j] = b + (st.dc[1][j] - st.ck_dc[1][j]);
+            st.dc[2][j] = c + (st.dc[2][j] - st.ck_dc[2][j]);
+            st.ck_n[j] = n; st.ck_dc[0][j] = a; st.ck_dc[1][j] = b; st.ck_dc[2][j] = c;
+            return;
+        }
+        st.ck_p[j] = p; st.ck_sm[j] = sm; st.ck_n[j] = n;
+        st.ck_dc[0][j] = a; st.ck_dc[1][j] = b; st.ck_dc[2][j] = c;
         decode_span<false>(words, nwords, p, end_bit, total_bits, sm, n, 0xFFFFFFFFu, a, b, c, hc, nullptr, 0, s_nat, dummy);
         st.exit_p[j] = p; st.exit_sm[j] = sm; st.n[j] = n;
         st.dc[0][j] = a; st.dc[1][j] = b; st.dc[2][j] = c;
@@ -329,7 +366,7 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
         // entry state: exact for the first subsequence of the chunk, a guess (AC code of the first block) elsewhere
         st.entry_p[tid] = tid == 0 ? s_carry_p : (chunk + tid) * kSubseqBits;
         st.entry_sm[tid] = tid == 0 ? s_carry_slot % hc.mcu_slots : 1u;
-        if (active) decode_into_state(chunk, tid);
+        if (active) decode_into_state(chunk, tid, true);
         __syncthreads();
         uint32_t rounds = 1, decodes = (uint32_t)cnt;
         // Re-decode every subsequence whose entry state differs from its left neighbour's exit state until none
@@ -351,7 +388,7 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
             if (total == 0) break;
             if (need) st.list[before + __popc(ballot & ((1u << lane) - 1))] = (uint32_t)tid;
             __syncthreads();
-            if ((uint32_t)tid < total) decode_into_state(chunk, (int)st.list[tid]);
+            if ((uint32_t)tid < total) decode_into_state(chunk, (int)st.list[tid], false);
             ++rounds;
             decodes += total;
             __syncthreads();

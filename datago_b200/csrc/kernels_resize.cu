@@ -142,7 +142,7 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
 // pixel x when k % C == c and zero otherwise.  The 16-bit weights are split into a signed high and an unsigned low
 // byte, w = 256 hi + lo, so that the product runs on the 8-bit integer tensor-core path with 32-bit accumulation:
 // out = 256 (src x hi) + (src x lo), which is exact -- the result equals the dp2a kernel's bit for bit.
-//   CTA  = one strip of 64 output bytes x up to 512 rows of one pass; warp q owns output bytes 8q .. 8q+7 of the strip.
+//   CTA  = one strip of 64 output bytes x up to 2048 rows of one pass; warp q owns output bytes 8q .. 8q+7 of the strip.
 //   B    = the warp's slice of Wt (source bytes under its eight outputs, at most 256), both limbs: every lane gathers its
 //          mma.m16n8k32 fragments from the filter table once and keeps them in registers for all rows of the CTA;
 //   A    = 32 source rows of the strip's band per chunk, brought in by 16-byte asynchronous copies into a ring of up to
