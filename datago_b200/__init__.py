@@ -186,6 +186,11 @@ EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ct
            "dg_feeder_get_stats dg_feeder_destroy").split()
 
 
+def _shape(result):
+    """numpy shape of a payload: H x W for one channel, H x W x C otherwise."""
+    return (result.height, result.width) if result.channels == 1 else (result.height, result.width, result.channels)
+
+
 def _check(rc):
     if rc:
         raise DatagoB200Error(rc, lib().dg_last_error().decode())
@@ -390,8 +395,7 @@ class Batch:
             if r.status:
                 outs.append(None)
             else:
-                shape = (r.height, r.width, 3) if r.channels == 3 else (r.height, r.width)
-                outs.append(np.empty(shape, np.uint8))
+                outs.append(np.empty(_shape(r), np.uint8))
         return outs
 
     def download(self, outs=None):
@@ -523,8 +527,7 @@ class Feeder:
 
     def fetch(self, ticket, result):
         """The payload of a finished ticket as a numpy array (H x W x 3, or H x W for one channel)."""
-        shape = (result.height, result.width, 3) if result.channels == 3 else (result.height, result.width)
-        out = np.empty(shape, np.uint8)
+        out = np.empty(_shape(result), np.uint8)
         _check(lib().dg_fetch(self._h, ticket, out.ctypes.data, out.nbytes))
         return out
 
@@ -533,7 +536,7 @@ class Feeder:
         valid until release()."""
         ptr = C.c_void_p()
         _check(lib().dg_peek(self._h, ticket, C.byref(ptr)))
-        shape = (result.height, result.width, 3) if result.channels == 3 else (result.height, result.width)
+        shape = _shape(result)
         return np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_uint8)), shape=(int(result.nbytes),)).reshape(shape)
 
     def release(self, ticket):

@@ -353,12 +353,15 @@ struct WavePlan {
     std::vector<uint32_t> copy_first;
     std::vector<ToRgbJob> torgb;
     std::vector<uint32_t> torgb_first;
+    // alpha images: multiply before / divide after each of the two resizes (0: before H1, 1: after V1, 2: before H2, 3: after V2)
+    std::vector<AlphaJob> alpha[4];
+    std::vector<uint32_t> alpha_first[4];
     // scratch layout (bytes from the wave scratch base)
     size_t us_bytes = 0, coef_blocks = 0, plane_bytes = 0, decoded_bytes = 0, mid_bytes = 0, nseg = 0;
     size_t off_us = 0, off_uslen = 0, off_segstart = 0, off_segfound = 0, off_coef = 0, off_planes = 0, off_decoded = 0, off_mid = 0, total = 0;
     // meta offsets
-    size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0, m_torgbs = 0;
-    OwnerMapOff m_restart, m_blocks, m_color, m_fchroma, m_ftile, m_pass[4], m_copy, m_torgb;
+    size_t m_descs = 0, m_spec = 0, m_restart_list = 0, m_passes[4] = {0, 0, 0, 0}, m_copies = 0, m_torgbs = 0, m_alphas[4] = {0, 0, 0, 0};
+    OwnerMapOff m_restart, m_blocks, m_color, m_fchroma, m_ftile, m_pass[4], m_copy, m_torgb, m_alpha[4];
 };
 
 struct StageEvent { int stage; cudaEvent_t a, b; };
@@ -594,6 +597,24 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
     Buf cur{src, src_pitch, 0, 0};
     const int n_pass = (int)h1 + (int)v1 + (int)h2 + (int)v2;
     int done = 0;
+    // Images with an alpha channel: fast_image_resize multiplies the colour channels by alpha before each convolution
+    // resize and divides afterwards (a resize that only copies touches no value).  The multiplied copy of a source that
+    // must stay intact (the batch's input) goes to the scratch area; otherwise both steps work in place.
+    const bool alpha = C == 2 || C == 4;
+    auto add_alpha = [&](int slot, const uint8_t* s, uint32_t spitch, uint8_t* d, uint32_t dpitch, uint32_t width, uint32_t rows, bool divide) {
+        AlphaJob j;
+        memset(&j, 0, sizeof j);
+        j.src = s; j.dst = d; j.src_pitch = spitch; j.dst_pitch = dpitch; j.width = width; j.rows = rows; j.channels = C; j.divide = divide ? 1 : 0;
+        wv.alpha[slot].push_back(j);
+    };
+    auto premultiplied_copy = [&](int slot) {  // of the whole source image
+        const uint32_t pitch = (uint32_t)align_up((size_t)w * C, 16);
+        uint8_t* pm = mid_base + *mid_used;
+        *mid_used += align_up((size_t)pitch * h, 256);
+        add_alpha(slot, src, src_pitch, pm, pitch, w, h, false);
+        cur = Buf{pm, pitch, 0, 0};
+    };
+    if (alpha && (h1 || v1)) premultiplied_copy(0);
     auto next_dst = [&](uint32_t out_w, uint32_t out_h, uint32_t* pitch) -> uint8_t* {
         if (done + 1 == n_pass) { *pitch = tw * C; return dst; }
         *pitch = (uint32_t)align_up((size_t)out_w * C, 16);
@@ -638,6 +659,17 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         emit(1, false, T_v1, o_v1, (uint32_t)ra, ow, oh, cur.ptr + (size_t)(ca - cur.col0) * C, cur.row0, cur.pitch, d, pitch);
         cur = Buf{d, pitch, ca, ra};
     }
+    if (alpha && (h1 || v1)) {  // the first resize is complete: divide its result (region [ca, cb) x [ra, rb)) in place
+        uint8_t* region = const_cast<uint8_t*>(cur.ptr) + (size_t)(ra - cur.row0) * cur.pitch + (size_t)(ca - cur.col0) * C;
+        add_alpha(1, region, cur.pitch, region, cur.pitch, (uint32_t)(cb - ca), (uint32_t)(rb - ra), true);
+    }
+    if (alpha && (h2 || v2)) {  // the second resize multiplies again
+        if (cur.ptr == src) premultiplied_copy(2);
+        else {
+            uint8_t* region = const_cast<uint8_t*>(cur.ptr) + (size_t)(ra - cur.row0) * cur.pitch + (size_t)(ca - cur.col0) * C;
+            add_alpha(2, region, cur.pitch, region, cur.pitch, (uint32_t)(cb - ca), (uint32_t)(rb - ra), false);
+        }
+    }
     if (h2) {  // columns [ca, cb) -> output columns [0, tw), rows [ra, rb)
         uint32_t pitch;
         const uint32_t oh = (uint32_t)(rb - ra);
@@ -652,6 +684,7 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         emit(3, false, T_v2, o_v2, 0, tw, th, cur.ptr + (size_t)(ca - cur.col0) * C, cur.row0, cur.pitch, d, pitch);
         cur = Buf{d, pitch, 0, 0};
     }
+    if (alpha && (h2 || v2)) add_alpha(3, dst, tw * C, dst, tw * C, tw, th, true);
     if (n_pass == 0)  // same scale, integral crop: a strided copy
         add_copy(src + (size_t)ra * src_pitch + (size_t)ca * C, src_pitch, tw * C, th);
 }
@@ -659,6 +692,12 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
 // worst-case scratch of the intermediates of one image's resize
 static size_t resize_mid_bound(const dg_plan& p, uint32_t C) {
     if (p.identity) return 0;
+    if (C == 2 || C == 4) {  // plus the pre-multiplied copy of the source
+        const size_t pm = align_up(align_up((size_t)p.src_w * C, 16) * p.src_h, 256);
+        const size_t a = align_up((size_t)p.new_w * C, 16) * (size_t)(std::max(p.src_h, p.new_h) + 8);
+        const size_t b = align_up((size_t)p.new_w * C, 16) * (size_t)(p.new_h + 8);
+        return pm + align_up(a, 256) + 2 * align_up(b, 256);
+    }
     const size_t a = align_up((size_t)p.new_w * C, 16) * (size_t)(std::max(p.src_h, p.new_h) + 8);
     const size_t b = align_up((size_t)p.new_w * C, 16) * (size_t)(p.new_h + 8);
     return align_up(a, 256) + 2 * align_up(b, 256);
@@ -704,8 +743,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         if (!src.data) { it.status = DG_E_INVALID; return; }
         const bool want_rgb = (src.flags & DG_ITEM_TO_RGB8) != 0;
         if (src.raw_w) {
-            const bool alpha = src.raw_c == 2 || src.raw_c == 4;
-            if (src.raw_h == 0 || src.raw_c < 1 || src.raw_c > 4 || (alpha && !want_rgb) ||
+            if (src.raw_h == 0 || src.raw_c < 1 || src.raw_c > 4 ||
                 src.len < (uint64_t)src.raw_w * src.raw_h * src.raw_c) { it.status = DG_E_INVALID; return; }
             it.w = src.raw_w; it.h = src.raw_h; it.c = src.raw_c;
         } else {
@@ -736,8 +774,6 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             it.out_w = it.w; it.out_h = it.h;
             it.plan.src_w = it.w; it.plan.src_h = it.h; it.plan.channels = it.c;
         }
-        // images with an alpha channel would need fast_image_resize's alpha pre-multiplication to be resized
-        if ((it.c == 2 || it.c == 4) && transform && !it.plan.identity) { it.status = DG_E_UNSUPPORTED; return; }
         it.to_rgb = want_rgb && it.c != 3;
         it.c_out = it.to_rgb ? 3 : it.c;
         it.out_bytes = (size_t)it.out_w * it.out_h * it.c_out;
@@ -988,6 +1024,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             for (int s = 0; s < 4; ++s) { wv.passes[s].clear(); wv.pass_first[s].clear(); }
             wv.copies.clear(); wv.copy_first.clear();
             wv.torgb.clear(); wv.torgb_first.clear();
+            for (int a = 0; a < 4; ++a) { wv.alpha[a].clear(); wv.alpha_first[a].clear(); }
             size_t mid_used = 0;
             for (int i = wv.first_item; i < wv.last_item; ++i) {
                 ItemPlan& it = b->items[i];
@@ -1031,6 +1068,15 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
                 t += (uint32_t)(((uint64_t)j.row_bytes * j.rows + kCopyTileBytes - 1) / kCopyTileBytes);
                 wv.copy_first.push_back(t);
             }
+            for (int a = 0; a < 4; ++a) {
+                t = 0;
+                wv.alpha_first[a].push_back(0);
+                for (AlphaJob& j : wv.alpha[a]) {
+                    j.tile_first = t;
+                    t += (j.width * j.rows + kAlphaTilePx - 1) / kAlphaTilePx;
+                    wv.alpha_first[a].push_back(t);
+                }
+            }
             t = 0;
             wv.torgb_first.push_back(0);
             for (ToRgbJob& j : wv.torgb) {
@@ -1062,6 +1108,11 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.m_copies = m.put(wv.copies, 16);
             if (wv.copy_first.empty()) wv.copy_first.push_back(0);
             wv.m_copy = put_owner_map(m, wv.copy_first);
+            for (int a = 0; a < 4; ++a) {
+                wv.m_alphas[a] = m.put(wv.alpha[a], 16);
+                if (wv.alpha_first[a].empty()) wv.alpha_first[a].push_back(0);
+                wv.m_alpha[a] = put_owner_map(m, wv.alpha_first[a]);
+            }
             wv.m_torgbs = m.put(wv.torgb, 16);
             if (wv.torgb_first.empty()) wv.torgb_first.push_back(0);
             wv.m_torgb = put_owner_map(m, wv.torgb_first);
@@ -1076,7 +1127,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             if (rc) return abandon(b, rc);
             b->d_persist = (uint8_t*)ctx->dev.blocks[b->blk_persist].ptr;
             bool pointers = transform;  // resize passes and copy jobs carry device pointers: lay them out again for real
-            for (const WavePlan& wv : b->waves) pointers = pointers || !wv.copies.empty() || !wv.torgb.empty();
+            for (const WavePlan& wv : b->waves) pointers = pointers || !wv.copies.empty() || !wv.torgb.empty();  // (alpha jobs only exist with a transform)
             if (!pointers) break;
         }
     }
@@ -1318,14 +1369,25 @@ static int batch_run_locked(dg_batch* b) {
         if (transform) {
             const uint32_t* tables = (const uint32_t*)(meta + b->m_tables);
             static const int kStageOf[4] = {DG_STAGE_RESIZE_H, DG_STAGE_RESIZE_V, DG_STAGE_RESIZE_SHIFT, DG_STAGE_RESIZE_SHIFT};
-            for (int st = 0; st < 4; ++st) {
-                if (wv.passes[st].empty()) continue;
-                CU(mark(kStageOf[st], true));
-                const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
-                if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
-                else { launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s); b->used_hmma = b->used_hmma || wv.mma_tiles[st] != 0; }
+            auto alpha_step = [&](int a) -> int {
+                if (wv.alpha[a].empty()) return DG_OK;
+                CU(mark(DG_STAGE_RESIZE_SHIFT, true));
+                launch_alpha((const AlphaJob*)(meta + wv.m_alphas[a]), resolve(b, wv.m_alpha[a]), s);
                 ++b->launches;
-                CU(mark(kStageOf[st], false));
+                CU(mark(DG_STAGE_RESIZE_SHIFT, false));
+                return DG_OK;
+            };
+            for (int st = 0; st < 4; ++st) {
+                if (st == 0 || st == 2) { const int rc = alpha_step(st); if (rc) return rc; }                 // multiply before a resize
+                if (!wv.passes[st].empty()) {
+                    CU(mark(kStageOf[st], true));
+                    const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
+                    if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
+                    else { launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s); b->used_hmma = b->used_hmma || wv.mma_tiles[st] != 0; }
+                    ++b->launches;
+                    CU(mark(kStageOf[st], false));
+                }
+                if (st == 1 || st == 3) { const int rc = alpha_step(st); if (rc) return rc; }                 // divide after it
             }
         }
         if (!wv.copies.empty()) {

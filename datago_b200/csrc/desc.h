@@ -92,6 +92,16 @@ struct CopyJob {  // identity payloads / pitch removal
     uint32_t src_pitch, row_bytes, rows, tile_first;
 };
 
+// Alpha pre-multiplication / division around a convolution resize of an image with an alpha channel (2 = luma + alpha,
+// 4 = RGBA): what fast_image_resize does inside Resizer::resize for such pixel types.
+struct AlphaJob {
+    const uint8_t* src;
+    uint8_t* dst;            // may equal src
+    uint32_t src_pitch, dst_pitch, width, rows, channels;  // width in pixels
+    uint32_t divide;         // 0: colour = mul_div_255(colour, alpha); 1: colour = colour * recip(alpha), rounded and clipped
+    uint32_t tile_first, pad;
+};
+
 struct ToRgbJob {  // convert_to_rgb8 of one payload: channels 1, 2 or 4 -> 3
     const uint8_t* src;
     uint8_t* dst;

@@ -100,6 +100,8 @@ void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
 unsigned int read_conv_timeouts(cudaStream_t s);
 void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
 void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s);
+constexpr uint32_t kAlphaTilePx = 2048;  // pixels per CTA of the alpha multiply / divide kernel
+void launch_alpha(const AlphaJob* jobs, OwnerMap map, cudaStream_t s);
 constexpr uint32_t kToRgbTilePx = 2048;  // pixels per CTA of the RGB8 conversion
 void launch_to_rgb8(const ToRgbJob* jobs, OwnerMap map, cudaStream_t s);
 

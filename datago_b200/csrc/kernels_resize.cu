@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int32_t d = 32 * ks + 16 * hf + 4 * (int32_t)t4 + e - first;
-                        const int32_t i = C == 3 ? d / 3 : d;
+                        const int32_t i = C == 1 ? d : C == 3 ? d / 3 : d / (int32_t)C;
                         if (d >= 0 && i < taps && i * (int32_t)C == d) {
                             const int32_t wv = __ldg(k + (size_t)i * tab_n);
                             hi[hf] |= ((uint32_t)(wv >> 8) & 255u) << (8 * e);   // signed high byte
@@ -374,6 +374,25 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
     if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
 }
 
+// Two- and four-channel images (alpha) that the tensor-core kernel cannot take: a plain loop, one tap at a time.
+__device__ void conv_h_rows_any(const ConvPass& p, const Table& tb, uint32_t x, uint32_t y0) {
+    const uint32_t t = p.t0 + x, C = p.channels;
+    const int32_t first = __ldg(tb.start + t) - p.src_origin;
+    const int32_t taps = __ldg(tb.size + t);
+    const int16_t* k = tb.k + t;
+    const uint32_t nrows = min((uint32_t)kHRowsPerThread, p.out_h - y0);
+    for (uint32_t r = 0; r < nrows; ++r) {
+        const uint8_t* g = p.src + (size_t)(y0 + r) * p.src_pitch + (size_t)first * C;
+        int32_t acc[4] = {1 << (p.precision - 1), 1 << (p.precision - 1), 1 << (p.precision - 1), 1 << (p.precision - 1)};
+        for (int32_t i = 0; i < taps; ++i) {
+            const int32_t wv = __ldg(k + (size_t)i * p.tab_n);
+            for (uint32_t c = 0; c < C; ++c) acc[c] += wv * (int32_t)__ldg(g + (size_t)i * C + c);
+        }
+        uint8_t* o = p.dst + (size_t)(y0 + r) * p.dst_pitch + (size_t)x * C;
+        for (uint32_t c = 0; c < C; ++c) o[c] = (uint8_t)clip8(acc[c], p.precision);
+    }
+}
+
 __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t first_tile) {
     const uint32_t tile_index = first_tile + blockIdx.x;
     const ConvPass& p = passes[owner_of_tile(map, tile_index)];
@@ -383,6 +402,7 @@ __global__ void __launch_bounds__(kConvHThreads) k_conv_h(const ConvPass* passes
     const uint32_t y0 = ty * kConvTileH + (threadIdx.x / kConvTileW) * kHRowsPerThread;
     if (x >= p.out_w || y0 >= p.out_h) return;
     const Table tb = table_of(p, tables);
+    if (p.channels == 2 || p.channels == 4) { conv_h_rows_any(p, tb, x, y0); return; }
     if (p.guard_hi) {
         if (p.channels == 3) conv_h_rows<3, true>(p, tb, x, y0);
         else conv_h_rows<1, true>(p, tb, x, y0);
@@ -566,6 +586,35 @@ __global__ void __launch_bounds__(256) k_copy(const CopyJob* jobs, OwnerMap map)
 
 void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s) {
     if (map.total) k_copy<<<map.total, 256, 0, s>>>(jobs, map);
+}
+
+// ---- alpha pre-multiplication and division (what fast_image_resize does around a convolution of U8x2 / U8x4 images) ----
+// multiply: colour = ((colour * alpha + 128) + ((colour * alpha + 128) >> 8)) >> 8
+// divide:   colour = min(255, (colour * recip + 2^15) >> 16), recip = ((255 * 2^17) / alpha + 1) >> 1, 0 for alpha 0
+__global__ void __launch_bounds__(256) k_alpha(const AlphaJob* jobs, OwnerMap map) {
+    const AlphaJob& j = jobs[owner_of_tile(map, blockIdx.x)];
+    const uint32_t base = (blockIdx.x - j.tile_first) * kAlphaTilePx, npx = j.width * j.rows, C = j.channels;
+    for (uint32_t k = threadIdx.x; k < kAlphaTilePx; k += 256) {
+        const uint32_t i = base + k;
+        if (i >= npx) break;
+        const uint32_t y = i / j.width, x = i - y * j.width;
+        const uint8_t* s = j.src + (size_t)y * j.src_pitch + (size_t)x * C;
+        uint8_t* d = j.dst + (size_t)y * j.dst_pitch + (size_t)x * C;
+        const uint32_t a = s[C - 1];
+        const uint32_t recip = a ? ((255u << 17) / a + 1u) >> 1 : 0u;
+        for (uint32_t c = 0; c + 1 < C; ++c) {
+            const uint32_t v = s[c];
+            uint32_t r;
+            if (j.divide) r = min(255u, (v * recip + (1u << 15)) >> 16);
+            else { const uint32_t t = v * a + 128u; r = ((t >> 8) + t) >> 8; }
+            d[c] = (uint8_t)r;
+        }
+        d[C - 1] = (uint8_t)a;
+    }
+}
+
+void launch_alpha(const AlphaJob* jobs, OwnerMap map, cudaStream_t s) {
+    if (map.total) k_alpha<<<map.total, 256, 0, s>>>(jobs, map);
 }
 
 // ---- convert_to_rgb8 (datago src/image_processing.rs:163-186) -------------------------------------------------------

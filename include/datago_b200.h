@@ -79,8 +79,7 @@ typedef struct dg_jpeg_info {
 typedef struct dg_item {
     const uint8_t* data;   /* JPEG file bytes, or raw interleaved 8-bit pixels when raw_w > 0 (host memory) */
     uint64_t len;
-    uint32_t raw_w, raw_h, raw_c; /* raw input: size and channels (1 = L8, 3 = RGB8; 2 = LA8 and 4 = RGBA8 only with
-                                     DG_ITEM_TO_RGB8 and no resize); 0 for JPEG input */
+    uint32_t raw_w, raw_h, raw_c; /* raw input: size and channels (1 = L8, 2 = LA8, 3 = RGB8, 4 = RGBA8); 0 for JPEG input */
     uint32_t flags;        /* DG_ITEM_* */
     const char* forced_key; /* NULL or "": bucket chosen from the image's own aspect ratio; else the key to force
                                (the "same bucket for every payload of a sample" rule, src/worker_wds.rs:68-76) */
@@ -91,9 +90,10 @@ typedef struct dg_item {
  * crop_and_resize a payload that is not RGB8 is converted by convert_to_rgb8 (:163-186, applied at :366-372):
  * one-channel images repeat their value in three channels, RGBA is composited over an opaque (128,128,128)
  * background (source-over in f32, truncated to 8 bits), and the payload reports channels = 3.  datago sets it for
- * the main image and never for masks / additional images (src/worker_http.rs:188-192).  RGBA and LA inputs are
- * accepted only when nothing has to be resized: datago resizes them with alpha pre-multiplication inside
- * fast_image_resize, which this library does not restate (DG_E_UNSUPPORTED). */
+ * the main image and never for masks / additional images (src/worker_http.rs:188-192).
+ * Images with an alpha channel (LA8, RGBA8) are resized as fast_image_resize does it for U8x2 / U8x4 pixels
+ * (src/image_processing.rs:269-274): colour multiplied by alpha before each convolution resize and divided by it
+ * afterwards; without the flag the payload keeps its 2 or 4 channels. */
 enum { DG_ITEM_TO_RGB8 = 1u };
 
 /* Per-item outcome: the fields of ImagePayload (src/structs.rs:52-71) plus where the pixels are. */

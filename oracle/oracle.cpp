@@ -290,11 +290,40 @@ void vert_pass(const uint8_t* src, int sw, int C, int col0, int w_out, uint8_t* 
     }
 }
 
+// Alpha handling of fast_image_resize for 8-bit pixels with an alpha channel (U8x2 = luma + alpha, U8x4 = RGBA), which
+// its Resizer applies around every convolution resize (`use_alpha`, on by default): colour channels are multiplied by
+// alpha before the convolution and divided by it afterwards; alpha itself is convolved like any channel.  Restated from
+// the crate's published scalar code (mul_div_255, and a 16-bit reciprocal table for the division); not checkable here.
+inline uint8_t mul_div_255(uint32_t a, uint32_t b) { const uint32_t t = a * b + 128; return (uint8_t)(((t >> 8) + t) >> 8); }
+inline uint32_t recip_alpha(uint32_t a) { return a ? ((255u * (1u << 17)) / a + 1) >> 1 : 0; }
+inline uint8_t div_and_clip(uint32_t v, uint32_t recip) { const uint32_t r = (v * recip + (1u << 15)) >> 16; return (uint8_t)(r > 255 ? 255 : r); }
+
+void alpha_multiply(uint8_t* px, size_t n, int C) {
+    for (size_t i = 0; i < n; ++i) {
+        uint8_t* q = px + i * C;
+        for (int c = 0; c + 1 < C; ++c) q[c] = mul_div_255(q[c], q[C - 1]);
+    }
+}
+void alpha_divide(uint8_t* px, size_t n, int C) {
+    for (size_t i = 0; i < n; ++i) {
+        uint8_t* q = px + i * C;
+        const uint32_t r = recip_alpha(q[C - 1]);
+        for (int c = 0; c + 1 < C; ++c) q[c] = div_and_clip(q[c], r);
+    }
+}
+
 // One `Resizer::resize` call with Convolution(Lanczos3) and a floating-point source box.
 void resample(const uint8_t* src, int sw, int sh, int C, double left, double top, double bw, double bh,
               uint8_t* dst, int dw, int dh, int mode) {
     bool need_h = (double)dw != bw || left != std::round(left);
     bool need_v = (double)dh != bh || top != std::round(top);
+    std::vector<uint8_t> premultiplied;
+    const bool alpha = (C == 2 || C == 4) && (need_h || need_v);  // a plain copy touches no pixel value
+    if (alpha) {
+        premultiplied.assign(src, src + (size_t)sw * sh * C);
+        alpha_multiply(premultiplied.data(), (size_t)sw * sh, C);
+        src = premultiplied.data();
+    }
     if (need_h && need_v) {
         Coeffs hc = make_coeffs(sw, left, left + bw, dw, mode), vc = make_coeffs(sh, top, top + bh, dh, mode);
         int y_first = vc.start[0], y_last = vc.start[dh - 1] + vc.size[dh - 1];
@@ -313,6 +342,7 @@ void resample(const uint8_t* src, int sw, int sh, int C, double left, double top
         for (int y = 0; y < dh; ++y)
             memcpy(dst + (size_t)y * dw * C, src + ((size_t)((int)top + y) * sw + (int)left) * C, (size_t)dw * C);
     }
+    if (alpha) alpha_divide(dst, (size_t)dw * dh, C);
 }
 
 }  // namespace

@@ -69,16 +69,32 @@ def test_gray_sources_are_resized_in_one_channel_then_expanded():
     assert_same(out, oracle.to_rgb8(oracle.jpeg_decode(gj)), "decode-only gray")
 
 
-def test_alpha_inputs_need_the_flag_and_cannot_be_resized():
+def test_alpha_images_are_resized_with_premultiplied_colour():
+    # RGBA and LA inputs: colour multiplied by alpha before each convolution resize and divided afterwards, as
+    # fast_image_resize does for U8x4 / U8x2; with image_to_rgb8 the result is then composited over gray
     rng = np.random.default_rng(93)
-    rgba = rng.integers(0, 256, (100, 150, 4), dtype=np.uint8)
-    exact = rng.integers(0, 256, (224, 224, 4), dtype=np.uint8)   # already has its bucket's size: returned as is
-    st, _, _ = ctx(None).process([rgba], None, 0)[0]
-    assert st == 1                                              # invalid: four channels without to_rgb8
-    res = ctx(CFG224).process([rgba, exact], None, 0, to_rgb8=True)
-    assert res[0][0] == 5                                       # unsupported: alpha-aware resize is not restated
-    assert res[1][0] == 0
-    assert_same(res[1][1], oracle.to_rgb8(exact), "identity bucket")
+    shapes = [(100, 150, 4), (224, 224, 4), (300, 777, 4), (640, 481, 2), (224, 229, 4), (231, 224, 2), (1500, 2200, 4)]
+    raws = [rng.integers(0, 256, s, dtype=np.uint8) for s in shapes]
+    raws[2][:, :, 3] = 255                                       # opaque: must equal the three-channel result
+    raws[0][:40, :, 3] = 0                                       # a fully transparent band
+    c = ctx(CFG224)
+    plain = c.process(raws, None, 0)
+    for a, (st, out, r) in zip(raws, plain):
+        want, p = oracle.crop_and_resize(CFG224, a)
+        assert st == 0 and r.channels == a.shape[2] and r.plan.as_tuple() == p.as_tuple()
+        assert_same(out, want, f"alpha payload {a.shape}")
+    opaque_rgb = oracle.crop_and_resize(CFG224, np.ascontiguousarray(raws[2][:, :, :3]))[0]
+    assert np.array_equal(plain[2][1][:, :, :3], opaque_rgb) and np.all(plain[2][1][:, :, 3] == 255)
+    for a, (st, out, r) in zip(raws, c.process(raws, None, 0, to_rgb8=True)):
+        assert st == 0 and r.channels == 3
+        assert_same(out, oracle.to_rgb8(oracle.crop_and_resize(CFG224, a)[0]), f"alpha to rgb8 {a.shape}")
+    # forced bucket far from the image's aspect ratio, and a four-channel image without any transform
+    (st, out, r), = c.process([raws[0]], ["1.900"], 0)
+    assert st == 0
+    assert_same(out, oracle.crop_and_resize(CFG224, raws[0], "1.900")[0])
+    (st, out, r), = ctx(None).process([raws[0]], None, 0)
+    assert st == 0 and r.channels == 4
+    assert_same(out, raws[0])
 
 
 def test_collated_buckets_use_the_payload_channel_count():
