@@ -9,8 +9,11 @@ goes through the CUDA library in batches.
 Differences that are stated, not hidden:
   * `source_type` "webdataset" reads LOCAL tar shards (`url` is a path, a glob or a {a..b} brace pattern); the reference
     streams them over HTTP (src/generator_wds.rs:56-204);
-  * only baseline JPEG payloads are decoded here (the library's scope); other image types in a sample are skipped with a
-    warning, where the reference would use the `image` crate;
+  * baseline JPEG payloads are decoded by the CUDA library; every other image type a sample may carry (PNG masks above
+    all, src/worker_http.rs:186-201, but also progressive JPEG, BMP, GIF, WebP) is decoded on the host by Pillow to raw
+    8-bit pixels, the way the reference hands them to the `image` crate, and then takes the library's raw-pixel path
+    (bucket, crop and resize on the GPU).  `pre_encode_images` re-encodes finished payloads on the host as well
+    (src/image_processing.rs:375-416);
   * two opt-in keys the reference ignores: `"device"` (CUDA ordinal, default LOCAL_RANK or 0) and `"batch_size"`;
     `"device_payloads": true` keeps the pixels on the GPU (`ImagePayload.__cuda_array_interface__` / `__dlpack__`).
 """
@@ -52,6 +55,10 @@ class ImagePayload:
 
     def to_numpy_array(self):
         """src/structs.rs:154-188"""
+        if self.is_encoded:
+            import io
+            from PIL import Image
+            return np.asarray(Image.open(io.BytesIO(self.data)).convert("RGB"))
         if self._device_ptr and not len(self.data):
             return self._keepalive.ctx.copy_to_host(self._device_ptr, self.height * self.width * self.channels).reshape(self._shape())
         return np.frombuffer(self.data, np.uint8).reshape(self._shape())
@@ -59,6 +66,9 @@ class ImagePayload:
     def to_pil_image(self):
         """src/structs.rs:103-151: mode L for one channel, RGBA for four, RGB otherwise."""
         from PIL import Image
+        if self.is_encoded:
+            import io
+            return Image.open(io.BytesIO(self.data))
         a = self.to_numpy_array()
         if self.channels == 1:
             return Image.fromarray(a.reshape(self.height, self.width)).convert("L")
@@ -147,6 +157,51 @@ def initialize_logging(log_level=None):
     return True
 
 
+# ---- host-side codecs around the GPU path ---------------------------------------------------------------------------
+def is_baseline_jpeg(data):
+    """True when the CUDA decoder takes the file (baseline, Huffman, 8 bit): a header-only look."""
+    try:
+        jpeg_probe(data)
+        return True
+    except DatagoB200Error:
+        return False
+
+
+def decode_on_host(data):
+    """Any image Pillow reads -> raw uint8 pixels shaped (H, W) or (H, W, C), C in 2..4, as `image::load_from_memory`
+    yields Luma8 / LumaA8 / Rgb8 / Rgba8 (src/worker_wds.rs:45).  Palette images become RGB or RGBA, 1-bit and 16-bit
+    gray become 8-bit gray.  Returns None when the bytes are no image."""
+    import io
+    from PIL import Image
+    try:
+        im = Image.open(io.BytesIO(data))
+        im.load()
+    except Exception:  # noqa: BLE001
+        return None
+    if im.mode == "P":
+        im = im.convert("RGBA" if "transparency" in im.info else "RGB")
+    elif im.mode in ("1", "I;16", "I;16B", "I", "F"):
+        im = im.convert("L")
+    elif im.mode not in ("L", "LA", "RGB", "RGBA"):
+        im = im.convert("RGB")
+    return np.ascontiguousarray(np.asarray(im, dtype=np.uint8))
+
+
+def encode_payload(pixels, encode_format="jpeg", jpeg_quality=92):
+    """src/image_processing.rs:375-416: the payload re-encoded as JPEG (given quality) or PNG (fast compression)."""
+    import io
+    from PIL import Image
+    im = Image.fromarray(pixels)
+    out = io.BytesIO()
+    if str(encode_format).lower() == "png":
+        im.save(out, "PNG", compress_level=1)
+    else:
+        if im.mode in ("RGBA", "LA"):
+            im = im.convert("RGB" if im.mode == "RGBA" else "L")  # JPEG has no alpha channel
+        im.save(out, "JPEG", quality=int(jpeg_quality))
+    return out.getvalue()
+
+
 # ---- generators ---------------------------------------------------------------------------------------------------------
 def enumerate_files(root_path, limit, rank=0, world_size=1, random_sampling=False):
     """src/generator_files.rs:44-125: walk, extension filter, take 2*limit, contiguous rank slice, optional shuffle,
@@ -227,6 +282,10 @@ class DatagoClient:
         self.image_config = cfg.get("image_config")
         self.batch_size = int(cfg.get("batch_size", 256))
         self.device_payloads = bool(cfg.get("device_payloads", False))
+        ic = self.image_config or {}
+        self.pre_encode = bool(ic.get("pre_encode_images", False))        # src/image_processing.rs:60-70
+        self.encode_format = str(ic.get("encode_format", "jpeg"))
+        self.jpeg_quality = int(ic.get("jpeg_quality", 92))
         device = int(cfg.get("device", os.environ.get("LOCAL_RANK", 0)))
         tfm = self.image_config if self.image_config and self.image_config.get("crop_and_resize") else None
         self.ctx = Context(device, tfm)  # raises when no CUDA device: there is no CPU path
@@ -368,10 +427,18 @@ class DatagoClient:
                 if self.source_type == "webdataset" and ext not in IMG_TYPES:
                     continue
                 forced = sample_key
+                if not is_baseline_jpeg(data):
+                    pixels = decode_on_host(data)  # PNG masks and whatever else the CUDA decoder does not take
+                    if pixels is not None:
+                        data = pixels
                 if has_tfm and sample_key is None:
                     try:
-                        info = jpeg_probe(data)
-                        p = self.ctx.plan_geometry(info.width, info.height, info.channels)
+                        if isinstance(data, np.ndarray):
+                            h_, w_, c_ = data.shape[0], data.shape[1], (1 if data.ndim == 2 else data.shape[2])
+                        else:
+                            info = jpeg_probe(data)
+                            w_, h_, c_ = info.width, info.height, info.channels
+                        p = self.ctx.plan_geometry(w_, h_, c_)
                         sample_key = aspect_ratio_to_str(p.target_w, p.target_h)
                     except DatagoB200Error:
                         pass  # the item fails in the batch as well and the sample is handled there
@@ -395,10 +462,15 @@ class DatagoClient:
             if r.status != 0:
                 log.error("decode failed for %s (status %d)", name, r.status)
                 continue
-            pl = ImagePayload(data=b"" if self.device_payloads else outs[i].tobytes(), original_height=r.original_height,
-                              original_width=r.original_width, height=r.height, width=r.width, channels=r.channels,
-                              bit_depth=8, is_encoded=False, device_ptr=r.device_data if self.device_payloads else 0,
-                              keepalive=batch if self.device_payloads else None)
+            if self.pre_encode and not self.device_payloads:
+                pl = ImagePayload(data=encode_payload(outs[i], self.encode_format, self.jpeg_quality),
+                                  original_height=r.original_height, original_width=r.original_width, height=r.height,
+                                  width=r.width, channels=-1, bit_depth=8, is_encoded=True)
+            else:
+                pl = ImagePayload(data=b"" if self.device_payloads else outs[i].tobytes(), original_height=r.original_height,
+                                  original_width=r.original_width, height=r.height, width=r.width, channels=r.channels,
+                                  bit_depth=8, is_encoded=False, device_ptr=r.device_data if self.device_payloads else 0,
+                                  keepalive=batch if self.device_payloads else None)
             payloads.setdefault(ui, []).append((name, pl))
         if not self.device_payloads:
             batch.close()

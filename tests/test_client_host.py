@@ -111,3 +111,34 @@ def test_sample_auto_convert_and_logging():
     assert d["masks"] == {} and d["latents"] == {} and d["tags"] == [] and d["coca_embedding"] == []
     first = client.initialize_logging("warn")
     assert client.initialize_logging() is False or first is False   # a second call reports that logging was set up already
+
+
+def test_host_decode_of_png_masks_and_other_formats():
+    # what the CUDA decoder does not take goes through Pillow to raw 8-bit pixels (src/worker_http.rs:186-201: masks are PNG)
+    import io
+    from PIL import Image
+    rng = np.random.default_rng(3)
+    mask = (rng.integers(0, 2, (40, 60)) * 255).astype(np.uint8)
+    rgba = rng.integers(0, 256, (20, 30, 4), dtype=np.uint8)
+
+    def enc(arr, fmt, **kw):
+        b = io.BytesIO()
+        Image.fromarray(arr).save(b, fmt, **kw)
+        return b.getvalue()
+
+    assert np.array_equal(client.decode_on_host(enc(mask, "PNG")), mask)
+    assert np.array_equal(client.decode_on_host(enc(rgba, "PNG")), rgba)
+    pal = Image.fromarray(rgba[:, :, :3]).quantize(16)
+    b = io.BytesIO(); pal.save(b, "PNG")
+    assert client.decode_on_host(b.getvalue()).shape == (20, 30, 3)
+    prog = enc(rgba[:, :, :3], "JPEG", progressive=True)
+    assert not client.is_baseline_jpeg(prog) and client.decode_on_host(prog).shape == (20, 30, 3)
+    assert client.is_baseline_jpeg(enc(rgba[:, :, :3], "JPEG"))
+    assert client.decode_on_host(b"not an image at all") is None
+    # re-encoding of finished payloads (src/image_processing.rs:375-416)
+    j = client.encode_payload(rgba[:, :, :3], "jpeg", 92)
+    assert j[:2] == b"\xff\xd8" and Image.open(io.BytesIO(j)).size == (30, 20)
+    p = client.encode_payload(mask, "png")
+    assert p[:4] == b"\x89PNG" and np.array_equal(np.asarray(Image.open(io.BytesIO(p))), mask)
+    enc_payload = client.ImagePayload(p, 40, 60, 40, 60, -1, 8, True)
+    assert enc_payload().size == (60, 40)

@@ -155,3 +155,42 @@ def test_image_to_rgb8_config_key_turns_gray_files_into_rgb(tmp_path):
         assert (s.image.channels, s.image.width, s.image.height) == (channels, p.target_w, p.target_h)
         got = s.image.to_numpy_array()
         assert np.array_equal(got, oracle.to_rgb8(want) if flag else want.reshape(got.shape))
+
+
+def test_png_masks_ride_in_the_image_bucket_and_payloads_can_be_re_encoded(tmp_path):
+    # a webdataset sample with a JPEG image and a PNG mask (the reference's masks are PNG, src/worker_http.rs:186-201):
+    # the mask is decoded on the host, then bucketed, cropped and resized on the GPU with the image's key
+    import io
+    import tarfile
+    from PIL import Image
+    from datago_b200 import synth
+    rng = np.random.default_rng(56)
+    path = str(tmp_path / "m.tar")
+    want = {}
+    with tarfile.open(path, "w") as tf:
+        for k in range(4):
+            w, h = int(rng.integers(200, 500)), int(rng.integers(200, 500))
+            img = synth.encode_jpeg(synth.natural_image(rng, w, h, 4.0, True), 90, "4:2:0", 0)
+            mask = synth.ellipse_mask(rng, w, h)
+            b = io.BytesIO(); Image.fromarray(mask).save(b, "PNG")
+            key = f"s{k:03d}"
+            for name, payload in ((key + ".jpg", img), (key + ".png", b.getvalue())):
+                ti = tarfile.TarInfo(name); ti.size = len(payload); tf.addfile(ti, io.BytesIO(payload))
+            want[key] = (img, mask)
+    cfg = dict(source_type="webdataset", source_config=dict(url=path), image_config=CFG, limit=10, samples_buffer_size=4)
+    samples = _drain(DatagoClient(json.dumps(cfg)))
+    assert sorted(s.id for s in samples) == sorted(want)
+    for s in samples:
+        img, mask = want[s.id]
+        payload, p = oracle.jpeg_to_payload(img, CFG)
+        assert np.array_equal(s.image.to_numpy_array(), payload)
+        (name, extra), = s.additional_images.items()
+        assert name.endswith(".png") and extra.channels == 1 and (extra.width, extra.height) == (s.image.width, s.image.height)
+        key = oracle.aspect_ratio_to_str(p.target_w, p.target_h)
+        assert np.array_equal(extra.to_numpy_array(), oracle.crop_and_resize(CFG, mask, key)[0])
+    # pre_encode_images: payloads come back as encoded files (src/image_processing.rs:375-416)
+    cfg["image_config"] = dict(CFG, pre_encode_images=True, encode_format="png")
+    for s in _drain(DatagoClient(json.dumps(cfg))):
+        assert s.image.is_encoded and s.image.channels == -1 and bytes(s.image.data[:4]) == b"\x89PNG"
+        payload, _ = oracle.jpeg_to_payload(want[s.id][0], CFG)
+        assert np.array_equal(np.asarray(s.image.to_pil_image()), payload)      # PNG is lossless
