@@ -85,6 +85,13 @@ class Bucket(C.Structure):
                 ("packed_offset", C.c_uint64), ("items", C.POINTER(C.c_int32))]
 
 
+class CtxCounters(C.Structure):
+    _fields_ = [("items", C.c_uint64 * 13), ("batches", C.c_uint64), ("bytes_in", C.c_uint64), ("bytes_out", C.c_uint64)]
+
+
+LOG_FN = C.CFUNCTYPE(None, C.c_int, C.c_char_p, C.c_void_p)
+
+
 class FeederConfig(C.Structure):
     _fields_ = [("lanes", C.c_uint32), ("max_batch", C.c_uint32), ("max_wait_us", C.c_uint32),
                 ("queue_limit", C.c_uint32), ("batch_flags", C.c_uint32), ("reserved", C.c_uint32)]
@@ -132,6 +139,8 @@ def lib():
         "dg_ctx_create_on_stream": (C.c_int, [C.c_int, C.POINTER(ImageConfig), vp, C.POINTER(vp)]),
         "dg_ctx_destroy": (None, [vp]),
         "dg_ctx_stream": (vp, [vp]),
+        "dg_ctx_get_counters": (C.c_int, [vp, C.POINTER(CtxCounters)]),
+        "dg_set_log_callback": (None, [LOG_FN, vp]),
         "dg_size_list": (C.c_int, [C.POINTER(ImageConfig), C.c_int, vp, vp]),
         "dg_bucket_table": (C.c_int, [vp, C.c_int, vp, vp, vp, vp]),
         "dg_closest_aspect_ratio": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_char_p]),
@@ -177,7 +186,7 @@ def lib():
     return L
 
 
-EXPORTS = ("dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
+EXPORTS = ("dg_set_log_callback dg_ctx_get_counters dg_last_error dg_version dg_ctx_create dg_ctx_create_on_stream dg_ctx_destroy dg_ctx_stream dg_size_list "
            "dg_bucket_table dg_closest_aspect_ratio dg_aspect_ratio_to_str dg_plan_geometry dg_jpeg_probe dg_rank_slice "
            "dg_key_hash dg_key_rank dg_batch_create dg_batch_upload dg_batch_run dg_batch_download dg_batch_sync "
            "dg_batch_download_packed dg_batch_packed_bytes dg_batch_bucket_count dg_batch_bucket "
@@ -194,6 +203,22 @@ def _shape(result):
 def _check(rc):
     if rc:
         raise DatagoB200Error(rc, lib().dg_last_error().decode())
+
+
+_log_keep = None
+
+
+def set_log_callback(fn):
+    """fn(level, message) receives one line per dropped item (level 1 = error) and the library's own warnings;
+    None removes it.  The counterpart of the `log` records datago writes for failed samples."""
+    global _log_keep
+    if fn is None:
+        lib().dg_set_log_callback(C.cast(None, LOG_FN), None)
+        _log_keep = None
+        return
+    cb = LOG_FN(lambda level, msg, user: fn(int(level), msg.decode(errors="replace")))
+    lib().dg_set_log_callback(cb, None)
+    _log_keep = cb
 
 
 # ---- host-only helpers ----------------------------------------------------------------------------------------------
@@ -305,6 +330,13 @@ class Context:
         _check(lib().dg_resize_device_static(self._h, C.c_void_p(src_ptr), w, h, channels,
                                              forced_key.encode() if forced_key else None, C.c_void_p(dst_ptr), C.byref(p)))
         return p
+
+    def counters(self):
+        """Items finished by this context per status name, batches, bytes in and out."""
+        c = CtxCounters()
+        _check(lib().dg_ctx_get_counters(self._h, C.byref(c)))
+        items = {STATUS_NAMES[i]: int(c.items[i]) for i in range(13) if c.items[i]}
+        return dict(items=items, batches=int(c.batches), bytes_in=int(c.bytes_in), bytes_out=int(c.bytes_out))
 
     def copy_to_host(self, device_ptr, nbytes):
         out = np.empty(nbytes, np.uint8)

@@ -49,6 +49,40 @@ int dg::dg_set_error(int code, const char* msg) { return fail(code, "%s", msg); 
         if (e_ != cudaSuccess) return fail(DG_E_CUDA, "%s: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
     } while (0)
 
+// ---- logging ----------------------------------------------------------------------------------------------------------
+static std::mutex g_log_mu;
+static dg_log_fn g_log_fn = nullptr;
+static void* g_log_user = nullptr;
+
+extern "C" void dg_set_log_callback(dg_log_fn fn, void* user) {
+    std::lock_guard<std::mutex> lock(g_log_mu);
+    g_log_fn = fn;
+    g_log_user = user;
+}
+
+static void log_line(int level, const char* fmt, ...) {
+    dg_log_fn fn;
+    void* user;
+    {
+        std::lock_guard<std::mutex> lock(g_log_mu);
+        fn = g_log_fn;
+        user = g_log_user;
+    }
+    if (!fn) return;
+    char buf[256];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    fn(level, buf, user);
+}
+
+static const char* status_name(int st) {
+    static const char* const names[DG_STATUS_COUNT] = {"ok", "invalid", "cuda", "truncated", "bad_marker", "unsupported", "bad_table",
+                                                       "bad_code", "unknown_key", "no_transform", "sync_limit", "too_large", "timeout"};
+    return st >= 0 && st < DG_STATUS_COUNT ? names[st] : "?";
+}
+
 extern "C" const char* dg_last_error(void) { return g_err; }
 extern "C" const char* dg_version(void) { return "datago_b200 0.1 (sm_100a)"; }
 
@@ -139,6 +173,7 @@ struct dg_ctx {
     // dp2a kernel (measurements, and the test-suite's coverage of that kernel).
     bool hmma = true;
     unsigned int conv_timeouts_seen = 0;
+    dg_ctx_counters counters{};  // guarded by mu
     // Largest decoded image accepted (width * height * channels bytes); the `image` crate's default allocation limit is 512 MiB.
     uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
@@ -216,6 +251,13 @@ extern "C" void dg_ctx_destroy(dg_ctx* c) {
 }
 
 extern "C" void* dg_ctx_stream(dg_ctx* c) { return c ? (void*)c->stream : nullptr; }
+
+extern "C" int dg_ctx_get_counters(dg_ctx* c, dg_ctx_counters* out) {
+    if (!c || !out) return fail(DG_E_INVALID, "NULL argument");
+    std::lock_guard<std::mutex> lock(c->mu);
+    *out = c->counters;
+    return DG_OK;
+}
 
 // ---------------------------------------------------------------------------------------------------------------
 // host-only entry points
@@ -401,6 +443,7 @@ struct dg_batch {
     uint64_t h2d = 0, d2h = 0;
     uint32_t launches = 0;
     bool uploaded = false, ran = false;
+    bool counted = false;    // its items have been added to the context's counters
     bool used_hmma = false;  // a pass of this batch ran on the tensor-core resize kernel, whose waits are bounded
     std::vector<StageEvent> events;
     float stage_ms[DG_STAGE_COUNT] = {0};
@@ -1469,6 +1512,17 @@ extern "C" int dg_batch_sync(dg_batch* b) {
     if (b->ran) {
         for (int i = 0; i < b->n; ++i)
             if (b->items[i].status == DG_OK && b->h_status[i]) b->items[i].status = device_status_to_code(b->h_status[i]);
+        if (!b->counted) {  // once per batch, however often it is run and synchronised
+            b->counted = true;
+            ++ctx->counters.batches;
+            ctx->counters.bytes_in += b->blob_bytes + b->rawin_bytes;
+            for (int i = 0; i < b->n; ++i) {
+                const int st = b->items[i].status;
+                ++ctx->counters.items[st >= 0 && st < DG_STATUS_COUNT ? st : DG_E_INVALID];
+                if (st == DG_OK) ctx->counters.bytes_out += b->items[i].out_bytes;
+                else log_line(DG_LOG_ERROR, "item %d: %s (status %d)", i, status_name(st), st);  // the sample is dropped
+            }
+        }
         if (b->flags & DG_BATCH_TIMING) {
             for (float& v : b->stage_ms) v = 0.f;
             for (const StageEvent& se : b->events) {

@@ -137,6 +137,24 @@ enum { DG_STAGE_UNSTUFF = 0, DG_STAGE_COEF_CLEAR, DG_STAGE_HUFF_RESTART, DG_STAG
 DG_API const char* dg_last_error(void);
 DG_API const char* dg_version(void);
 
+/* ---- logging and counters --------------------------------------------------------------------------------------------
+ * datago reports every sample it drops through the `log` crate (src/worker_files.rs:63-70, src/worker_wds.rs:134-137) and
+ * lets the embedding process choose the sink (initialize_logging, src/client.rs:253-263).  Here the embedding process
+ * installs a callback; the library calls it from the thread that runs dg_batch_sync / the feeder lanes, once per failed
+ * item (DG_LOG_ERROR: "item 17: truncated (status 3)") and for rare conditions of the library itself (DG_LOG_WARN).
+ * NULL removes the callback (the default: silent).  The callback must not call back into the library. */
+enum { DG_LOG_ERROR = 1, DG_LOG_WARN = 2, DG_LOG_INFO = 3, DG_LOG_DEBUG = 4 };
+typedef void (*dg_log_fn)(int level, const char* message, void* user);
+DG_API void dg_set_log_callback(dg_log_fn fn, void* user);
+
+/* Items a context has finished, by dg_status (index = status code, [0] = succeeded), counted in dg_batch_sync:
+ * the per-reason drop counters a data-loading service exports. */
+#define DG_STATUS_COUNT 13
+typedef struct dg_ctx_counters {
+    uint64_t items[DG_STATUS_COUNT];
+    uint64_t batches, bytes_in, bytes_out;  /* batches synchronised; compressed / raw bytes uploaded; payload bytes produced */
+} dg_ctx_counters;
+
 /* ---- context ------------------------------------------------------------------------------------------------ */
 /* DatagoClient::new builds the transform once (src/client.rs:92-95 -> image_processing.rs:77-120).
  * cfg NULL or crop_and_resize == 0: no transform (payloads are the decoded images).
@@ -148,6 +166,7 @@ DG_API int dg_ctx_create_on_stream(int device, const dg_image_config* cfg, void*
 DG_API void dg_ctx_destroy(dg_ctx* ctx);
 /* The cudaStream_t all work of this ctx is queued on. */
 DG_API void* dg_ctx_stream(dg_ctx* ctx);
+DG_API int dg_ctx_get_counters(dg_ctx* ctx, dg_ctx_counters* out);
 
 /* ---- bucket logic (host only; no device work) ------------------------------------------------------------------- */
 /* build_image_size_list, src/image_processing.rs:188-219: the raw list, duplicates kept. Returns the count. */

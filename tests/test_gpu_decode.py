@@ -184,3 +184,22 @@ def test_forged_frame_size_is_refused_per_item():
     assert res[0][0] == 0 and res[2][0] == 0 and res[1][0] == 11
     assert_same(res[0][1], oracle.jpeg_decode(good))
     assert_same(res[2][1], oracle.jpeg_decode(good))
+
+
+def test_log_callback_and_per_status_counters():
+    # every dropped item is reported once, as datago logs a failed sample (src/worker_files.rs:63-70), and counted by reason
+    rng = np.random.default_rng(14)
+    good = jpeg(rng, 160, 120)
+    lines = []
+    dg.set_log_callback(lambda level, msg: lines.append((level, msg)))
+    try:
+        c = dg.Context(0, None)
+        res = c.process([good, good[: len(good) // 2], b"nope", good])
+        assert [r[0] for r in res] == [0, 3, 4, 0]
+        counts = c.counters()
+        assert counts["items"] == {"ok": 2, "truncated": 1, "bad_marker": 1} and counts["batches"] == 1
+        assert counts["bytes_out"] == 2 * 160 * 120 * 3 and counts["bytes_in"] > 0
+        assert sorted(lines) == [(1, "item 1: truncated (status 3)"), (1, "item 2: bad_marker (status 4)")]
+        c.close()
+    finally:
+        dg.set_log_callback(None)
