@@ -1130,8 +1130,8 @@ __device__ __noinline__ void idct_full_to_tile(const uint4* rows, uint32_t swz, 
     });
 }
 
-// Persistent: CTA b handles tiles b, b + gridDim.x, ...  While a tile is being reconstructed, the inputs of the CTA's
-// next tile are already on their way into shared memory, so no CTA waits for DRAM except on its first tile.
+// CTA b handles tiles b, b + gridDim.x, ...: while a tile is being converted, the inputs of the CTA's next tile (if the
+// grid is smaller than the tile count) are already on their way into shared memory.
 #ifndef DG_FUSED_MIN_CTAS
 #define DG_FUSED_MIN_CTAS (12 / DG_FUSED_MCU_ROWS)
 #endif
@@ -1284,7 +1284,11 @@ void launch_luma_color(const JpegWave& w, uint32_t first_tile, uint32_t count, b
         cudaFuncSetAttribute(k_luma_color, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FusedSmem));
         sm_count[dev] = n > 0 ? n : 148;
     }
-    const uint32_t grid = min(count, (uint32_t)(sm_count[dev] * DG_FUSED_MIN_CTAS));
+    // One CTA per tile.  The kernel also works as a persistent loop over tiles with the next tile's inputs prefetched
+    // (any smaller grid), but measured slower that way: resident CTAs of this kernel then keep the other stream's
+    // entropy decoders off the SMs for a whole launch, and the block scheduler already overlaps tiles across CTAs.
+    const uint32_t grid = count;
+    (void)sm_count;
     k_luma_color<<<grid, kFusedThreads, sizeof(FusedSmem), s>>>(w, first_tile, count, rezero);
 }
 
