@@ -386,6 +386,7 @@ struct WavePlan {
     // descs [fused_first, descs.size()) take the fused 4:2:0 path: prefix sums of their chroma blocks and tiles, and
     // their own launch groups (first chroma block, count, first tile, count)
     uint32_t fused_first = 0;
+    uint32_t n_huge = 0;  // leading entries of spec_list (sorted longest first) with more than kSpecHugeBytes of entropy-coded data
     std::vector<uint32_t> fchroma_first, ftile_first;
     std::vector<std::array<uint32_t, 4>> fgroups;
     std::vector<ConvPass> passes[4];    // H1, V1, H2, V2
@@ -1017,6 +1018,9 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
         // longest streams first: one CTA decodes one image, and the launch ends with its slowest CTA
         std::stable_sort(wv.spec_list.begin(), wv.spec_list.end(),
                          [&](uint32_t a, uint32_t c) { return wv.descs[a].raw_len > wv.descs[c].raw_len; });
+        wv.n_huge = 0;
+        // (at most kSpecHugeMax of them: one such CTA fills an SM, so they trade throughput for a shorter critical path)
+        while (wv.n_huge < wv.spec_list.size() && wv.n_huge < kSpecHugeMax && wv.descs[wv.spec_list[wv.n_huge]].raw_len > kSpecHugeBytes) ++wv.n_huge;
         wv.us_bytes = us; wv.coef_blocks = blocks; wv.plane_bytes = planes; wv.decoded_bytes = decoded; wv.mid_bytes = mids; wv.nseg = segs;
         size_t o = 0;
         wv.off_coef = o; o += align_up(blocks * 128, 256);  // first: the zero prefix of a scratch block is tracked from offset 0
@@ -1364,28 +1368,37 @@ static int batch_run_locked(dg_batch* b) {
             CU(mark(DG_STAGE_COEF_CLEAR, false));
             // The two entropy kernels work on disjoint images and are both latency bound: outside timing mode they run
             // side by side, the restart-interval one on the lane's auxiliary stream.
-            const bool side_by_side = !timing && w.restart_segs.total && w.n_spec;
+            // The auxiliary stream of the lane takes what can run beside the speculative decoder: the restart-interval
+            // decoder, and the speculative decoder's widest CTAs for the few longest images of the wave.
+            const uint32_t n_huge = wv.n_huge;
+            const bool aux_restart = !timing && w.restart_segs.total && w.n_spec;
+            const bool aux_huge = n_huge && w.n_spec > n_huge;  // also in a timing batch: the two launches are one stage
             const int lane = (int)(wi & 1);
+            cudaStream_t aux = ctx->aux[lane];
+            if (w.n_spec) {  // the longest images first: they decide when the stage ends
+                CU(mark(DG_STAGE_HUFF_SPEC, true));
+                if (aux_restart || aux_huge) {
+                    CU(cudaEventRecord(ctx->ev_aux_go[lane], s));
+                    CU(cudaStreamWaitEvent(aux, ctx->ev_aux_go[lane], 0));
+                }
+                launch_huff_spec(w, n_huge, s, aux_huge ? aux : s);
+                b->launches += (n_huge ? 1 : 0) + (w.n_spec > n_huge ? 1 : 0);
+                if (timing && aux_huge) {  // the stage ends when both launches have
+                    CU(cudaEventRecord(ctx->ev_aux_done[lane], aux));
+                    CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
+                }
+                CU(mark(DG_STAGE_HUFF_SPEC, false));
+            }
             if (w.restart_segs.total) {
                 CU(mark(DG_STAGE_HUFF_RESTART, true));
-                if (side_by_side) {
-                    CU(cudaEventRecord(ctx->ev_aux_go[lane], s));
-                    CU(cudaStreamWaitEvent(ctx->aux[lane], ctx->ev_aux_go[lane], 0));
-                    launch_huff_restart(w, ctx->aux[lane]);
-                    CU(cudaEventRecord(ctx->ev_aux_done[lane], ctx->aux[lane]));
-                } else {
-                    launch_huff_restart(w, s);
-                }
+                launch_huff_restart(w, aux_restart ? aux : s);
                 ++b->launches;
                 CU(mark(DG_STAGE_HUFF_RESTART, false));
             }
-            if (w.n_spec) {
-                CU(mark(DG_STAGE_HUFF_SPEC, true));
-                launch_huff_spec(w, s);
-                ++b->launches;
-                CU(mark(DG_STAGE_HUFF_SPEC, false));
+            if (!timing && (aux_restart || aux_huge)) {
+                CU(cudaEventRecord(ctx->ev_aux_done[lane], aux));
+                CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
             }
-            if (side_by_side) CU(cudaStreamWaitEvent(s, ctx->ev_aux_done[lane], 0));
             for (const auto& g : wv.groups) {
                 if (!g[1]) continue;
                 CU(mark(DG_STAGE_IDCT, true));

@@ -46,7 +46,10 @@ struct JpegWave {
 
 void launch_unstuff(const JpegWave& w, cudaStream_t s);
 void launch_huff_restart(const JpegWave& w, cudaStream_t s);
-void launch_huff_spec(const JpegWave& w, cudaStream_t s);
+// the first n_huge images of spec_list (longest first) have more than kSpecHugeBytes of entropy-coded data: they get the
+// widest CTAs, on huge_stream, beside the others on s
+constexpr uint32_t kSpecHugeBytes = 1024 * 2048 / 8, kSpecHugeMax = 64;
+void launch_huff_spec(const JpegWave& w, uint32_t n_huge, cudaStream_t s, cudaStream_t huge_stream);
 // blocks [first, first + count) of the wave / colour tiles [first, first + count): callers may launch them in groups of
 // images (the planes written by the IDCT are then still in L2 when the colour kernel reads them) or once per wave
 // rezero: the kernel writes zeros back over every coefficient row it found non-zero, which leaves the coefficient

@@ -294,19 +294,33 @@ struct SpecState {
 };
 constexpr uint32_t kSyncCheckBits = 256;
 
+template <int T>
+struct SpecSmem {
+    HuffTable tab[6];
+    SpecState<T> st;
+    Scan4 warp[T / 32];
+    uint32_t wcount[T / 32];
+    uint32_t carry_p, carry_slot;
+    int32_t carry_dc[3];
+    uint8_t nat[64];
+};
+
 template <int T, int MIN_CTAS>
-__global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w) {
-    const uint32_t img = w.spec_list[blockIdx.x];
+__global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w, uint32_t first) {
+    const uint32_t img = w.spec_list[first + blockIdx.x];
     const JpegDesc& d = w.descs[img];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    __shared__ __align__(16) HuffTable s_tab[6];
-    __shared__ uint8_t s_nat[64];
-    __shared__ SpecState<T> st;
-    __shared__ Scan4 s_warp[T / 32];
-    __shared__ uint32_t s_wcount[T / 32];
-    __shared__ uint32_t s_carry_p, s_carry_slot;
-    __shared__ int32_t s_carry_dc[3];
+    extern __shared__ __align__(16) unsigned char spec_smem[];
+    SpecSmem<T>& sh = *reinterpret_cast<SpecSmem<T>*>(spec_smem);
+    HuffTable (&s_tab)[6] = sh.tab;
+    uint8_t (&s_nat)[64] = sh.nat;
+    SpecState<T>& st = sh.st;
+    Scan4 (&s_warp)[T / 32] = sh.warp;
+    uint32_t (&s_wcount)[T / 32] = sh.wcount;
+    uint32_t& s_carry_p = sh.carry_p;
+    uint32_t& s_carry_slot = sh.carry_slot;
+    int32_t (&s_carry_dc)[3] = sh.carry_dc;
 
     {   // stage the image's Huffman tables in shared memory (word copies)
         const uint32_t ids[6] = {d.dc_tab[0], d.dc_tab[1], d.dc_tab[2], d.ac_tab[0], d.ac_tab[1], d.ac_tab[2]};
@@ -442,10 +456,31 @@ void launch_huff_restart(const JpegWave& w, cudaStream_t s) {
         k_huff_restart<<<(w.restart_segs.total + kRestartThreads - 1) / kRestartThreads, kRestartThreads, 0, s>>>(w);
 }
 
-void launch_huff_spec(const JpegWave& w, cudaStream_t s) {
+// Three CTA sizes.  A CTA walks its image chunk by chunk (T subsequences each), so the launch lasts as long as the
+// longest image needs chunks: the first `n_huge` images of the list (the longest: more than 1024 subsequences) get
+// 1024-thread CTAs, launched on `huge_stream` beside the rest.
+constexpr int kSpecThreadsHuge = 1024;
+template <int T, int MIN_CTAS>
+static void launch_spec_variant(const JpegWave& w, uint32_t first, uint32_t count, cudaStream_t s) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!configured[dev]) {
+        cudaFuncSetAttribute(k_huff_spec<T, MIN_CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(SpecSmem<T>));
+        configured[dev] = true;
+    }
+    k_huff_spec<T, MIN_CTAS><<<count, T, sizeof(SpecSmem<T>), s>>>(w, first);
+}
+
+void launch_huff_spec(const JpegWave& w, uint32_t n_huge, cudaStream_t s, cudaStream_t huge_stream) {
     if (!w.n_spec) return;
-    if (w.n_spec < kSpecWideBelow) k_huff_spec<kSpecThreadsWide, kSpecMinCtasWide><<<w.n_spec, kSpecThreadsWide, 0, s>>>(w);
-    else k_huff_spec<kSpecThreads, DG_SPEC_MIN_CTAS><<<w.n_spec, kSpecThreads, 0, s>>>(w);
+    n_huge = min(n_huge, w.n_spec);
+    if (n_huge) launch_spec_variant<kSpecThreadsHuge, 1>(w, 0, n_huge, huge_stream);
+    const uint32_t rest = w.n_spec - n_huge;
+    if (!rest) return;
+    if (rest < kSpecWideBelow) launch_spec_variant<kSpecThreadsWide, kSpecMinCtasWide>(w, n_huge, rest, s);
+    else launch_spec_variant<kSpecThreads, DG_SPEC_MIN_CTAS>(w, n_huge, rest, s);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

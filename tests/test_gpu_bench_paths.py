@@ -139,3 +139,19 @@ def test_general_kernels_still_decode_420_images():
     for i, (st, out, _) in enumerate(ctx().process(datas)):
         assert st == 0
         assert_same(out, want[i], f"fused path image {i}")
+
+
+def test_longest_images_take_the_widest_decoder_beside_the_others():
+    # images with more than 1024 subsequences are decoded by 1024-thread CTAs on the lane's auxiliary stream while the
+    # rest of the wave goes through the ordinary variant; alone in a batch they run on the main stream
+    rng = np.random.default_rng(303)
+    big = [synth.encode_jpeg(rng.integers(0, 256, (1024, 1024, 3), dtype=np.uint8), 97, "4:4:4", 0),
+           synth.encode_jpeg(rng.integers(0, 256, (1400, 900, 3), dtype=np.uint8), 95, "4:2:0", 0)]
+    assert all(len(b) > 400_000 for b in big)
+    small = [jpeg(rng, 320, 200), jpeg(rng, 200, 320, rst=3), jpeg(rng, 640, 480, q=95, noise=20.0)]
+    datas = [small[0], big[0], small[1], big[1], small[2]]
+    want = _oracle_all(datas)
+    for batch in (datas, big, [big[1]]):
+        for (st, out, _), d in zip(ctx().process(batch), batch):
+            assert st == 0
+            assert_same(out, want[datas.index(d)], f"{len(d)} bytes")
