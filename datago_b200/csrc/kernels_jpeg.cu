@@ -169,8 +169,10 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
                                             int32_t& dc2, const HuffCtx& hc, int16_t* __restrict__ coef,
                                             const uint32_t slot_abs, const uint8_t* __restrict__ natural, uint32_t& err) {
     auto word = [&](uint32_t i) -> uint32_t { return i < nwords ? __byte_perm(__ldg(words + i), 0, 0x0123) : 0u; };
+    // a window of three stream words: the word fetched when the position crosses a word boundary is first needed one
+    // boundary later, so its latency (the streams sit in global memory) stays off the symbol-to-symbol critical path
     uint32_t wi = p >> 5;
-    uint32_t w0 = word(wi), w1 = word(wi + 1);
+    uint32_t w0 = word(wi), w1 = word(wi + 1), w2 = word(wi + 2);
     while (p < end_bit && nslots < max_slots) {
         const uint32_t top = __funnelshift_l(w1, w0, p & 31u);
         const uint32_t z = slotmod & 63u, c = slotmod >> 6;
@@ -205,7 +207,7 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
         slotmod += adv;
         if (slotmod >= hc.mcu_slots) slotmod -= hc.mcu_slots;
         const uint32_t nwi = p >> 5;
-        if (nwi != wi) { w0 = w1; w1 = word(nwi + 1); wi = nwi; }
+        if (nwi != wi) { w0 = w1; w1 = w2; w2 = word(nwi + 2); wi = nwi; }  // a symbol has at most 27 bits: one boundary at a time
     }
 }
 
@@ -346,7 +348,7 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w, uint32_t 
     const uint32_t total_slots = d.nblocks * 64u;
     const uint32_t nsub = (total_bits + kSubseqBits - 1) / kSubseqBits;
     const uint32_t* words = reinterpret_cast<const uint32_t*>(w.us + d.us_off);
-    const uint32_t nwords = (us_len + 3) / 4 + 2;
+    const uint32_t nwords = (us_len + 3) / 4 + 2;  // the unstuffed stream is followed by 16 zero bytes
     int16_t* coef = w.coef + d.block_off * 64;
     uint32_t err = 0;
 
