@@ -13,6 +13,7 @@
 //               tile's rows are staged in shared memory as ready-made pairs.
 // Vertical passes over unaligned or unpadded rows take the plain 4-byte path.
 #include <cstdint>
+#include <type_traits>
 
 #include "kernels.h"
 
@@ -142,62 +143,63 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
 // pixel x when k % C == c and zero otherwise.  The 16-bit weights are split into a signed high and an unsigned low
 // byte, w = 256 hi + lo, so that the product runs on the 8-bit integer tensor-core path with 32-bit accumulation:
 // out = 256 (src x hi) + (src x lo), which is exact -- the result equals the dp2a kernel's bit for bit.
-//   CTA  = one strip of 64 output bytes x up to 2048 rows of one pass; warp q owns output bytes 8q .. 8q+7 of the strip.
+//   CTA  = one strip of 64 output bytes x up to 2048 rows of one pass; warp q of the first eight owns output bytes
+//          8q .. 8q+7 of the strip, four more warps only copy.
 //   B    = the warp's slice of Wt (source bytes under its eight outputs, at most 256), both limbs: every lane gathers its
 //          mma.m16n8k32 fragments from the filter table once and keeps them in registers for all rows of the CTA;
 //   A    = 32 source rows of the strip's band per chunk, brought in by 16-byte asynchronous copies into a ring of up to
 //          four chunks (the planner only sends passes here whose source rows start on 16-byte boundaries), so the copies
 //          of the next chunks are in flight while a chunk is multiplied; read with ldmatrix;
-//   D    = two 16-row tiles per warp and chunk; merged, rounded, saturated, turned by 90 degrees through the warp's own
-//          piece of shared memory and written out as eight bytes per row.  Warps never wait for each other: the only
-//          synchronisation in the loop is the pair of barriers of each ring slot.
+//   D    = two 16-row tiles per warp and chunk; merged, rounded, saturated, collected in a 32 x 64 byte tile of shared
+//          memory and written out as whole 64-byte row pieces (one store instruction covers four rows; eight-byte
+//          stores of single tiles, 32 rows per instruction, cost a third more time).  The multiplying warps meet at one
+//          named barrier per chunk for that; the copying warps only ever wait on the ring slots' barriers.
 // The interleaved channel layout costs two thirds of the multiplies (zeros in Wt), which the tensor cores have to
 // spare; in exchange the source needs no de-interleaving and the result is produced in its final byte order.
 constexpr int kHMmaConsumers = 256;   // eight warps multiply
-constexpr int kHMmaProducers = 64;    // two warps only move source rows into the ring
+constexpr int kHMmaProducers = 128;   // four warps only move source rows into the ring
 constexpr int kHMmaThreads = kHMmaConsumers + kHMmaProducers;
 constexpr int kHMmaChunk = 32;                       // rows per chunk (two mma row tiles)
 constexpr int kHMmaRing = 98304;                     // bytes of the A ring: two CTAs per SM keep ~190 KB of source rows in flight
 constexpr int kHMmaMaxStages = 8;
+constexpr int kHMmaOutPitch = kHMmaStrip + 8;         // 18 words: the tiles' two-byte writes fall into different banks
 
 struct HMmaSmem {
-    uint8_t out[kHMmaConsumers / 32][kHMmaChunk][8];  // per warp: the eight output bytes of a chunk's rows, before they go out row by row
+    uint8_t out[2][kHMmaChunk][kHMmaOutPitch];  // a chunk's output bytes, before they go out as 64-byte row pieces
     uint8_t A[kHMmaRing];
 };
 static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 32) <= kHMmaRing, "the ring must hold two chunks of the widest band");
 
+// ldmatrix stays ordered after the wait on the ring slot (volatile, memory); the multiplies are pure register functions
+// that the compiler may move between the loads
+__device__ __forceinline__ void load_a(uint32_t (&a)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(addr) : "memory");
+}
 __device__ __forceinline__ void mma_u8s8(int32_t (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma_u8u8(int32_t (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// mbarrier helpers: one barrier per ring slot counts the bytes of the bulk copies into it
+// mbarrier helpers: two barriers per ring slot, "filled" (the copies into it have landed) and "drained"
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    // the last operand lets the hardware park the thread for up to that many nanoseconds instead of returning at once
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(bar), "r"(parity), "r"(2000u) : "memory");
     return done != 0;
 }
-// one row of a chunk: `bytes` (a multiple of 16) from 16-byte aligned global memory to 16-byte aligned shared memory
-__device__ __forceinline__ void bulk_copy_row(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-constexpr uint32_t kHMmaWaitLimit = 1u << 22;  // polls of a ring slot's barrier before a CTA gives up on it
+constexpr uint32_t kHMmaWaitLimit = 1u << 20;  // waits of up to 2 us each on a ring slot's barrier before a CTA gives up on it
 
 __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
                                                                 unsigned int* timeouts) {
@@ -245,7 +247,7 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
     }
     __syncthreads();
 
-    // Ring protocol.  Chunk c (rows y_first + 32 c ...) lives in slot c % nstage.  The two producer warps fill a slot
+    // Ring protocol.  Chunk c (rows y_first + 32 c ...) lives in slot c % nstage.  The four producer warps fill a slot
     // with 16-byte asynchronous copies and let the slot's "filled" barrier count them in (one deferred arrival per
     // producer thread); a consumer warp waits for "filled", multiplies, and arrives on the slot's "drained" barrier,
     // which the producers wait for before they fill the slot again.  Every wait is bounded: a CTA that runs out of
@@ -260,15 +262,16 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
         }
     };
     if (warp >= kHMmaConsumers / 32) {
-        // ---- producers: thread q of 64 copies pieces q % 2, q % 2 + 2, ... of row q / 2 of every chunk
-        const uint32_t q = threadIdx.x - kHMmaConsumers, r = q >> 1;
+        // ---- producers: thread q of 128 copies pieces q % 4, q % 4 + 4, ... of row q / 4 of every chunk
+        constexpr uint32_t kPer = kHMmaProducers / kHMmaChunk;  // threads per row
+        const uint32_t q = threadIdx.x - kHMmaConsumers, r = q / kPer;
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint32_t slot = c % nstage, use = c / nstage;
             if (use > 0) wait_for(bar0 + 8 * (kHMmaMaxStages + slot), (use - 1) & 1u);
             const uint32_t y = min(y_first + c * kHMmaChunk + r, out_h - 1);  // rows past the end repeat the last one
             const uint8_t* src = p_src + (size_t)y * src_pitch + strip_lo;
             const uint32_t dst = a_base + slot * stage_bytes + r * pitch_a;
-            for (uint32_t v = q & 1u; v < span16; v += 2)
+            for (uint32_t v = q % kPer; v < span16; v += kPer)
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + v * 16), "l"(src + v * 16) : "memory");
             // the barrier counts this thread in once the copies it has issued so far have landed
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * slot) : "memory");
@@ -314,6 +317,10 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
             bfr[ks][0] = hi[0]; bfr[ks][1] = hi[1]; bfr[ks][2] = lo[0]; bfr[ks][3] = lo[1];
         }
     }
+    // The chunk loop is compiled once per number of k steps, so that the multiplies of a chunk form one straight run
+    // of loads and tensor-core instructions.
+    auto consume = [&](auto ks_tag) {
+    constexpr int KS = decltype(ks_tag)::value;
     for (uint32_t c = 0; c < nchunks; ++c) {
         const uint32_t slot = c % nstage;
         wait_for(bar0 + 8 * slot, (c / nstage) & 1u);  // chunk c is the (c / nstage)-th filling of its slot
@@ -324,26 +331,30 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
             for (int i = 0; i < 4; ++i) { acc_hi[mt][i] = 0; acc_lo[mt][i] = half; }
         if (warp_active) {
             const uint32_t a_addr = a_base + slot * stage_bytes + a_lane;
+            uint32_t a[2][2][4];  // [k step parity][row tile]
+            load_a(a[0][0], a_addr);
+            load_a(a[0][1], a_addr + 16 * pitch_a);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                if ((uint32_t)ks < ksteps) {
+            for (int ks = 0; ks < KS; ++ks) {
+                // the fragments of the next k step are requested before this step's multiplies are issued
+                if (ks + 1 < KS) {
+                    load_a(a[(ks + 1) & 1][0], a_addr + (ks + 1) * 32);
+                    load_a(a[(ks + 1) & 1][1], a_addr + 16 * pitch_a + (ks + 1) * 32);
+                }
 #pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) {
-                        uint32_t a[4];
-                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]) : "r"(a_addr + (uint32_t)mt * 16 * pitch_a + ks * 32));
-                        mma_u8s8(acc_hi[mt], a, bfr[ks][0], bfr[ks][1]);
-                        mma_u8u8(acc_lo[mt], a, bfr[ks][2], bfr[ks][3]);
-                    }
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma_u8s8(acc_hi[mt], a[ks & 1][mt], bfr[ks][0], bfr[ks][1]);
+                    mma_u8u8(acc_lo[mt], a[ks & 1][mt], bfr[ks][2], bfr[ks][3]);
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar0 + 8 * (kHMmaMaxStages + slot));  // this warp is done with the slot
+        // ---- merge the limbs, round, saturate; accumulator i of a tile is row g + 8 (i / 2), output byte 2 t + i % 2.
+        //      The chunk's 32 x 64 bytes are collected in shared memory (two buffers in turn, so that one barrier of the
+        //      multiplying warps per chunk is enough) and leave as whole 64-byte row pieces, four rows per warp.
+        uint8_t (*ob)[kHMmaOutPitch] = sm.out[c & 1];
         if (warp_active) {
-            // ---- merge the limbs, round, saturate; accumulator i of a tile is row g + 8 (i / 2), output byte 2 t + i % 2.
-            //      The warp's 32 x 8 bytes pass through its own piece of shared memory, so that a lane can write out the
-            //      eight bytes of one row.
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -352,24 +363,37 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
                     const int32_t v1 = (acc_hi[mt][2 * h + 1] * 256 + acc_lo[mt][2 * h + 1]) >> precision;
                     uint32_t pk;
                     asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(pk) : "r"(v1), "r"(v0), "r"(0));
-                    *reinterpret_cast<uint16_t*>(&sm.out[warp][mt * 16 + g + 8 * h][2 * t4]) = (uint16_t)pk;
+                    *reinterpret_cast<uint16_t*>(&ob[mt * 16 + g + 8 * h][warp * 8 + 2 * t4]) = (uint16_t)pk;
                 }
-            __syncwarp();
-            const uint32_t y = y_first + c * kHMmaChunk + lane;
-            if (y < y_end) {
-                const uint2 v = *reinterpret_cast<const uint2*>(&sm.out[warp][lane][0]);
-                uint8_t* o = p_dst + (size_t)y * dst_pitch + jn0;
-                if (dst8 && jn0 + 8 <= row_bytes) {
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kHMmaConsumers) : "memory");
+        {
+            const uint32_t row = warp * 4 + (lane >> 3), jb = j0 + (lane & 7u) * 8;
+            const uint32_t y = y_first + c * kHMmaChunk + row;
+            if (y < y_end && jb < row_bytes) {
+                const uint2 v = *reinterpret_cast<const uint2*>(&ob[row][(lane & 7u) * 8]);
+                uint8_t* o = p_dst + (size_t)y * dst_pitch + jb;
+                if (dst8 && jb + 8 <= row_bytes) {
                     *reinterpret_cast<uint2*>(o) = v;
                 } else {
-                    const uint32_t nb = min(8u, row_bytes - jn0);
+                    const uint32_t nb = min(8u, row_bytes - jb);
 #pragma unroll
                     for (int kb = 0; kb < 8; ++kb)
                         if ((uint32_t)kb < nb) o[kb] = (uint8_t)((kb < 4 ? v.x : v.y) >> (8 * (kb & 3)));
                 }
             }
-            __syncwarp();  // the warp's piece of shared memory is rewritten by the next chunk
         }
+    }
+    };
+    switch (ksteps) {
+        case 1: consume(std::integral_constant<int, 1>{}); break;
+        case 2: consume(std::integral_constant<int, 2>{}); break;
+        case 3: consume(std::integral_constant<int, 3>{}); break;
+        case 4: consume(std::integral_constant<int, 4>{}); break;
+        case 5: consume(std::integral_constant<int, 5>{}); break;
+        case 6: consume(std::integral_constant<int, 6>{}); break;
+        case 7: consume(std::integral_constant<int, 7>{}); break;
+        default: consume(std::integral_constant<int, 8>{}); break;
     }
     if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
 }
