@@ -557,10 +557,13 @@ def main():
     import datago_b200 as dg
 
     torch.cuda.set_device(local_rank)
+    # several ranks on one box: host threads and the page-locked staging memory of each rank next to its GPU (a box may
+    # have more than one socket).  A single rank keeps all cores: the CPU baseline of the same run uses them.
+    bound = dg.bind_to_gpu_cpus(local_rank) if world > 1 and os.environ.get("DATAGO_B200_BENCH_BIND", "1") != "0" else None
+    print(f"[bench] rank {rank}: host cores {'unchanged' if bound is None else f'{bound[0]}..{bound[-1]} ({len(bound)})'}", file=sys.stderr)
     # stdout carries the one JSON line: keep NCCL's own banner (NCCL_DEBUG=VERSION) and debug text off it
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 

@@ -208,6 +208,35 @@ def _check(rc):
 _log_keep = None
 
 
+def bind_to_gpu_cpus(device):
+    """Restricts the calling process (and the threads it starts afterwards: the library's host pool, Python workers) to
+    the host cores NVML reports as local to CUDA device `device`, so that the page-locked staging memory the library
+    allocates is placed on that socket and the device-to-host copies of one rank do not cross the inter-socket link.  To
+    be called before the first Context of the process.  Changes nothing on the GPU.  Returns the cores, or None when NVML,
+    the PCI id or a non-empty intersection with the current affinity mask is not available (nothing is changed then)."""
+    import os
+    try:
+        import pynvml
+        import torch
+        pr = torch.cuda.get_device_properties(device)
+        bus_id = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        pynvml.nvmlInit()
+        try:
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+            words = (max(os.sched_getaffinity(0)) + 64) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(h, max(words, 16))
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = {64 * i + b for i, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return sorted(cpus)
+    except Exception:  # noqa: BLE001 - a missing NVML, an old torch, a container without the call: all mean "do not bind"
+        return None
+
+
 def set_log_callback(fn):
     """fn(level, message) receives one line per dropped item (level 1 = error) and the library's own warnings;
     None removes it.  The counterpart of the `log` records datago writes for failed samples."""
