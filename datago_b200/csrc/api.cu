@@ -4,6 +4,7 @@
 // staged in pinned memory and uploaded with a handful of large copies, and its images run through the kernels
 // in "waves": groups of images whose intermediates (unstuffed streams, coefficients, planes, full-size decoded
 // images, resize intermediates) share one scratch block that the next wave reuses.
+#include <cuda.h>  // CUtensorMap and the enumerations of cuTensorMapEncodeTiled; the entry point itself comes through the runtime
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -178,6 +179,20 @@ struct dg_ctx {
     uint64_t max_image_bytes = (uint64_t)512 << 20;
 };
 
+// cuTensorMapEncodeTiled, looked up through the runtime (the library does not link against the driver library).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static const EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
 static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool have_stream, dg_ctx** out) {
     if (!out) return fail(DG_E_INVALID, "out is NULL");
     *out = nullptr;
@@ -220,6 +235,7 @@ static int ctx_create(int device, const dg_image_config* cfg, void* stream, bool
     if (const char* mb = getenv("DATAGO_B200_TABLE_CACHE_MB")) { long v = atol(mb); if (v >= 0) c->table_cache_cap = (size_t)v << 20; }
     if (const char* v = getenv("DATAGO_B200_FUSED")) c->fused_path = atoi(v) != 0;
     if (const char* v = getenv("DATAGO_B200_HMMA")) c->hmma = atoi(v) != 0;
+    if (!encode_tiled_fn()) c->hmma = false;  // a driver without tensor maps: every horizontal pass takes the dp2a kernel
     if (const char* mb = getenv("DATAGO_B200_MAX_IMAGE_MB")) { long v = atol(mb); if (v >= 1) c->max_image_bytes = (uint64_t)v << 20; }
     if (const char* mb = getenv("DATAGO_B200_WAVE_MB")) { long v = atol(mb); if (v >= 16) c->wave_bytes = (size_t)v << 20; }
     *out = c;
@@ -455,6 +471,8 @@ namespace {
 struct Planner {
     dg_ctx* ctx;
     dg_batch* b;
+    bool final_round = true;   // device addresses are final: tensor maps are encoded (the sizing round skips them)
+    bool tmap_failed = false;  // a tensor map could not be encoded
     std::unordered_map<std::string, uint32_t> huff_ids, qt_ids;
     std::vector<HuffTable> huff_pool;
     std::vector<uint32_t> qt_pool;  // 32 words per table, the layout JpegWave::qt32 documents
@@ -597,14 +615,39 @@ struct PassDraft {
 
 // Whether the tensor-core horizontal pass can take outputs [t0, t0 + out_w) of table T: the source bytes under every
 // 8-byte output tile and under every 64-byte strip must fit what a CTA stages (see conv_h_mma in kernels_resize.cu).
-static bool hmma_fits(const FilterTable& T, uint32_t t0, uint32_t out_w, uint32_t C, int32_t origin) {
+static bool hmma_fits(const FilterTable& T, uint32_t t0, uint32_t out_w, uint32_t C, int32_t origin, uint32_t* box_pieces) {
     const uint32_t row_bytes = out_w * C;
     auto lo = [&](uint32_t j) { return ((T.start[t0 + j / C] - origin) * (int32_t)C) & ~15; };
     auto hi = [&](uint32_t j) { const uint32_t x = std::min(out_w - 1, j / C); return (T.start[t0 + x] + T.size[t0 + x] - origin) * (int32_t)C; };
     for (uint32_t j = 0; j < row_bytes; j += 8)
         if (hi(j + 7) - lo(j) > (int32_t)kHMmaMaxBand) return false;
-    for (uint32_t j = 0; j < row_bytes; j += kHMmaStrip)
-        if (hi(j + kHMmaStrip - 1) - lo(j) > (int32_t)kHMmaMaxSpan) return false;
+    int32_t widest = 0;
+    for (uint32_t j = 0; j < row_bytes; j += kHMmaStrip) {
+        if (lo(j) < 0) return false;  // the copy's first coordinate
+        widest = std::max(widest, hi(j + kHMmaStrip - 1) - lo(j));
+    }
+    if (widest > (int32_t)kHMmaMaxSpan) return false;
+    *box_pieces = ((uint32_t)(widest + 15) / 16) | 1u;  // odd: the staged rows then start in different shared-memory banks
+    return true;
+}
+
+// The source of a tensor-core horizontal pass as rows of 32-bit words: `rows` rows of `pitch` bytes from `src` (16-byte
+// aligned, pitch a multiple of 16); one copy brings box_pieces * 16 bytes of 32 consecutive rows.  Words and rows outside
+// the array read as zero (the kernel multiplies them by zero weights or never stores their results).
+static bool encode_source_map(ConvPass& cp) {
+    static_assert(sizeof(CUtensorMap) == sizeof(cp.tmap), "tensor map size");
+    const EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {cp.src_pitch / 4, cp.out_h};
+    const cuuint64_t gstride[1] = {cp.src_pitch};
+    const cuuint32_t box[2] = {cp.box_pieces * 4, 32};
+    const cuuint32_t estride[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(cp.src), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    memcpy(cp.tmap, &m, sizeof m);
     return true;
 }
 
@@ -677,7 +720,10 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
         if (horizontal) {
             cp.fast = 1;
             if (guarded) { cp.guard_lo = src; cp.guard_hi = src + (size_t)w * h * C; }
-            else if (pl.ctx->hmma && (((uintptr_t)s | spitch) & 15) == 0 && hmma_fits(*T, t0, out_w, C, origin)) cp.fast = 2;
+            else if (pl.ctx->hmma && (((uintptr_t)s | spitch) & 15) == 0 && hmma_fits(*T, t0, out_w, C, origin, &cp.box_pieces)) {
+                cp.fast = 2;
+                if (pl.final_round && !encode_source_map(cp)) pl.tmap_failed = true;
+            }
         } else {
             const uintptr_t bits = (uintptr_t)s | (uintptr_t)d | spitch | dpitch;
             cp.fast = (bits & 15) == 0 && (uint32_t)T->window <= kVFastMaxWindow && (size_t)align_up((size_t)out_w * C, 16) <= spitch &&
@@ -1065,6 +1111,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
     }
     for (int round = 0; round < 2; ++round) {
         uint8_t* baseP = round == 0 ? b->d_scratch : b->d_persist;
+        pl.final_round = round == 1;
         for (size_t wi = 0; wi < b->waves.size(); ++wi) {
             WavePlan& wv = b->waves[wi];
             uint8_t* const kBaseS = (wi & 1) ? b->d_scratch2 : b->d_scratch;
@@ -1148,7 +1195,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.m_fchroma = put_owner_map(m, wv.fchroma_first);
             wv.m_ftile = put_owner_map(m, wv.ftile_first);
             for (int s = 0; s < 4; ++s) {
-                wv.m_passes[s] = m.put(wv.passes[s], 16);
+                wv.m_passes[s] = m.put(wv.passes[s], 64);
                 if (wv.pass_first[s].empty()) wv.pass_first[s].push_back(0);
                 wv.m_pass[s] = put_owner_map(m, wv.pass_first[s]);
             }
@@ -1178,6 +1225,7 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             if (!pointers) break;
         }
     }
+    if (pl.tmap_failed) return abandon(b, fail(DG_E_CUDA, "cuTensorMapEncodeTiled rejected the source of a horizontal resize pass"));
 
     // ---- pinned staging: [status zeros | blob | raw pixel inputs] + meta ------------------------------------------
     // Raw inputs are staged too: a copy from pageable caller memory is serialised by the driver at a fraction of the
@@ -1736,7 +1784,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
             wv.pass_first[s].push_back(t);
             if (!(s & 1) && cp.fast == 2) wv.mma_tiles[s] = t;
         }
-        m_passes[s] = m.put(wv.passes[s], 16);
+        m_passes[s] = m.put(wv.passes[s], 64);
         m_pass[s] = put_owner_map(m, wv.pass_first[s]);
     }
     {

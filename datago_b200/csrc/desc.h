@@ -79,12 +79,17 @@ struct ConvPass {
     uint32_t tile_first;            // first CTA tile of this pass in the launch (prefix sum)
     uint32_t tiles_x;               // tiles per row of tiles
     uint32_t fast;                  // vertical: 1 = the vectorised path applies; horizontal: 2 = the tensor-core path (see kernels_resize.cu)
-    uint32_t pad;
+    uint32_t box_pieces;            // tensor-core path: 16-byte pieces per staged source row (odd), the width of the tensor map's box
     // Set when `src` is memory the library does not own (no slack behind it): the horizontal pass then loads no byte
     // outside [guard_lo, guard_hi).  Both null for sources inside the library's own padded arenas.
     const uint8_t* guard_lo;
     const uint8_t* guard_hi;
+    // Tensor-core path: the CUtensorMap (128 opaque bytes, written by cuTensorMapEncodeTiled) of the pass's source as a
+    // two-dimensional array of 32-bit words, box = box_pieces * 4 words x 32 rows; the copying thread of a CTA hands its
+    // address to cp.async.bulk.tensor.  Unused (zero) for every other pass.
+    alignas(64) unsigned char tmap[128];
 };
+static_assert(sizeof(ConvPass) % 64 == 0, "passes are stored as an array: every tensor map must stay 64-byte aligned");
 
 struct CopyJob {  // identity payloads / pitch removal
     const uint8_t* src;

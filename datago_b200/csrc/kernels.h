@@ -84,7 +84,7 @@ constexpr uint32_t kVFastBytes = 1024, kVFastRows = 32; // vertical pass, vector
 constexpr uint32_t kVFastMaxWindow = 128;
 // horizontal pass on the tensor cores (ConvPass::fast == 2): output bytes per strip x rows per CTA; limits of what a CTA
 // can stage -- source bytes under one 8-byte output tile, and under a whole strip
-constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 2048, kHMmaMaxBand = 256, kHMmaMaxSpan = 1024;
+constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 2048, kHMmaMaxBand = 256, kHMmaMaxSpan = 1008;  // span: 63 pieces of 16 bytes = 252 words, inside the 256 elements a tensor-map box may have
 inline uint32_t conv_tiles_x(const ConvPass& p, bool vertical) {
     if (!vertical && p.fast == 2) return (p.out_w * p.channels + kHMmaStrip - 1) / kHMmaStrip;
     if (!vertical) return (p.out_w + kConvTileW - 1) / kConvTileW;

@@ -144,12 +144,13 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
 // byte, w = 256 hi + lo, so that the product runs on the 8-bit integer tensor-core path with 32-bit accumulation:
 // out = 256 (src x hi) + (src x lo), which is exact -- the result equals the dp2a kernel's bit for bit.
 //   CTA  = one strip of 64 output bytes x up to 2048 rows of one pass; warp q of the first eight owns output bytes
-//          8q .. 8q+7 of the strip, four more warps only copy.
+//          8q .. 8q+7 of the strip, one thread of a ninth warp issues the copies.
 //   B    = the warp's slice of Wt (source bytes under its eight outputs, at most 256), both limbs: every lane gathers its
 //          mma.m16n8k32 fragments from the filter table once and keeps them in registers for all rows of the CTA;
-//   A    = 32 source rows of the strip's band per chunk, brought in by 16-byte asynchronous copies into a ring of up to
-//          four chunks (the planner only sends passes here whose source rows start on 16-byte boundaries), so the copies
-//          of the next chunks are in flight while a chunk is multiplied; read with ldmatrix;
+//   A    = 32 source rows of the strip's band per chunk, brought in by one tensor-map copy (cp.async.bulk.tensor, box of
+//          box_pieces * 16 bytes x 32 rows; the planner only sends passes here whose source rows start on 16-byte
+//          boundaries) into a ring of up to eight chunks, so the copies of the next chunks are in flight while a chunk is
+//          multiplied; read with ldmatrix;
 //   D    = two 16-row tiles per warp and chunk; merged, rounded, saturated, collected in a 32 x 64 byte tile of shared
 //          memory and written out as whole 64-byte row pieces (one store instruction covers four rows; eight-byte
 //          stores of single tiles, 32 rows per instruction, cost a third more time).  The multiplying warps meet at one
@@ -157,7 +158,7 @@ __device__ __forceinline__ void conv_h_rows(const ConvPass& p, const Table& tb, 
 // The interleaved channel layout costs two thirds of the multiplies (zeros in Wt), which the tensor cores have to
 // spare; in exchange the source needs no de-interleaving and the result is produced in its final byte order.
 constexpr int kHMmaConsumers = 256;   // eight warps multiply
-constexpr int kHMmaProducers = 128;   // four warps only move source rows into the ring
+constexpr int kHMmaProducers = 32;    // one more warp, of which one thread issues the copies into the ring
 constexpr int kHMmaThreads = kHMmaConsumers + kHMmaProducers;
 constexpr int kHMmaChunk = 32;                       // rows per chunk (two mma row tiles)
 constexpr int kHMmaRing = 98304;                     // bytes of the A ring: two CTAs per SM keep ~190 KB of source rows in flight
@@ -168,7 +169,7 @@ struct HMmaSmem {
     uint8_t out[2][kHMmaChunk][kHMmaOutPitch];  // a chunk's output bytes, before they go out as 64-byte row pieces
     uint8_t A[kHMmaRing];
 };
-static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 32) <= kHMmaRing, "the ring must hold two chunks of the widest band");
+static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 16) <= kHMmaRing, "the ring must hold two chunks of the widest band");
 
 // ldmatrix stays ordered after the wait on the ring slot (volatile, memory); the multiplies are pure register functions
 // that the compiler may move between the loads
@@ -189,6 +190,15 @@ __device__ __forceinline__ void mma_u8u8(int32_t (&d)[4], const uint32_t (&a)[4]
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {  // one arrival that also announces `bytes` of copies
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// One box of a two-dimensional tensor map into shared memory; (x, y) in elements / rows, x * element size a multiple
+// of 16 bytes.  The barrier receives the box's bytes as they land.
+__device__ __forceinline__ void tensor_copy_2d(uint32_t dst, const void* map, int32_t x, int32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -203,15 +213,14 @@ constexpr uint32_t kHMmaWaitLimit = 1u << 20;  // waits of up to 2 us each on a 
 
 __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
                                                                 unsigned int* timeouts) {
-    extern __shared__ __align__(16) unsigned char conv_h_smem[];
+    extern __shared__ __align__(128) unsigned char conv_h_smem[];
     HMmaSmem& sm = *reinterpret_cast<HMmaSmem*>(conv_h_smem);
     __shared__ __align__(8) unsigned long long s_bar[2 * kHMmaMaxStages];  // per ring slot: "filled" (bytes arrived) and "drained" (all warps done reading)
     const ConvPass& pg = passes[owner_of_tile(map, blockIdx.x)];
     // everything the loops need from the descriptor, once (the asynchronous-copy statements below are memory barriers
     // for the compiler, which would otherwise fetch these fields again after each of them)
-    const uint8_t* const p_src = pg.src;
     uint8_t* const p_dst = pg.dst;
-    const uint32_t src_pitch = pg.src_pitch, dst_pitch = pg.dst_pitch, out_w = pg.out_w, out_h = pg.out_h, C = pg.channels;
+    const uint32_t dst_pitch = pg.dst_pitch, out_w = pg.out_w, out_h = pg.out_h, C = pg.channels;
     const uint32_t t0 = pg.t0, tab_n = pg.tab_n, precision = pg.precision, tiles_x = pg.tiles_x;
     const int32_t origin = pg.src_origin;
     const uint32_t tile = blockIdx.x - pg.tile_first;
@@ -222,12 +231,12 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
     const uint32_t j0 = tx * kHMmaStrip;                          // first output byte of the strip
     const uint32_t jn0 = j0 + warp * 8;                           // ... of this warp's tile
     const uint32_t y_first = ty * kHMmaRows, y_end = min(out_h, y_first + kHMmaRows);
-    // source byte range of the strip, in bytes from the start of a source row of the pass
-    const uint32_t xs0 = j0 / C, xs1 = min(out_w - 1, (j0 + kHMmaStrip - 1) / C);
+    // first source byte of the strip, from the start of a source row of the pass (a multiple of 16)
+    const uint32_t xs0 = j0 / C;
     const int32_t strip_lo = ((__ldg(tb.start + t0 + xs0) - origin) * (int32_t)C) & ~15;
-    const int32_t strip_hi = (__ldg(tb.start + t0 + xs1) + __ldg(tb.size + t0 + xs1) - origin) * (int32_t)C;
-    const uint32_t span16 = (uint32_t)(strip_hi - strip_lo + 15) >> 4;   // 16-byte pieces per staged row
-    const uint32_t pitch_a = (span16 | 1u) * 16;                         // an odd number of pieces: ldmatrix rows hit different banks
+    // staged rows: the box width of the pass's tensor map, an odd number of 16-byte pieces (ldmatrix rows then hit
+    // different banks) that covers the widest strip of the pass
+    const uint32_t pitch_a = pg.box_pieces * 16;
     const uint32_t stage_bytes = kHMmaChunk * pitch_a;
     const uint32_t nstage = min((uint32_t)kHMmaMaxStages, (uint32_t)kHMmaRing / stage_bytes);  // >= 2 by the planner's span limit
     // ... and of this warp's eight output bytes (a warp past the end of the row has no tile)
@@ -242,16 +251,16 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
     }
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&s_bar[0]);
     if (threadIdx.x == 0) {
-        for (uint32_t i = 0; i < (uint32_t)kHMmaMaxStages; ++i) { mbar_init(bar0 + 8 * i, kHMmaProducers); mbar_init(bar0 + 8 * (kHMmaMaxStages + i), kHMmaConsumers / 32); }
+        for (uint32_t i = 0; i < (uint32_t)kHMmaMaxStages; ++i) { mbar_init(bar0 + 8 * i, 1); mbar_init(bar0 + 8 * (kHMmaMaxStages + i), kHMmaConsumers / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    // Ring protocol.  Chunk c (rows y_first + 32 c ...) lives in slot c % nstage.  The four producer warps fill a slot
-    // with 16-byte asynchronous copies and let the slot's "filled" barrier count them in (one deferred arrival per
-    // producer thread); a consumer warp waits for "filled", multiplies, and arrives on the slot's "drained" barrier,
-    // which the producers wait for before they fill the slot again.  Every wait is bounded: a CTA that runs out of
-    // patience counts a timeout (reported by the host) instead of hanging the GPU.
+    // Ring protocol.  Chunk c (rows y_first + 32 c ...) lives in slot c % nstage.  The copying thread announces the
+    // box's bytes on the slot's "filled" barrier and issues one tensor-map copy, which reports to that barrier; a
+    // multiplying warp waits for "filled", multiplies, and arrives on the slot's "drained" barrier, which the copying
+    // thread waits for before it fills the slot again.  Every wait is bounded: a CTA that runs out of patience counts a
+    // timeout (reported by the host) instead of hanging the GPU.
     const uint32_t nchunks = (y_end - y_first + kHMmaChunk - 1) / kHMmaChunk;
     const uint32_t a_base = (uint32_t)__cvta_generic_to_shared(sm.A);
     bool gave_up = false;
@@ -262,22 +271,22 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
         }
     };
     if (warp >= kHMmaConsumers / 32) {
-        // ---- producers: thread q of 128 copies pieces q % 4, q % 4 + 4, ... of row q / 4 of every chunk
-        constexpr uint32_t kPer = kHMmaProducers / kHMmaChunk;  // threads per row
-        const uint32_t q = threadIdx.x - kHMmaConsumers, r = q / kPer;
-        for (uint32_t c = 0; c < nchunks; ++c) {
+        // ---- the copying thread
+        if (lane != 0) return;
+        const void* map = pg.tmap;
+        // the descriptor sits in global memory that earlier batches may have used for other descriptors
+        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(map) : "memory");
+        const int32_t x_word = strip_lo >> 2;
+        for (uint32_t c = 0; c < nchunks && !gave_up; ++c) {
             const uint32_t slot = c % nstage, use = c / nstage;
             if (use > 0) wait_for(bar0 + 8 * (kHMmaMaxStages + slot), (use - 1) & 1u);
-            const uint32_t y = min(y_first + c * kHMmaChunk + r, out_h - 1);  // rows past the end repeat the last one
-            const uint8_t* src = p_src + (size_t)y * src_pitch + strip_lo;
-            const uint32_t dst = a_base + slot * stage_bytes + r * pitch_a;
-            for (uint32_t v = q % kPer; v < span16; v += kPer)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + v * 16), "l"(src + v * 16) : "memory");
-            // the barrier counts this thread in once the copies it has issued so far have landed
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar0 + 8 * slot) : "memory");
+            if (gave_up) break;
+            mbar_expect_tx(bar0 + 8 * slot, stage_bytes);
+            tensor_copy_2d(a_base + slot * stage_bytes, map, x_word, (int32_t)(y_first + c * kHMmaChunk), bar0 + 8 * slot);
         }
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
+        // stay until every copy has landed: nothing may arrive in the shared memory of a CTA that has gone
+        for (uint32_t c = nchunks > nstage ? nchunks - nstage : 0; c < nchunks; ++c) wait_for(bar0 + 8 * (c % nstage), (c / nstage) & 1u);
+        if (gave_up) atomicAdd(timeouts, 1u);
         return;
     }
 
