@@ -161,7 +161,11 @@ constexpr int kHMmaConsumers = 256;   // eight warps multiply
 constexpr int kHMmaProducers = 32;    // one more warp, of which one thread issues the copies into the ring
 constexpr int kHMmaThreads = kHMmaConsumers + kHMmaProducers;
 constexpr int kHMmaChunk = 32;                       // rows per chunk (two mma row tiles)
-constexpr int kHMmaRing = 98304;                     // bytes of the A ring: two CTAs per SM keep ~190 KB of source rows in flight
+#ifndef DG_HMMA_CTAS
+#define DG_HMMA_CTAS 3
+#endif
+constexpr int kHMmaCtasPerSm = DG_HMMA_CTAS;
+constexpr int kHMmaRing = kHMmaCtasPerSm == 3 ? 69632 : 98304;  // bytes of the A ring: the CTAs of an SM keep ~200 KB of source rows in flight
 constexpr int kHMmaMaxStages = 8;
 constexpr int kHMmaOutPitch = kHMmaStrip + 8;         // 18 words: the tiles' two-byte writes fall into different banks
 
@@ -169,7 +173,8 @@ struct HMmaSmem {
     uint8_t out[2][kHMmaChunk][kHMmaOutPitch];  // a chunk's output bytes, before they go out as 64-byte row pieces
     uint8_t A[kHMmaRing];
 };
-static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 16) <= kHMmaRing, "the ring must hold two chunks of the widest band");
+constexpr int kHMmaRingSlack = 64;
+static_assert(2 * kHMmaChunk * ((int)kHMmaMaxSpan + 16) + kHMmaRingSlack <= kHMmaRing, "the ring must hold two chunks of the widest band");
 
 // ldmatrix stays ordered after the wait on the ring slot (volatile, memory); the multiplies are pure register functions
 // that the compiler may move between the loads
@@ -211,7 +216,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 constexpr uint32_t kHMmaWaitLimit = 1u << 20;  // waits of up to 2 us each on a ring slot's barrier before a CTA gives up on it
 
-__global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
+__global__ void __launch_bounds__(kHMmaThreads, kHMmaCtasPerSm) k_conv_h_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
                                                                 unsigned int* timeouts) {
     extern __shared__ __align__(128) unsigned char conv_h_smem[];
     HMmaSmem& sm = *reinterpret_cast<HMmaSmem*>(conv_h_smem);
@@ -238,7 +243,9 @@ __global__ void __launch_bounds__(kHMmaThreads, 2) k_conv_h_mma(const ConvPass* 
     // different banks) that covers the widest strip of the pass
     const uint32_t pitch_a = pg.box_pieces * 16;
     const uint32_t stage_bytes = kHMmaChunk * pitch_a;
-    const uint32_t nstage = min((uint32_t)kHMmaMaxStages, (uint32_t)kHMmaRing / stage_bytes);  // >= 2 by the planner's span limit
+    // The last k step of a warp may read up to 47 bytes past the end of a staged row (they meet zero weights): the ring
+    // keeps that much room behind its last slot.
+    const uint32_t nstage = min((uint32_t)kHMmaMaxStages, (uint32_t)(kHMmaRing - kHMmaRingSlack) / stage_bytes);  // >= 2 by the planner's span limit
     // ... and of this warp's eight output bytes (a warp past the end of the row has no tile)
     const bool warp_active = jn0 < row_bytes;
     int32_t band_lo = strip_lo;
