@@ -651,6 +651,59 @@ static bool encode_source_map(ConvPass& cp) {
     return true;
 }
 
+// Whether the tensor-core vertical pass can take output rows [t0, t0 + out_h) of table T: the source rows under the eight
+// output rows of a warp and under the 64 of a CTA must fit what a CTA stages (see k_conv_v_mma in kernels_resize.cu).
+// box: rows of a tensor-map box | boxes per chunk << 16; src_rows: source rows the pass reads, from row 0 of its source.
+static bool vmma_fits(const FilterTable& T, uint32_t t0, uint32_t out_h, int32_t origin, uint32_t* box, uint32_t* src_rows) {
+    int32_t tallest = 0, last = 0;
+    for (uint32_t y0 = 0; y0 < out_h; y0 += kVMmaRows) {
+        const uint32_t y1 = std::min(out_h, y0 + kVMmaRows) - 1;
+        const int32_t lo = T.start[t0 + y0] - origin;
+        if (lo < 0) return false;
+        int32_t hi = lo;
+        for (uint32_t y = y0; y <= y1; ++y) {
+            if (T.start[t0 + y] < T.start[t0 + y0]) return false;  // the windows move down with the output rows
+            hi = std::max(hi, T.start[t0 + y] + T.size[t0 + y] - origin);
+        }
+        tallest = std::max(tallest, hi - lo);
+        last = std::max(last, hi);
+        for (uint32_t yw = y0; yw <= y1; yw += 8) {
+            const uint32_t yl = std::min(y1, yw + 7);
+            int32_t bhi = 0;
+            for (uint32_t y = yw; y <= yl; ++y) {
+                if (T.start[t0 + y] < T.start[t0 + yw]) return false;
+                bhi = std::max(bhi, T.start[t0 + y] + T.size[t0 + y]);
+            }
+            // the kernel takes the band's end from the warp's last row
+            if (bhi != T.start[t0 + yl] + T.size[t0 + yl] || bhi - T.start[t0 + yw] > (int32_t)kVMmaMaxBand) return false;
+        }
+    }
+    if (tallest <= 0 || tallest > (int32_t)kVMmaMaxSpan) return false;
+    const uint32_t boxes = ((uint32_t)tallest + 255) / 256;
+    const uint32_t rows = (uint32_t)align_up(((size_t)tallest + boxes - 1) / boxes, 8);
+    *box = rows | boxes << 16;
+    *src_rows = (uint32_t)last;
+    return true;
+}
+
+// The source of a tensor-core vertical pass as rows of bytes: one copy brings 64 bytes of `box rows` consecutive rows, laid
+// out with the 64-byte swizzle.  Bytes and rows outside the array read as zero.
+static bool encode_source_map_v(ConvPass& cp, uint32_t src_rows) {
+    const EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t gdim[2] = {cp.src_pitch, src_rows};
+    const cuuint64_t gstride[1] = {cp.src_pitch};
+    const cuuint32_t box[2] = {64, cp.box_pieces & 0xFFFFu};
+    const cuuint32_t estride[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(cp.src), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    memcpy(cp.tmap, &m, sizeof m);
+    return true;
+}
+
 // Plans the resize of one image: appends passes / copy jobs to the wave.  src: device pointer of the source image
 // (tight pitch), dst: device pointer of the payload (tight pitch), mid: scratch for intermediates.
 // caller_owned_src: the source is memory of the caller with nothing guaranteed around it (the batch path's sources sit
@@ -730,6 +783,11 @@ static void plan_resize(Planner& pl, WavePlan& wv, const dg_plan& p, uint32_t C,
                       (size_t)align_up((size_t)out_w * C, 16) <= dpitch;
             // the vector path reads whole 16-byte chunks: in caller memory they must end inside the row they start in
             if (guarded && (size_t)(s - src) % spitch + align_up((size_t)out_w * C, 16) > spitch) cp.fast = 0;
+            uint32_t src_rows = 0;
+            if (cp.fast && !guarded && pl.ctx->hmma && vmma_fits(*T, t0, out_h, origin, &cp.box_pieces, &src_rows)) {
+                cp.fast = 2;
+                if (pl.final_round && !encode_source_map_v(cp, src_rows)) pl.tmap_failed = true;
+            }
         }
         cp.tiles_x = conv_tiles_x(cp, !horizontal);
         wv.passes[stage].push_back(cp);
@@ -1146,13 +1204,13 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             for (int s = 0; s < 4; ++s) {
                 uint32_t t = 0;
                 wv.pass_first[s].push_back(0);
-                if (!(s & 1)) std::stable_partition(wv.passes[s].begin(), wv.passes[s].end(), [](const ConvPass& cp) { return cp.fast == 2; });
+                std::stable_partition(wv.passes[s].begin(), wv.passes[s].end(), [](const ConvPass& cp) { return cp.fast == 2; });
                 wv.mma_tiles[s] = 0;
                 for (ConvPass& cp : wv.passes[s]) {
                     cp.tile_first = t;
                     t += conv_tiles(cp, (s & 1) != 0);
                     wv.pass_first[s].push_back(t);
-                    if (!(s & 1) && cp.fast == 2) wv.mma_tiles[s] = t;
+                    if (cp.fast == 2) wv.mma_tiles[s] = t;
                 }
             }
             uint32_t t = 0;
@@ -1486,8 +1544,9 @@ static int batch_run_locked(dg_batch* b) {
                 if (!wv.passes[st].empty()) {
                     CU(mark(kStageOf[st], true));
                     const ConvPass* passes = (const ConvPass*)(meta + wv.m_passes[st]);
-                    if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, s);
-                    else { launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s); b->used_hmma = b->used_hmma || wv.mma_tiles[st] != 0; }
+                    if (st & 1) launch_conv_v(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s);
+                    else launch_conv_h(passes, resolve(b, wv.m_pass[st]), tables, wv.mma_tiles[st], s);
+                    b->used_hmma = b->used_hmma || wv.mma_tiles[st] != 0;
                     ++b->launches;
                     CU(mark(kStageOf[st], false));
                 }
@@ -1782,7 +1841,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
             cp.tile_first = t;
             t += conv_tiles(cp, (s & 1) != 0);
             wv.pass_first[s].push_back(t);
-            if (!(s & 1) && cp.fast == 2) wv.mma_tiles[s] = t;
+            if (cp.fast == 2) wv.mma_tiles[s] = t;
         }
         m_passes[s] = m.put(wv.passes[s], 64);
         m_pass[s] = put_owner_map(m, wv.pass_first[s]);
@@ -1817,7 +1876,7 @@ extern "C" int dg_resize_device_static(dg_ctx* ctx, const uint8_t* device_src, u
     for (int st = 0; st < 4; ++st) {
         if (wv.passes[st].empty()) continue;
         const ConvPass* passes = (const ConvPass*)(scratch + m_passes[st]);
-        if (st & 1) launch_conv_v(passes, map_at(m_pass[st]), tables, s);
+        if (st & 1) launch_conv_v(passes, map_at(m_pass[st]), tables, wv.mma_tiles[st], s);
         else launch_conv_h(passes, map_at(m_pass[st]), tables, wv.mma_tiles[st], s);
     }
     if (!wv.copies.empty()) launch_copy((const CopyJob*)(scratch + m_copies), map_at(m_copy), s);

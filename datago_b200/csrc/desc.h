@@ -78,15 +78,17 @@ struct ConvPass {
     uint64_t tab_off;               // word offset in the table pool: start[tab_n] | size[tab_n] | int16 k[window][tab_n]
     uint32_t tile_first;            // first CTA tile of this pass in the launch (prefix sum)
     uint32_t tiles_x;               // tiles per row of tiles
-    uint32_t fast;                  // vertical: 1 = the vectorised path applies; horizontal: 2 = the tensor-core path (see kernels_resize.cu)
-    uint32_t box_pieces;            // tensor-core path: 16-byte pieces per staged source row (odd), the width of the tensor map's box
+    uint32_t fast;                  // vertical: 1 = the vectorised path applies; 2 (both directions) = the tensor-core path (see kernels_resize.cu)
+    uint32_t box_pieces;            // tensor-core path, horizontal: 16-byte pieces per staged source row (odd), the width of the tensor map's
+                                    // box; vertical: rows of a box | boxes per chunk << 16
     // Set when `src` is memory the library does not own (no slack behind it): the horizontal pass then loads no byte
     // outside [guard_lo, guard_hi).  Both null for sources inside the library's own padded arenas.
     const uint8_t* guard_lo;
     const uint8_t* guard_hi;
-    // Tensor-core path: the CUtensorMap (128 opaque bytes, written by cuTensorMapEncodeTiled) of the pass's source as a
-    // two-dimensional array of 32-bit words, box = box_pieces * 4 words x 32 rows; the copying thread of a CTA hands its
-    // address to cp.async.bulk.tensor.  Unused (zero) for every other pass.
+    // Tensor-core path: the CUtensorMap (128 opaque bytes, written by cuTensorMapEncodeTiled) of the pass's source; the
+    // copying thread of a CTA hands its address to cp.async.bulk.tensor.  Horizontal: a two-dimensional array of 32-bit
+    // words, box = box_pieces * 4 words x 32 rows; vertical: of bytes, box = 64 bytes x the rows of a box, 64-byte
+    // swizzle.  Unused (zero) for every other pass.
     alignas(64) unsigned char tmap[128];
 };
 static_assert(sizeof(ConvPass) % 64 == 0, "passes are stored as an array: every tensor map must stay 64-byte aligned");

@@ -85,14 +85,18 @@ constexpr uint32_t kVFastMaxWindow = 128;
 // horizontal pass on the tensor cores (ConvPass::fast == 2): output bytes per strip x rows per CTA; limits of what a CTA
 // can stage -- source bytes under one 8-byte output tile, and under a whole strip
 constexpr uint32_t kHMmaStrip = 64, kHMmaRows = 2048, kHMmaMaxBand = 256, kHMmaMaxSpan = 1008;  // span: 63 pieces of 16 bytes = 252 words, inside the 256 elements a tensor-map box may have
+// vertical pass on the tensor cores (ConvPass::fast == 2): output rows x bytes of a row per CTA; limits of what a CTA can
+// stage -- source rows under the eight output rows of one warp, and under all rows of the CTA
+constexpr uint32_t kVMmaRows = 64, kVMmaCols = 4096, kVMmaMaxBand = 256, kVMmaMaxSpan = 704;
 inline uint32_t conv_tiles_x(const ConvPass& p, bool vertical) {
     if (!vertical && p.fast == 2) return (p.out_w * p.channels + kHMmaStrip - 1) / kHMmaStrip;
+    if (vertical && p.fast == 2) return (p.out_w * p.channels + kVMmaCols - 1) / kVMmaCols;
     if (!vertical) return (p.out_w + kConvTileW - 1) / kConvTileW;
     const uint32_t row_bytes = p.out_w * p.channels;
     return p.fast ? (row_bytes + kVFastBytes - 1) / kVFastBytes : (row_bytes + kVTileBytes - 1) / kVTileBytes;
 }
 inline uint32_t conv_tiles(const ConvPass& p, bool vertical) {
-    const uint32_t rows = !vertical ? (p.fast == 2 ? kHMmaRows : kConvTileH) : p.fast ? kVFastRows : kVTileH;
+    const uint32_t rows = !vertical ? (p.fast == 2 ? kHMmaRows : kConvTileH) : p.fast == 2 ? kVMmaRows : p.fast ? kVFastRows : kVTileH;
     return conv_tiles_x(p, vertical) * ((p.out_h + rows - 1) / rows);
 }
 constexpr uint32_t kCopyTileBytes = 4096;
@@ -101,7 +105,7 @@ constexpr uint32_t kCopyTileBytes = 4096;
 void launch_conv_h(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s);
 // CTAs of the tensor-core horizontal pass that ran out of patience waiting for a copy since the library was loaded
 unsigned int read_conv_timeouts(cudaStream_t s);
-void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s);
+void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s);
 void launch_copy(const CopyJob* jobs, OwnerMap map, cudaStream_t s);
 constexpr uint32_t kAlphaTilePx = 2048;  // pixels per CTA of the alpha multiply / divide kernel
 void launch_alpha(const AlphaJob* jobs, OwnerMap map, cudaStream_t s);

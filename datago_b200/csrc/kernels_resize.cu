@@ -592,22 +592,221 @@ __device__ __forceinline__ void conv_v_vector(const ConvPass& p, const Table& tb
     }
 }
 
-__global__ void __launch_bounds__(kConvVThreads) k_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables) {
+// ---- vertical pass on the tensor cores --------------------------------------------------------------------------------
+// out[y][x] = sum_k w[y][k] * src[k][x] as a matrix product with the image's columns as the M dimension, the output rows
+// as N and the source rows as K, on the same 8-bit path with the weights split into two limbs as in the horizontal pass.
+//   CTA  = 64 output rows (warp q of the first eight owns rows 8q .. 8q+7) x up to 4096 bytes of the rows, walked in chunks
+//          of 64 bytes (four tiles of 16 columns); one thread of a ninth warp issues the copies.
+//   B    = the warp's weights (eight output rows x the source rows under them, at most 256), both limbs, gathered once
+//          into registers.
+//   A    = per chunk the source rows under the CTA's 64 output rows x 64 bytes, brought in by tensor-map copies with the
+//          64-byte swizzle (boxes of at most 256 rows) into a ring.  The reduction runs over rows, which are not
+//          contiguous in memory: ldmatrix.trans hands a lane the bytes (rows 2t, 2t+1) x (columns 2g, 2g+1) of each 8-row
+//          group, and one byte permute per register turns two such words into four source rows of one column.  The k
+//          slots of a fragment then hold rows {2t, 2t+1, 8+2t, 9+2t} (+16) of the 32-row step rather than 4t .. 4t+3;
+//          the weights are gathered in the same order, so the product is the same.  With the swizzle the eight 16-byte
+//          row pieces of an ldmatrix fall into different banks.
+//   D    = 16 columns x 8 rows per tile: merged, rounded, saturated, collected per warp as 8 rows x 64 bytes in shared
+//          memory and stored as 16 bytes per lane.
+constexpr int kVMmaConsumers = 256, kVMmaThreads = kVMmaConsumers + 32;
+constexpr int kVMmaChunk = 64;            // bytes of a row per chunk
+constexpr int kVMmaRing = 98304;          // bytes of the ring: two CTAs per SM
+constexpr int kVMmaRingSlack = 2048;      // a warp's last k step reads up to 31 rows past the staged ones (zero weights)
+constexpr int kVMmaMaxStages = 8;
+static_assert(2 * (int)kVMmaMaxSpan * kVMmaChunk + kVMmaRingSlack <= kVMmaRing, "the ring must hold two chunks of the tallest span");
+
+struct VMmaSmem {
+    uint8_t A[kVMmaRing];                                // first: slots start on 512-byte boundaries (swizzle pattern)
+    uint8_t out[kVMmaConsumers / 32][8][kVMmaChunk + 16];  // per warp: a chunk's 8 x 64 output bytes (rows padded against bank conflicts)
+};
+
+__global__ void __launch_bounds__(kVMmaThreads, 2) k_conv_v_mma(const ConvPass* passes, OwnerMap map, const uint32_t* tables,
+                                                                unsigned int* timeouts) {
+    extern __shared__ __align__(1024) unsigned char conv_v_smem[];
+    VMmaSmem& sm = *reinterpret_cast<VMmaSmem*>(conv_v_smem);
+    __shared__ __align__(8) unsigned long long s_bar[2 * kVMmaMaxStages];
+    const ConvPass& pg = passes[owner_of_tile(map, blockIdx.x)];
+    uint8_t* const p_dst = pg.dst;
+    const uint32_t dst_pitch = pg.dst_pitch, out_h = pg.out_h, row_bytes = pg.out_w * pg.channels;
+    const uint32_t t0 = pg.t0, tab_n = pg.tab_n, precision = pg.precision, tiles_x = pg.tiles_x;
+    const int32_t origin = pg.src_origin;
+    const uint32_t box_rows = pg.box_pieces & 0xFFFFu, boxes = pg.box_pieces >> 16;
+    const uint32_t tile = blockIdx.x - pg.tile_first;
+    const Table tb = table_of(pg, tables);
+    const uint32_t ty = tile / tiles_x, tx = tile - ty * tiles_x;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t y0 = ty * kVMmaRows, yw = y0 + warp * 8;
+    const uint32_t x_first = tx * kVMmaCols, x_end = min(row_bytes, x_first + kVMmaCols);
+    const uint32_t nchunks = (x_end - x_first + kVMmaChunk - 1) / kVMmaChunk;
+    // first source row under the CTA's output rows (row 0 = the first row of the pass's source)
+    const int32_t r_lo = __ldg(tb.start + t0 + y0) - origin;
+    const uint32_t stage_bytes = box_rows * boxes * kVMmaChunk;
+    const uint32_t nstage = min((uint32_t)kVMmaMaxStages, (uint32_t)(kVMmaRing - kVMmaRingSlack) / stage_bytes);  // >= 2 by the planner's span limit
+    const bool warp_active = warp < kVMmaConsumers / 32 && yw < out_h;
+    int32_t band_lo = 0;  // first staged row under the warp's output rows
+    uint32_t ksteps = 0;
+    if (warp_active) {
+        const uint32_t yl = min(out_h - 1, yw + 7);
+        band_lo = __ldg(tb.start + t0 + yw) - origin - r_lo;
+        const int32_t band_hi = __ldg(tb.start + t0 + yl) + __ldg(tb.size + t0 + yl) - origin - r_lo;
+        ksteps = (uint32_t)(band_hi - band_lo + 31) >> 5;
+    }
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&s_bar[0]);
+    if (threadIdx.x == 0) {
+        for (uint32_t i = 0; i < (uint32_t)kVMmaMaxStages; ++i) { mbar_init(bar0 + 8 * i, 1); mbar_init(bar0 + 8 * (kVMmaMaxStages + i), kVMmaConsumers / 32); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    const uint32_t a_base = (uint32_t)__cvta_generic_to_shared(sm.A);
+    bool gave_up = false;
+    auto wait_for = [&](uint32_t bar, uint32_t parity) {
+        uint32_t polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if (++polls > kHMmaWaitLimit) { gave_up = true; break; }
+        }
+    };
+    if (warp >= kVMmaConsumers / 32) {
+        // ---- the copying thread: per chunk `boxes` copies of box_rows rows x 64 bytes, one below the other
+        if (lane != 0) return;
+        const void* tmap = pg.tmap;
+        asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(tmap) : "memory");
+        for (uint32_t c = 0; c < nchunks && !gave_up; ++c) {
+            const uint32_t slot = c % nstage, use = c / nstage;
+            if (use > 0) wait_for(bar0 + 8 * (kVMmaMaxStages + slot), (use - 1) & 1u);
+            if (gave_up) break;
+            mbar_expect_tx(bar0 + 8 * slot, stage_bytes);
+            for (uint32_t bx = 0; bx < boxes; ++bx)
+                tensor_copy_2d(a_base + slot * stage_bytes + bx * box_rows * kVMmaChunk, tmap, (int32_t)(x_first + c * kVMmaChunk),
+                               r_lo + (int32_t)(bx * box_rows), bar0 + 8 * slot);
+        }
+        for (uint32_t c = nchunks > nstage ? nchunks - nstage : 0; c < nchunks; ++c) wait_for(bar0 + 8 * (c % nstage), (c / nstage) & 1u);
+        if (gave_up) atomicAdd(timeouts, 1u);
+        return;
+    }
+
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    const int32_t half = 1 << (precision - 1);
+    // ---- B fragments: output row yw + g; byte e of a register is k slot 4 t + e, which holds staged row
+    //      band_lo + 32 ks + 16 hf + {2t, 2t+1, 8+2t, 9+2t}[e]
+    uint32_t bfr[8][4];
+    {
+        const uint32_t y = yw + g;
+        const bool live = warp_active && y < out_h;
+        const int32_t first = live ? __ldg(tb.start + t0 + y) - origin - r_lo - band_lo : 0;  // in rows of the warp's band
+        const int32_t taps = live ? __ldg(tb.size + t0 + y) : 0;
+        const int16_t* k = tb.k + t0 + y;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t hi[2] = {0, 0}, lo[2] = {0, 0};
+            if ((uint32_t)ks < ksteps) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int32_t i = 32 * ks + 16 * hf + 2 * (int32_t)t4 + (e & 1) + 8 * (e >> 1) - first;
+                        if (i >= 0 && i < taps) {
+                            const int32_t wv = __ldg(k + (size_t)i * tab_n);
+                            hi[hf] |= ((uint32_t)(wv >> 8) & 255u) << (8 * e);   // signed high byte
+                            lo[hf] |= ((uint32_t)wv & 255u) << (8 * e);          // unsigned low byte
+                        }
+                    }
+            }
+            bfr[ks][0] = hi[0]; bfr[ks][1] = hi[1]; bfr[ks][2] = lo[0]; bfr[ks][3] = lo[1];
+        }
+    }
+    const uint32_t out_base = (uint32_t)__cvta_generic_to_shared(&sm.out[warp][0][0]);
+    constexpr uint32_t kOutPitch = kVMmaChunk + 16;
+    auto consume = [&](auto ks_tag) {
+    constexpr int KS = decltype(ks_tag)::value;
+    for (uint32_t c = 0; c < nchunks; ++c) {
+        const uint32_t slot = c % nstage;
+        wait_for(bar0 + 8 * slot, (c / nstage) & 1u);
+        if (warp_active) {
+            const uint32_t stage = a_base + slot * stage_bytes;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt) {
+                int32_t acc_hi[4] = {0, 0, 0, 0}, acc_lo[4] = {half, half, half, half};
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    // lane i names staged row band_lo + 32 ks + i; its 16-byte piece mt sits at piece mt ^ (row / 2 % 4)
+                    const uint32_t row = (uint32_t)band_lo + 32u * ks + lane;
+                    uint32_t r[4];
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                                 : "r"(stage + row * kVMmaChunk + 16u * ((uint32_t)mt ^ ((row >> 1) & 3u))) : "memory");
+                    uint32_t a[4];
+                    a[0] = __byte_perm(r[0], r[1], 0x6420);  // column 2g
+                    a[1] = __byte_perm(r[0], r[1], 0x7531);  // column 2g + 1
+                    a[2] = __byte_perm(r[2], r[3], 0x6420);
+                    a[3] = __byte_perm(r[2], r[3], 0x7531);
+                    mma_u8s8(acc_hi, a, bfr[ks][0], bfr[ks][1]);
+                    mma_u8u8(acc_lo, a, bfr[ks][2], bfr[ks][3]);
+                }
+                // accumulators: (column 2g, row 2t), (column 2g, row 2t+1), (column 2g+1, row 2t), (column 2g+1, row 2t+1)
+                int32_t v[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[i] = (acc_hi[i] * 256 + acc_lo[i]) >> precision;
+                uint32_t pk;
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(pk) : "r"(v[2]), "r"(v[0]), "r"(0));
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_base + (2 * t4) * kOutPitch + 16 * mt + 2 * g), "h"((uint16_t)pk) : "memory");
+                asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(pk) : "r"(v[3]), "r"(v[1]), "r"(0));
+                asm volatile("st.shared.u16 [%0], %1;" ::"r"(out_base + (2 * t4 + 1) * kOutPitch + 16 * mt + 2 * g), "h"((uint16_t)pk) : "memory");
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar0 + 8 * (kVMmaMaxStages + slot));  // this warp is done with the slot
+        if (warp_active) {
+            const uint32_t row = lane >> 2, xb = x_first + c * kVMmaChunk + (lane & 3u) * 16;
+            if (yw + row < out_h && xb < row_bytes)  // rows are padded to 16 bytes: the last piece of a row is stored in full
+                *reinterpret_cast<uint4*>(p_dst + (size_t)(yw + row) * dst_pitch + xb) = *reinterpret_cast<const uint4*>(&sm.out[warp][row][(lane & 3u) * 16]);
+        }
+        __syncwarp();  // the warp's piece of shared memory is rewritten by the next chunk
+    }
+    };
+    switch (ksteps) {
+        case 1: consume(std::integral_constant<int, 1>{}); break;
+        case 2: consume(std::integral_constant<int, 2>{}); break;
+        case 3: consume(std::integral_constant<int, 3>{}); break;
+        case 4: consume(std::integral_constant<int, 4>{}); break;
+        case 5: consume(std::integral_constant<int, 5>{}); break;
+        case 6: consume(std::integral_constant<int, 6>{}); break;
+        case 7: consume(std::integral_constant<int, 7>{}); break;
+        default: consume(std::integral_constant<int, 8>{}); break;
+    }
+    if (gave_up && lane == 0) atomicAdd(timeouts, 1u);
+}
+
+__global__ void __launch_bounds__(kConvVThreads) k_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t first_tile) {
     __shared__ uint32_t s_k[kVFastRows][kVFastMaxWindow / 2];
     __shared__ int32_t s_first[kVFastRows], s_taps[kVFastRows];
     __shared__ uint32_t s_pass;
-    if (threadIdx.x == 0) s_pass = owner_of_tile(map, blockIdx.x);
+    const uint32_t tile_index = first_tile + blockIdx.x;
+    if (threadIdx.x == 0) s_pass = owner_of_tile(map, tile_index);
     __syncthreads();
     const ConvPass& p = passes[s_pass];
-    const uint32_t tile = blockIdx.x - p.tile_first;
+    const uint32_t tile = tile_index - p.tile_first;
     const uint32_t ty = tile / p.tiles_x, tx = tile - ty * p.tiles_x;
     const Table tb = table_of(p, tables);
     if (p.fast) conv_v_vector(p, tb, tx, ty, s_k, s_first, s_taps);
     else conv_v_plain(p, tb, tx, ty);
 }
 
-void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, cudaStream_t s) {
-    if (map.total) k_conv_v<<<map.total, kConvVThreads, 0, s>>>(passes, map, tables);
+// Vertical passes of one stage: the tensor-core passes come first in `passes` and own tiles [0, mma_tiles) of the map.
+void launch_conv_v(const ConvPass* passes, OwnerMap map, const uint32_t* tables, uint32_t mma_tiles, cudaStream_t s) {
+    if (!map.total) return;
+    if (mma_tiles) {
+        static bool configured[64] = {false};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64) dev = 0;
+        if (!configured[dev]) {
+            cudaFuncSetAttribute(k_conv_v_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(VMmaSmem));
+            configured[dev] = true;
+        }
+        k_conv_v_mma<<<mma_tiles, kVMmaThreads, sizeof(VMmaSmem), s>>>(passes, map, tables, conv_timeouts());
+    }
+    if (map.total > mma_tiles) k_conv_v<<<map.total - mma_tiles, kConvVThreads, 0, s>>>(passes, map, tables, mma_tiles);
 }
 
 // ---- plain copies (identity payloads, integral crops without any filtering) ----------------------------------------
