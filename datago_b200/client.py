@@ -269,6 +269,8 @@ class DatagoClient:
         self.is_started = False
         self._thread = None
         self._stop = threading.Event()
+        self._reader_stop = threading.Event()
+        self._buffers = [None, None]
         cfg = self._check_config(str_config)
         if cfg is None:
             return
@@ -323,6 +325,7 @@ class DatagoClient:
         if not self.is_valid or self.is_started:
             return
         self._stop.clear()
+        self._reader_stop.clear()
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
         self.is_started = True
@@ -388,22 +391,93 @@ class DatagoClient:
                     yield key, source, files
 
     def _run(self):
+        """The engine: a reader thread walks files / shards ahead of this thread (datago's generator task), and this
+        thread keeps one batch on the GPU while it plans the next (datago's worker pool): a batch is launched -- host
+        planning, upload, kernels and the packed download queued on the context's stream -- before the previous one is
+        waited for and turned into samples.  Samples leave in source order."""
         produced = 0
-        pending = []
+        units_q = queue.Queue(maxsize=max(4 * self.batch_size, 16))
+        reader = threading.Thread(target=self._read_ahead, args=(units_q,), daemon=True)
+        reader.start()
+        in_flight, flight_units = None, 0
         try:
-            for unit in self._units():
-                if self._stop.is_set() or produced + len(pending) >= self.limit:
-                    break
-                pending.append(unit)
-                if len(pending) >= self.batch_size:
-                    produced += self._flush(pending)
-                    pending = []
-            if pending and not self._stop.is_set():
-                produced += self._flush(pending[: max(0, self.limit - produced)])
+            pending, lane, eof = [], 0, False
+            while not self._stop.is_set():
+                room = self.limit - produced - flight_units - len(pending)
+                if not eof and room > 0 and len(pending) < self.batch_size:
+                    try:
+                        unit = units_q.get(timeout=0.1)
+                    except queue.Empty:  # the reader is still at work (or the client is being stopped)
+                        continue
+                    if unit is None:
+                        eof = True
+                    else:
+                        pending.append(unit)
+                    continue
+                if pending:  # a full batch, the last units below the limit, or the end of the source
+                    launched = self._launch(pending, lane)
+                    lane ^= 1
+                    if in_flight is not None:
+                        produced += self._finish(in_flight)
+                    in_flight, flight_units, pending = launched, len(pending), []
+                    continue
+                if in_flight is not None:  # samples that failed leave room below the limit: the loop reads on
+                    produced += self._finish(in_flight)
+                    in_flight, flight_units = None, 0
+                    continue
+                break
         except Exception:  # noqa: BLE001
             log.exception("datago_b200 worker failed")
         finally:
+            self._reader_stop.set()
+            if in_flight is not None:
+                try:
+                    in_flight[0].sync()
+                    in_flight[0].close()
+                except Exception:  # noqa: BLE001
+                    pass
+            while reader.is_alive():  # unblock a reader stuck on a full queue
+                try:
+                    units_q.get_nowait()
+                except queue.Empty:
+                    pass
+                reader.join(timeout=0.05)
             self._put(None)
+
+    def _read_ahead(self, units_q):
+        try:
+            for unit in self._units():
+                while not (self._stop.is_set() or self._reader_stop.is_set()):
+                    try:
+                        units_q.put(unit, timeout=0.1)
+                        break
+                    except queue.Full:
+                        continue
+                else:
+                    return
+        except Exception:  # noqa: BLE001
+            log.exception("datago_b200 reader failed")
+        finally:
+            while not (self._stop.is_set() or self._reader_stop.is_set()):
+                try:
+                    units_q.put(None, timeout=0.1)
+                    break
+                except queue.Full:
+                    continue
+
+    def _host_buffer(self, lane, nbytes):
+        """The lane's landing buffer for packed downloads: page-locked when torch can provide it (a copy into pageable
+        memory is staged by the driver at a fraction of the link rate), grown on demand."""
+        buf = self._buffers[lane]
+        if buf is None or buf.nbytes < nbytes:
+            want = max(nbytes, 1 << 20) * 5 // 4
+            try:
+                import torch
+                buf = torch.empty(want, dtype=torch.uint8).pin_memory().numpy()
+            except Exception:  # noqa: BLE001 - no torch, or no page-locked memory to be had
+                buf = np.empty(want, np.uint8)
+            self._buffers[lane] = buf
+        return buf
 
     def _put(self, s):
         while not self._stop.is_set():
@@ -414,10 +488,10 @@ class DatagoClient:
                 continue
         return False
 
-    def _flush(self, units):
-        """One GPU batch for all image payloads of `units`.  Later payloads of a sample are forced into the bucket of
-        its first image (src/worker_wds.rs:68-76); the key comes from the header-only plan, so the whole sample rides
-        in one batch."""
+    def _launch(self, units, lane):
+        """Queues one GPU batch for all image payloads of `units`; returns what _finish needs.  Later payloads of a
+        sample are forced into the bucket of its first image (src/worker_wds.rs:68-76); the key comes from the
+        header-only plan, so the whole sample rides in one batch."""
         inputs, keys, slots = [], [], []  # slots: (unit index, filename, is first image)
         has_tfm = self.ctx.image_config is not None
         for ui, (_, _, files) in enumerate(units):
@@ -445,17 +519,23 @@ class DatagoClient:
                 inputs.append(data)
                 keys.append(forced)
                 slots.append((ui, name))
-        made = 0
-        if not inputs and not units:
-            return 0
         # `image_to_rgb8` of image_config applies to every image payload the file and webdataset workers produce
         # (src/worker_files.rs:19-30, src/worker_wds.rs:45-53 pass the client's ImageEncoding unchanged)
         to_rgb8 = True if (self.image_config or {}).get("image_to_rgb8") else None
         batch = self.ctx.batch(inputs, keys, 0 if has_tfm else BATCH_DECODE_ONLY, to_rgb8=to_rgb8)
         batch.upload()
         batch.run()
-        outs = None if self.device_payloads else batch.download()
+        buf = None
+        if not self.device_payloads and len(batch):
+            buf = self._host_buffer(lane, batch.packed_bytes())
+            batch.download_packed(buf)  # one copy; payload i lands at result(i).packed_offset
+        return batch, units, slots, buf
+
+    def _finish(self, launched):
+        """Waits for a launched batch and puts its samples on the queue; returns how many it made."""
+        batch, units, slots, buf = launched
         batch.sync()
+        made = 0
         payloads = {}
         for i, (ui, name) in enumerate(slots):
             r = batch.result(i)
@@ -463,11 +543,12 @@ class DatagoClient:
                 log.error("decode failed for %s (status %d)", name, r.status)
                 continue
             if self.pre_encode and not self.device_payloads:
-                pl = ImagePayload(data=encode_payload(outs[i], self.encode_format, self.jpeg_quality),
+                px = buf[r.packed_offset:r.packed_offset + r.nbytes].reshape(r.height, r.width, r.channels)
+                pl = ImagePayload(data=encode_payload(px, self.encode_format, self.jpeg_quality),
                                   original_height=r.original_height, original_width=r.original_width, height=r.height,
                                   width=r.width, channels=-1, bit_depth=8, is_encoded=True)
             else:
-                pl = ImagePayload(data=b"" if self.device_payloads else outs[i].tobytes(), original_height=r.original_height,
+                pl = ImagePayload(data=b"" if self.device_payloads else buf[r.packed_offset:r.packed_offset + r.nbytes].tobytes(), original_height=r.original_height,
                                   original_width=r.original_width, height=r.height, width=r.width, channels=r.channels,
                                   bit_depth=8, is_encoded=False, device_ptr=r.device_data if self.device_payloads else 0,
                                   keepalive=batch if self.device_payloads else None)
