@@ -4,6 +4,7 @@
 //
 // All of it is integer / byte work bound by HBM traffic or by serial bit-parsing latency; no tensor cores.
 #include <cstdint>
+#include <cstdlib>
 
 #include "kernels.h"
 
@@ -275,7 +276,7 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
 #endif
 constexpr int kSpecThreads = DG_SPEC_THREADS;      // the narrow variant
 constexpr int kSpecThreadsWide = 512, kSpecMinCtasWide = 3;
-constexpr uint32_t kSpecWideBelow = 1024;         // images per launch below which the wide variant is used
+constexpr uint32_t kSpecWideBelow = 1024;         // images per launch below which the wide variant is used (DATAGO_B200_SPEC_WIDE_BELOW overrides)
 constexpr uint32_t kSubseqBits = DG_SUBSEQ_BITS;
 
 struct Scan4 { uint32_t n; int32_t a, b, c; };
@@ -481,7 +482,8 @@ void launch_huff_spec(const JpegWave& w, uint32_t n_huge, cudaStream_t s, cudaSt
     if (n_huge) launch_spec_variant<kSpecThreadsHuge, 1>(w, 0, n_huge, huge_stream);
     const uint32_t rest = w.n_spec - n_huge;
     if (!rest) return;
-    if (rest < kSpecWideBelow) launch_spec_variant<kSpecThreadsWide, kSpecMinCtasWide>(w, n_huge, rest, s);
+    static const uint32_t wide_below = [] { const char* e = getenv("DATAGO_B200_SPEC_WIDE_BELOW"); return e ? (uint32_t)atoi(e) : kSpecWideBelow; }();
+    if (rest < wide_below) launch_spec_variant<kSpecThreadsWide, kSpecMinCtasWide>(w, n_huge, rest, s);
     else launch_spec_variant<kSpecThreads, DG_SPEC_MIN_CTAS>(w, n_huge, rest, s);
 }
 
