@@ -212,3 +212,18 @@ def test_both_horizontal_kernels_agree_with_the_oracle():
             os.environ.pop("DATAGO_B200_HMMA", None)
         else:
             os.environ["DATAGO_B200_HMMA"] = old
+
+
+def test_tensor_core_passes_at_their_tile_edges():
+    # outputs wider than one column range of the vertical tensor-core pass (4096 bytes) and taller than many row tiles,
+    # strong enlargements (short bands), and reductions beyond what the tensor-core passes stage (> 9x: the dp2a kernels)
+    rng = np.random.default_rng(27)
+    big = [rng.integers(0, 256, (1500, 3000, 3), dtype=np.uint8),   # 2048/64 bucket about 2880 x 1472: three column ranges
+           rng.integers(0, 256, (200, 300, 3), dtype=np.uint8),     # enlarged about 9x
+           rng.integers(0, 256, (2900, 1400), dtype=np.uint8),      # gray, tall
+           rng.integers(0, 256, (70, 4000, 3), dtype=np.uint8)]     # far from every bucket: heavy crop
+    _check_raw(C4, big)
+    small = [rng.integers(0, 256, (3000, 4000, 3), dtype=np.uint8),  # 224-bucket: about 13x reduction
+             rng.integers(0, 256, (2300, 2300), dtype=np.uint8),    # gray, about 10x
+             rng.integers(0, 256, (1900, 1700, 3), dtype=np.uint8)]  # about 8x: still on the tensor cores
+    _check_raw(CFG224, small)
