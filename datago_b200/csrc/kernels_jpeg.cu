@@ -28,6 +28,9 @@ __device__ const uint8_t kNatural[64] = {0,  1,  8,  16, 9,  2,  3,  10, 17, 24,
 // K0  unstuff: one CTA per image walks the entropy-coded segment in 4 KB steps, drops stuffed zeros (FF 00 -> FF),
 //     fill bytes and RSTn markers, records where each restart segment starts in the compacted stream and stops at
 //     the first other marker (EOI).  The compacted stream lets the entropy decoder load aligned 32-bit words.
+//     The kept bytes of a step are collected in shared memory and leave as aligned 16-byte pieces (a thread's bytes land
+//     at an arbitrary offset of the output, and single-byte stores to global memory cost a partial sector write each);
+//     what does not fill a piece waits at the front of the buffer for the next step.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kUnstuffThreads = 256;
 
@@ -41,7 +44,9 @@ __global__ void __launch_bounds__(kUnstuffThreads) k_unstuff(JpegWave w) {
 
     __shared__ uint32_t s_end;
     __shared__ uint32_t s_warp[kUnstuffThreads / 32];
+    __shared__ __align__(16) uint8_t s_out[kUnstuffThreads * 16 + 16];  // a step's bytes behind at most 15 carried ones
     uint32_t kept = 0, nrst = 0;  // running totals, identical in every thread
+    uint32_t flushed = 0;         // bytes already in global memory, a multiple of 16; kept - flushed wait in s_out
     if (tid == 0) seg[0] = 0;
 
     for (uint32_t base = 0; base < len; base += kUnstuffThreads * 16) {
@@ -96,15 +101,25 @@ __global__ void __launch_bounds__(kUnstuffThreads) k_unstuff(JpegWave w) {
         uint32_t pos = kept + (excl & 0xFFFFu), r = nrst + (excl >> 16);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            if (keep & (1u << j)) out[pos++] = b[j + 1];
+            if (keep & (1u << j)) { s_out[pos - flushed] = b[j + 1]; ++pos; }
             if (rst & (1u << j)) { ++r; if (r < d.nseg) seg[r] = pos; }
         }
         kept += tot & 0xFFFFu;
         nrst += tot >> 16;
+        __syncthreads();  // the step's bytes are in s_out
+        const uint32_t pieces = (kept - flushed) >> 4, rem = (kept - flushed) & 15u;
+        for (uint32_t t = tid; t < pieces; t += kUnstuffThreads)
+            reinterpret_cast<uint4*>(out + flushed)[t] = reinterpret_cast<const uint4*>(s_out)[t];
+        const uint8_t carried = (uint32_t)tid < rem ? s_out[pieces * 16 + tid] : (uint8_t)0;
+        __syncthreads();  // ... and have been read: the rest moves to the front (the next step writes behind it, after
+                          // its own first barrier)
+        if ((uint32_t)tid < rem) s_out[tid] = carried;
+        flushed += pieces * 16;
         if (end != 0xFFFFFFFFu) break;
-        __syncthreads();  // s_end and s_warp are rewritten by the next step
     }
-    if (tid < 16) out[kept + tid] = 0;  // the bit reader may look a few bytes past the end
+    __syncthreads();
+    // the last bytes, and zeros behind them: the bit reader may look a few bytes past the end
+    if ((uint32_t)tid < kept - flushed + 16) out[flushed + tid] = (uint32_t)tid < kept - flushed ? s_out[tid] : (uint8_t)0;
     if (tid == 0) {
         w.us_len[blockIdx.x] = kept;
         w.seg_found[blockIdx.x] = nrst + 1;
