@@ -178,17 +178,33 @@ __device__ __forceinline__ uint32_t huff_long_code(const HuffTable* t, uint32_t 
 // dc0..2: sums of DC differences (WRITE == false) or running DC predictors (WRITE == true).
 // One code path for DC and AC symbols (selects instead of branches): the lanes of a warp are at unrelated places of
 // their streams, so every branch taken by one lane is paid by all of them.
-template <bool WRITE>
+//
+// Writing (WRITE == true).  Two-byte stores of single coefficients, every lane to another block, are what the decoders
+// spent most of their time on (each is a partial write of a 32-byte sector, which the memory system completes by reading
+// the sector first).  With ROWS > 0 a lane collects the first ROWS rows of its current block (ROWS * 16 bytes; the
+// low-frequency corner, where nearly all coefficients of a sparse block are) in shared memory, buf[row * T + thread], and
+// writes them out when the block ends: whole 32-byte sectors, two rows at a time, for the sectors that received a
+// coefficient (the coefficient region is zero beforehand, so rows that are still zero may be written or skipped).
+// Coefficients of later rows are stored one by one as before.  A block the span shares with a neighbouring span (a span
+// of the speculative decoder starts and ends anywhere) is never written in rows: its first block, when the span begins
+// inside it, is stored coefficient by coefficient, and so is what the buffer holds when the span ends inside a block.
+// The buffer is all zero when the call begins and when it returns.
+template <bool WRITE, int ROWS = 0, int T = 1>
 __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, const uint32_t nwords, uint32_t& p,
                                             const uint32_t end_bit, const uint32_t total_bits, uint32_t& slotmod,
                                             uint32_t& nslots, const uint32_t max_slots, int32_t& dc0, int32_t& dc1,
                                             int32_t& dc2, const HuffCtx& hc, int16_t* __restrict__ coef,
-                                            const uint32_t slot_abs, const uint8_t* __restrict__ natural, uint32_t& err) {
+                                            const uint32_t slot_abs, const uint8_t* __restrict__ natural, uint32_t& err,
+                                            uint4* buf = nullptr) {
+    static_assert(ROWS % 2 == 0, "rows are written out as 32-byte sectors");
     auto word = [&](uint32_t i) -> uint32_t { return i < nwords ? __byte_perm(__ldg(words + i), 0, 0x0123) : 0u; };
     // a window of three stream words: the word fetched when the position crosses a word boundary is first needed one
     // boundary later, so its latency (the streams sit in global memory) stays off the symbol-to-symbol critical path
     uint32_t wi = p >> 5;
     uint32_t w0 = word(wi), w1 = word(wi + 1), w2 = word(wi + 2);
+    uint32_t sectors = 0;                          // sectors of the buffer that hold a coefficient
+    bool direct = (slotmod & 63u) != 0;            // the span begins inside a block
+    const uint32_t buf_b = (WRITE && ROWS > 0) ? (uint32_t)__cvta_generic_to_shared(buf + threadIdx.x) : 0u;  // row 0 of this lane
     while (p < end_bit && nslots < max_slots) {
         const uint32_t top = __funnelshift_l(w1, w0, p & 31u);
         const uint32_t z = slotmod & 63u, c = slotmod >> 6;
@@ -210,12 +226,35 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
         dc1 += comp == 1 ? dv : 0;
         dc2 += comp == 2 ? dv : 0;
         if (WRITE) {
-            if (isdc) {
-                coef[(size_t)(slot_abs + nslots)] = (int16_t)(comp == 0 ? dc0 : comp == 1 ? dc1 : dc2);  // slot of a DC code = 64 * block
-            } else if (s != 0u) {
-                const uint32_t zz = z + r;
-                if (zz <= 63u) coef[(size_t)(slot_abs + nslots - z) + natural[zz]] = (int16_t)v;
-                else err |= kStCoefRange;
+            const uint32_t zz = isdc ? 0u : z + r;
+            const int32_t val = isdc ? (comp == 0 ? dc0 : comp == 1 ? dc1 : dc2) : v;
+            const bool has = isdc ? val != 0 : s != 0u;  // (a zero DC term needs no store: the region is zero beforehand)
+            if (has && zz > 63u) err |= kStCoefRange;
+            else if (has) {
+                const uint32_t nat = natural[zz];
+                int16_t* const block = coef + (size_t)(slot_abs + nslots - z);  // the slot of a DC code is 64 * its block
+                if (ROWS == 0 || direct || nat >= 8u * ROWS) {
+                    block[nat] = (int16_t)val;
+                } else {
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(buf_b + (nat >> 3) * (uint32_t)(T * 16) + (nat & 7u) * 2u), "h"((uint16_t)val) : "memory");
+                    sectors |= 1u << (nat >> 4);
+                }
+            }
+            if (ROWS > 0 && !isdc && z + adv == 64u) {  // the block ends with this symbol
+                if (sectors) {
+                    uint4* const block = reinterpret_cast<uint4*>(coef + (size_t)(slot_abs + nslots - z));
+#pragma unroll
+                    for (int sc = 0; sc < ROWS / 2; ++sc)
+                        if ((sectors >> sc) & 1u) {
+                            uint4* const b0 = buf + (2 * sc) * T + threadIdx.x;
+                            block[2 * sc] = b0[0];
+                            block[2 * sc + 1] = b0[T];
+                            b0[0] = make_uint4(0, 0, 0, 0);
+                            b0[T] = make_uint4(0, 0, 0, 0);
+                        }
+                    sectors = 0;
+                }
+                direct = false;
             }
         }
         p += used;
@@ -225,15 +264,37 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
         const uint32_t nwi = p >> 5;
         if (nwi != wi) { w0 = w1; w1 = w2; w2 = word(nwi + 2); wi = nwi; }  // a symbol has at most 27 bits: one boundary at a time
     }
+    if (WRITE && ROWS > 0 && sectors) {
+        // the span ends inside a block that the next span continues: coefficient by coefficient
+        int16_t* const block = coef + (size_t)(slot_abs + nslots - (slotmod & 63u));
+#pragma unroll
+        for (int row = 0; row < ROWS; ++row)
+            if ((sectors >> (row >> 1)) & 1u) {
+                uint4* const b0 = buf + row * T + threadIdx.x;
+                const uint4 q = *b0;
+                const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t h = (ww[k >> 1] >> (16 * (k & 1))) & 0xFFFFu;
+                    if (h) block[row * 8 + k] = (int16_t)h;
+                }
+                *b0 = make_uint4(0, 0, 0, 0);
+            }
+    }
 }
 
 // ---- restart-interval images: one thread per segment -----------------------------------------------------------
 constexpr int kRestartThreads = 128;
 constexpr uint32_t kRestartSharedTables = 8;  // a pool of at most this many Huffman tables is staged in shared memory
+constexpr int kRestartBufRows = 4;            // rows of its current block a lane collects before writing them out
 
 __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
     __shared__ uint8_t s_nat[64];
-    __shared__ __align__(16) HuffTable s_tab[kRestartSharedTables];
+    extern __shared__ __align__(16) unsigned char restart_smem[];
+    // dynamic: the block buffers of the lanes (kRestartBufRows x 128 x 16 bytes), then the staged tables (when the pool is small)
+    uint4* const s_buf = reinterpret_cast<uint4*>(restart_smem);
+    HuffTable* const s_tab = reinterpret_cast<HuffTable*>(restart_smem + kRestartBufRows * kRestartThreads * 16);
+    for (uint32_t i = threadIdx.x; i < (uint32_t)(kRestartBufRows * kRestartThreads); i += kRestartThreads) s_buf[i] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x < 64) s_nat[threadIdx.x] = kNatural[threadIdx.x];
     // The segments of a CTA belong to several images, but files written by the same encoder share their tables and the
     // pool holds each distinct table once: a small pool is copied whole, so that the per-symbol table look-ups (on the
@@ -270,8 +331,9 @@ __global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
     uint32_t p = b0 * 8u, slotmod = 0, nslots = 0, err = 0;
     int32_t dc0 = 0, dc1 = 0, dc2 = 0;
     const uint32_t want = (m1 - m0) * hc.mcu_slots;
-    decode_span<true>(reinterpret_cast<const uint32_t*>(w.us + d.us_off), (us_len + 3) / 4 + 2, p, b1 * 8u, b1 * 8u, slotmod,
-                      nslots, want, dc0, dc1, dc2, hc, w.coef + d.block_off * 64, m0 * hc.mcu_slots, s_nat, err);
+    decode_span<true, kRestartBufRows, kRestartThreads>(reinterpret_cast<const uint32_t*>(w.us + d.us_off), (us_len + 3) / 4 + 2, p, b1 * 8u,
+                                                       b1 * 8u, slotmod, nslots, want, dc0, dc1, dc2, hc, w.coef + d.block_off * 64,
+                                                       m0 * hc.mcu_slots, s_nat, err, s_buf);
     if (nslots < want) err |= kStTruncated;
     if (err) atomicOr(w.status + d.item, err);
 }
@@ -471,7 +533,11 @@ __global__ void __launch_bounds__(T, MIN_CTAS) k_huff_spec(JpegWave w, uint32_t 
 
 void launch_huff_restart(const JpegWave& w, cudaStream_t s) {
     if (w.restart_segs.total)
-        k_huff_restart<<<(w.restart_segs.total + kRestartThreads - 1) / kRestartThreads, kRestartThreads, 0, s>>>(w);
+    {
+        const size_t smem = (size_t)kRestartBufRows * kRestartThreads * 16 +
+                            (w.n_huff <= kRestartSharedTables ? (size_t)w.n_huff * sizeof(HuffTable) : 0);
+        k_huff_restart<<<(w.restart_segs.total + kRestartThreads - 1) / kRestartThreads, kRestartThreads, smem, s>>>(w);
+    }
 }
 
 // Three CTA sizes.  A CTA walks its image chunk by chunk (T subsequences each), so the launch lasts as long as the
