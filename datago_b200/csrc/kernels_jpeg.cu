@@ -286,9 +286,15 @@ __device__ __forceinline__ void decode_span(const uint32_t* __restrict__ words, 
 // ---- restart-interval images: one thread per segment -----------------------------------------------------------
 constexpr int kRestartThreads = 128;
 constexpr uint32_t kRestartSharedTables = 8;  // a pool of at most this many Huffman tables is staged in shared memory
-constexpr int kRestartBufRows = 4;            // rows of its current block a lane collects before writing them out
+#ifndef DG_RESTART_BUF_ROWS
+#define DG_RESTART_BUF_ROWS 4
+#endif
+#ifndef DG_RESTART_MIN_CTAS
+#define DG_RESTART_MIN_CTAS 1
+#endif
+constexpr int kRestartBufRows = DG_RESTART_BUF_ROWS;  // rows of its current block a lane collects before writing them out
 
-__global__ void __launch_bounds__(kRestartThreads) k_huff_restart(JpegWave w) {
+__global__ void __launch_bounds__(kRestartThreads, DG_RESTART_MIN_CTAS) k_huff_restart(JpegWave w) {
     __shared__ uint8_t s_nat[64];
     extern __shared__ __align__(16) unsigned char restart_smem[];
     // dynamic: the block buffers of the lanes (kRestartBufRows x 128 x 16 bytes), then the staged tables (when the pool is small)
