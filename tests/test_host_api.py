@@ -179,3 +179,15 @@ def test_header_parser_survives_garbage(data, splice):
             assert info.width > 0 and info.height > 0 and info.scan_offset + info.scan_len == len(blob)
         except dg.DatagoB200Error as e:
             assert e.code in (3, 4, 5, 6)
+
+
+def test_bind_to_gpu_cpus_changes_nothing_without_a_device():
+    # no CUDA device (or no NVML): the helper reports None and leaves the affinity mask alone
+    import os
+    before = os.sched_getaffinity(0)
+    got = dg.bind_to_gpu_cpus(0)
+    if got is None:
+        assert os.sched_getaffinity(0) == before
+    else:  # on a GPU box: a non-empty subset of the mask the process had
+        assert set(got) <= before and set(got) == os.sched_getaffinity(0)
+        os.sched_setaffinity(0, before)
