@@ -402,7 +402,8 @@ def measure(wl, local_rank, world, barrier, all_max, steps, warmup, e2e_steps, c
     # -- end to end through the batch API: host bytes in, host pixels out.  Sub-batches alternate between two contexts
     #    (two streams), the way a host batcher drives the library, so that the device-to-host copy of one sub-batch
     #    overlaps the planning, upload and kernels of the next.
-    chunk = max(1, min(chunk, len(items)))
+    # at least four sub-batches per pass, so that the two contexts have something to overlap on the smaller workloads
+    chunk = max(1, min(chunk, (len(items) + 3) // 4))
     if wl.name == "c4":
         chunk += chunk % 2  # keep the two payloads of a sample in one sub-batch
     max_out = 0
