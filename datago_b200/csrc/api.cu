@@ -472,7 +472,7 @@ struct Planner {
     dg_ctx* ctx;
     dg_batch* b;
     bool final_round = true;   // device addresses are final: tensor maps are encoded (the sizing round skips them)
-    bool tmap_failed = false;  // a tensor map could not be encoded
+    std::atomic<bool> tmap_failed{false};  // a tensor map could not be encoded (items are planned on several threads)
     std::unordered_map<std::string, uint32_t> huff_ids, qt_ids;
     std::vector<HuffTable> huff_pool;
     std::vector<uint32_t> qt_pool;  // 32 words per table, the layout JpegWave::qt32 documents
@@ -1177,28 +1177,54 @@ extern "C" int dg_batch_create(dg_ctx* ctx, const dg_item* items, int n, uint32_
             wv.copies.clear(); wv.copy_first.clear();
             wv.torgb.clear(); wv.torgb_first.clear();
             for (int a = 0; a < 4; ++a) { wv.alpha[a].clear(); wv.alpha_first[a].clear(); }
-            size_t mid_used = 0;
-            for (int i = wv.first_item; i < wv.last_item; ++i) {
-                ItemPlan& it = b->items[i];
-                if (it.status || it.wave < 0) continue;
+            // Every item is planned on its own (the filter tables are all there by now, so the planner is only read):
+            // its intermediates get the slice of the wave's scratch that its worst-case bound reserves, and its passes
+            // and jobs are appended to the wave's lists in item order afterwards.
+            const int n_wave_items = wv.last_item - wv.first_item;
+            std::vector<size_t> mid_at((size_t)n_wave_items + 1, 0);
+            for (int k = 0; k < n_wave_items; ++k) {
+                const ItemPlan& it = b->items[wv.first_item + k];
+                mid_at[k + 1] = mid_at[k] + ((transform && !it.status && it.wave >= 0) ? resize_mid_bound(it.plan, it.c) : 0);
+            }
+            size_t mid_used = mid_at[n_wave_items];
+            std::vector<WavePlan> parts((size_t)n_wave_items);
+            std::atomic<bool> overflow{false};
+            parallel_items(n_wave_items, [&](int k) {
+                ItemPlan& it = b->items[wv.first_item + k];
+                if (it.status || it.wave < 0) return;
+                // encoding a tensor map is a driver call and wants a current context, which the pool's threads do not
+                // have by themselves
+                static thread_local int bound_device = -1;
+                if (bound_device != ctx->device) { if (cudaSetDevice(ctx->device) != cudaSuccess) { pl.tmap_failed = true; return; } bound_device = ctx->device; }
+                WavePlan& part = parts[k];
                 const uint8_t* src = it.is_jpeg ? kBaseS + wv.off_decoded + it.decoded_off : baseP + b->off_rawin + it.raw_in_off;
                 uint8_t* dst = baseP + b->off_out + it.pipe_off;
                 const uint8_t* converted_from = dst;
-                if (transform) plan_resize(pl, wv, it.plan, it.c, src, it.src_pitch, dst, kBaseS + wv.off_mid, &mid_used);
-                else if (!it.is_jpeg) {  // raw pixels, no transform: the payload is the input (JPEGs decode straight into dst)
+                if (transform) {
+                    size_t used = 0;
+                    plan_resize(pl, part, it.plan, it.c, src, it.src_pitch, dst, kBaseS + wv.off_mid + mid_at[k], &used);
+                    if (used > mid_at[k + 1] - mid_at[k]) overflow = true;
+                } else if (!it.is_jpeg) {  // raw pixels, no transform: the payload is the input (JPEGs decode straight into dst)
                     if (it.to_rgb) converted_from = src;  // the conversion reads the input itself
                     else {
                         CopyJob j;
                         j.src = src; j.dst = dst; j.src_pitch = it.w * it.c; j.row_bytes = it.w * it.c; j.rows = it.h; j.tile_first = 0;
-                        wv.copies.push_back(j);
+                        part.copies.push_back(j);
                     }
                 }
                 if (it.to_rgb) {
                     ToRgbJob j;
                     j.src = converted_from; j.dst = baseP + b->off_out + it.out_off; j.npx = it.out_w * it.out_h; j.channels = it.c;
                     j.tile_first = 0; j.pad = 0;
-                    wv.torgb.push_back(j);
+                    part.torgb.push_back(j);
                 }
+            });
+            if (overflow) mid_used = wv.mid_bytes + 1;
+            for (const WavePlan& part : parts) {
+                for (int s = 0; s < 4; ++s) wv.passes[s].insert(wv.passes[s].end(), part.passes[s].begin(), part.passes[s].end());
+                for (int a = 0; a < 4; ++a) wv.alpha[a].insert(wv.alpha[a].end(), part.alpha[a].begin(), part.alpha[a].end());
+                wv.copies.insert(wv.copies.end(), part.copies.begin(), part.copies.end());
+                wv.torgb.insert(wv.torgb.end(), part.torgb.begin(), part.torgb.end());
             }
             if (mid_used > wv.mid_bytes) return abandon(b, fail(DG_E_INVALID, "internal: resize scratch bound exceeded"));
             for (int s = 0; s < 4; ++s) {
